@@ -1,0 +1,3 @@
+"""B200-native ops for the attention code Mercury's CommIR PyTorch backend emits."""
+from . import _lib  # noqa: F401  (fails loudly when libmercury_b200.so is missing)
+from .attention import attn_fwd_segments  # noqa: F401

@@ -1,0 +1,113 @@
+"""ctypes binding of libmercury_b200.so (the C ABI declared in include/mercury_b200.h).
+
+The library is the product: there is no Python or CPU fallback.  If the shared
+object is missing the import of this module raises, and every op raises when a
+call returns a non-zero code.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+MB_MAX_SEGMENTS = 8
+
+MB_SUCCESS = 0
+ERROR_NAMES = {
+    -1: "MB_E_INVALID (bad argument)",
+    -2: "MB_E_UNSUPPORTED (shape or option not implemented by the sm_100a kernels)",
+    -3: "MB_E_CUDA (a CUDA runtime call failed)",
+    -4: "MB_E_TENSORMAP (TMA descriptor rejected: check 16-byte alignment of pointers and strides)",
+    -5: "MB_E_DEVICE (device-side wait timed out)",
+}
+
+STATUS_NAMES = {
+    101: "Q tile never arrived",
+    102: "K/V stage never filled",
+    103: "K/V stage never released",
+    104: "score tile never completed",
+    105: "probabilities never written",
+    106: "output accumulation never completed",
+    107: "staged shard chunk never became ready",
+    108: "unspecified wait",
+}
+
+
+class KVSegment(C.Structure):
+    _fields_ = [
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("stride_b", C.c_int64),
+        ("stride_s", C.c_int64),
+        ("stride_h", C.c_int64),
+        ("sk", C.c_int32),
+        ("k_off", C.c_int32),
+    ]
+
+
+class AttnFwdArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p),
+        ("q_stride_b", C.c_int64),
+        ("q_stride_s", C.c_int64),
+        ("q_stride_h", C.c_int64),
+        ("o", C.c_void_p),
+        ("o_stride_b", C.c_int64),
+        ("o_stride_s", C.c_int64),
+        ("o_stride_h", C.c_int64),
+        ("lse", C.c_void_p),
+        ("batch", C.c_int32),
+        ("sq", C.c_int32),
+        ("hq", C.c_int32),
+        ("hkv", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("q_off", C.c_int32),
+        ("causal", C.c_int32),
+        ("softmax_scale", C.c_float),
+        ("nseg", C.c_int32),
+        ("seg", KVSegment * MB_MAX_SEGMENTS),
+        ("status", C.c_void_p),
+    ]
+
+
+LIB_PATH = Path(__file__).resolve().parent / "libmercury_b200.so"
+
+
+class MercuryB200Error(RuntimeError):
+    pass
+
+
+def _load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m mercury_artifact_b200.build` "
+            "(there is no fallback path)"
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    lib.mb_version.restype = C.c_int
+    lib.mb_version.argtypes = []
+    lib.mb_attn_fwd.restype = C.c_int
+    lib.mb_attn_fwd.argtypes = [C.POINTER(AttnFwdArgs), C.c_void_p]
+    lib.mb_status_fetch.restype = C.c_int
+    lib.mb_status_fetch.argtypes = [C.POINTER(C.c_int32), C.c_void_p]
+    return lib
+
+
+lib = _load()
+
+
+def check(code: int, what: str) -> None:
+    if code != MB_SUCCESS:
+        raise MercuryB200Error(f"{what} failed: {ERROR_NAMES.get(code, code)}")
+
+
+def status_fetch(stream_ptr: int) -> int:
+    """Synchronise the stream and return (then clear) the device status word."""
+    out = C.c_int32(0)
+    check(lib.mb_status_fetch(C.byref(out), C.c_void_p(stream_ptr)), "mb_status_fetch")
+    return int(out.value)
+
+
+def raise_on_status(stream_ptr: int) -> None:
+    st = status_fetch(stream_ptr)
+    if st != 0:
+        raise MercuryB200Error(f"device-side timeout: {STATUS_NAMES.get(st, st)} (code {st})")

@@ -1,0 +1,63 @@
+// extern "C" surface of libmercury_b200.so and the few host utilities the
+// kernels share (TMA descriptor encoding, the per-device status word).
+#include <cudaTypedefs.h>
+
+#include "mb_host.h"
+
+namespace mb {
+
+__device__ int g_status_word = 0;
+
+int* default_status_word() {
+  static int* cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<int*>(p);
+  }
+  return cached[dev];
+}
+
+int encode_tiled_bf16(CUtensorMap* map, void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+                      const cuuint32_t* box, const cuuint32_t* elem_strides) {
+  static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  if (encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || fn == nullptr)
+      return -1;
+    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  }
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), base, dims, strides_bytes,
+                      box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -1;
+}
+
+}  // namespace mb
+
+extern "C" {
+
+int mb_version(void) { return 1000; }
+
+int mb_attn_fwd(const mb_attn_fwd_args* args, void* cuda_stream) {
+  return mb::launch_attn_fwd(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int mb_status_fetch(int32_t* out, void* cuda_stream) {
+  if (out == nullptr) return MB_E_INVALID;
+  int* word = mb::default_status_word();
+  if (word == nullptr) return MB_E_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  int host = 0;
+  if (cudaMemcpyAsync(&host, word, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return MB_E_CUDA;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return MB_E_CUDA;
+  if (host != 0 && cudaMemsetAsync(word, 0, sizeof(int), st) != cudaSuccess) return MB_E_CUDA;
+  *out = host;
+  return MB_SUCCESS;
+}
+
+}  // extern "C"

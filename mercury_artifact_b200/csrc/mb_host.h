@@ -1,0 +1,21 @@
+// Host-side declarations shared by the translation units of libmercury_b200.so.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include "mercury_b200.h"
+
+namespace mb {
+
+// Encode a tiled bf16 TMA descriptor with 128-byte swizzle.  Returns 0 on success.
+int encode_tiled_bf16(CUtensorMap* map, void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+                      const cuuint32_t* box, const cuuint32_t* elem_strides);
+
+// Device address of the library's status word on the current device (nullptr on failure).
+int* default_status_word();
+
+int launch_attn_fwd(const mb_attn_fwd_args* args, cudaStream_t stream);
+
+}  // namespace mb

@@ -70,6 +70,50 @@ typedef struct mb_attn_fwd_args {
  * A row that sees no key gets o = 0 and lse = -inf. */
 MB_API int mb_attn_fwd(const mb_attn_fwd_args* args, void* cuda_stream);
 
+#define MB_DTYPE_BF16 0
+#define MB_DTYPE_F32 1
+
+typedef struct mb_merge_args {
+  float* out;            /* [batch, seq, heads, head_dim] fp32 contiguous, updated in place */
+  float* lse;            /* [batch, seq, heads, 1] fp32 contiguous, updated in place */
+  const void* block_out; /* [batch, seq, heads, head_dim], bf16 or fp32 */
+  int64_t block_stride_b, block_stride_s, block_stride_h;
+  const float* block_lse; /* [batch, heads, seq] fp32 contiguous */
+  int32_t batch, seq, heads, head_dim;
+  int32_t first;       /* non-zero: adopt the block (the reference's out-is-None call) */
+  int32_t block_dtype; /* MB_DTYPE_* of block_out */
+} mb_merge_args;
+
+/* One step of the running out/LSE merge:
+ *   out <- out - sigmoid(block_lse - lse) * (out - block_out)
+ *   lse <- lse - logsigmoid(lse - block_lse)
+ * Replaces update_out_and_lse / _update_out_and_lse, utils/flash_attn_dsl.py:31-71.
+ * Rows whose block_lse is -inf are left unchanged; rows whose lse is -inf adopt the block. */
+MB_API int mb_merge_out_lse(const mb_merge_args* args, void* cuda_stream);
+
+/* ---- peer memory over NVLink (one process per GPU) ------------------------------------
+ * Together these replace SendRecv.send_recv / commit / wait of
+ * mercury/backend/pytorch/utils.py:9-39 (NCCL batch_isend_irecv): a send is a copy into the
+ * peer's inbox followed by mb_flag_signal on the peer's flag; a wait is mb_flag_wait on the
+ * local flag. */
+
+/* cudaMalloc-backed allocation that mb_ipc_export can share with the other ranks. */
+MB_API int mb_mem_alloc(void** ptr, uint64_t bytes);
+MB_API int mb_mem_free(void* ptr);
+MB_API int mb_mem_zero(void* ptr, uint64_t bytes, void* cuda_stream);
+/* 64-byte handle of an mb_mem_alloc allocation / mapping of a peer's handle into this process. */
+MB_API int mb_ipc_export(void* ptr, unsigned char* handle64);
+MB_API int mb_ipc_import(const unsigned char* handle64, void** ptr);
+MB_API int mb_ipc_release(void* ptr);
+/* Stream-ordered copy; either side may be a peer mapping (copy engines over NVLink). */
+MB_API int mb_copy_async(void* dst, const void* src, uint64_t bytes, void* cuda_stream);
+/* Stream-ordered release-store of `value` to a flag word (local or peer mapping). */
+MB_API int mb_flag_signal(int32_t* flag, int32_t value, void* cuda_stream);
+/* Stream-ordered wait until *flag >= value.  After timeout_ns the wait gives up, writes a
+ * timeout code to `status` (NULL: the library's word) and lets the stream continue. */
+MB_API int mb_flag_wait(const int32_t* flag, int32_t value, uint64_t timeout_ns, int32_t* status,
+                        void* cuda_stream);
+
 /* Synchronise `cuda_stream`, copy the library's status word of the current
  * device into *out (0 = no device-side timeout so far) and clear it. */
 MB_API int mb_status_fetch(int32_t* out, void* cuda_stream);

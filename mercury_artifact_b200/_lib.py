@@ -69,6 +69,28 @@ class AttnFwdArgs(C.Structure):
     ]
 
 
+MB_DTYPE_BF16 = 0
+MB_DTYPE_F32 = 1
+
+
+class MergeArgs(C.Structure):
+    _fields_ = [
+        ("out", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("block_out", C.c_void_p),
+        ("block_stride_b", C.c_int64),
+        ("block_stride_s", C.c_int64),
+        ("block_stride_h", C.c_int64),
+        ("block_lse", C.c_void_p),
+        ("batch", C.c_int32),
+        ("seq", C.c_int32),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("first", C.c_int32),
+        ("block_dtype", C.c_int32),
+    ]
+
+
 LIB_PATH = Path(__file__).resolve().parent / "libmercury_b200.so"
 
 
@@ -87,6 +109,22 @@ def _load() -> C.CDLL:
     lib.mb_version.argtypes = []
     lib.mb_attn_fwd.restype = C.c_int
     lib.mb_attn_fwd.argtypes = [C.POINTER(AttnFwdArgs), C.c_void_p]
+    lib.mb_merge_out_lse.restype = C.c_int
+    lib.mb_merge_out_lse.argtypes = [C.POINTER(MergeArgs), C.c_void_p]
+    for name, argtypes in {
+        "mb_mem_alloc": [C.POINTER(C.c_void_p), C.c_uint64],
+        "mb_mem_free": [C.c_void_p],
+        "mb_mem_zero": [C.c_void_p, C.c_uint64, C.c_void_p],
+        "mb_ipc_export": [C.c_void_p, C.POINTER(C.c_ubyte)],
+        "mb_ipc_import": [C.POINTER(C.c_ubyte), C.POINTER(C.c_void_p)],
+        "mb_ipc_release": [C.c_void_p],
+        "mb_copy_async": [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p],
+        "mb_flag_signal": [C.c_void_p, C.c_int32, C.c_void_p],
+        "mb_flag_wait": [C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p],
+    }.items():
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = argtypes
     lib.mb_status_fetch.restype = C.c_int
     lib.mb_status_fetch.argtypes = [C.POINTER(C.c_int32), C.c_void_p]
     return lib

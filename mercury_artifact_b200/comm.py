@@ -1,0 +1,262 @@
+"""Peer-to-peer transport for one-process-per-GPU jobs and the SendRecv drop-in.
+
+torch.distributed (any backend) is used once per buffer to exchange IPC handles;
+after that every byte moves through peer mappings over NVLink: copies run on the
+copy engines, completion is a flag word raised in the receiver's memory, waits
+are bounded spins in a one-thread kernel (C ABI: mb_copy_async, mb_flag_signal,
+mb_flag_wait).
+
+`SendRecv` keeps the interface of mercury/backend/pytorch/utils.py:9-39
+(send_recv / commit / wait, "commit called twice" / "wait called before commit"
+errors, one outstanding batch per object) so the generated text runs unchanged.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import weakref
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_FLAG_TIMEOUT_NS = int(float(os.environ.get("MB_FLAG_TIMEOUT_MS", "5000")) * 1e6)
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class DeviceBuffer:
+    """An IPC-shareable device allocation owned by the library (mb_mem_alloc)."""
+
+    def __init__(self, nbytes: int, device: torch.device):
+        self.nbytes = int(nbytes)
+        self.device = torch.device(device)
+        ptr = C.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib.mb_mem_alloc(C.byref(ptr), C.c_uint64(self.nbytes)), "mb_mem_alloc")
+            self.ptr = int(ptr.value or 0)
+            _lib.check(
+                _lib.lib.mb_mem_zero(C.c_void_p(self.ptr), C.c_uint64(self.nbytes),
+                                     C.c_void_p(torch.cuda.current_stream().cuda_stream)), "mb_mem_zero")
+        self._bytes_view: Optional[torch.Tensor] = None
+
+    @property
+    def __cuda_array_interface__(self):
+        return {"shape": (self.nbytes,), "typestr": "|u1", "data": (self.ptr, False), "version": 2}
+
+    def bytes(self) -> torch.Tensor:
+        if self._bytes_view is None:
+            self._bytes_view = torch.as_tensor(self, device=self.device)
+        return self._bytes_view
+
+    def view(self, offset: int, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.bytes()[offset:offset + nbytes].view(dtype).view(*shape)
+
+    def export_handle(self) -> bytes:
+        buf = (C.c_ubyte * 64)()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib.mb_ipc_export(C.c_void_p(self.ptr), buf), "mb_ipc_export")
+        return bytes(buf)
+
+    def free(self) -> None:
+        if self.ptr:
+            self._bytes_view = None
+            with torch.cuda.device(self.device):
+                _lib.lib.mb_mem_free(C.c_void_p(self.ptr))
+            self.ptr = 0
+
+
+class SymmetricBuffer:
+    """The same-sized allocation on every rank, with every peer's copy mapped locally."""
+
+    def __init__(self, ctx: "PeerContext", nbytes: int):
+        import torch.distributed as dist
+
+        self.ctx = ctx
+        self.nbytes = _align(nbytes)
+        self.local = DeviceBuffer(self.nbytes, ctx.device)
+        torch.cuda.current_stream().synchronize()
+        handles: List[Optional[bytes]] = [None] * ctx.world
+        if ctx.world > 1:
+            dist.all_gather_object(handles, self.local.export_handle(), group=ctx.group)
+        self.peer_ptr: List[int] = [0] * ctx.world
+        self.peer_ptr[ctx.rank] = self.local.ptr
+        for r, h in enumerate(handles):
+            if r == ctx.rank or h is None:
+                continue
+            p = C.c_void_p()
+            hb = (C.c_ubyte * 64).from_buffer_copy(h)
+            with torch.cuda.device(ctx.device):
+                _lib.check(_lib.lib.mb_ipc_import(hb, C.byref(p)), f"mb_ipc_import(rank {r})")
+            self.peer_ptr[r] = int(p.value)
+        if ctx.world > 1:
+            dist.barrier(group=ctx.group)
+
+    def ptr(self, rank: int, offset: int = 0) -> int:
+        return self.peer_ptr[rank] + offset
+
+
+class PeerContext:
+    """Per-process state: rank/world, the side stream that carries transfers, flag helpers."""
+
+    def __init__(self, group=None, device: Optional[torch.device] = None):
+        import torch.distributed as dist
+
+        if dist.is_available() and dist.is_initialized():
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        else:
+            self.rank, self.world = 0, 1
+        self.group = group
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.comm_stream = torch.cuda.Stream(device=self.device)
+        self._channels: Dict[Tuple[int, int], "_Channel"] = {}
+
+    # -- primitive, stream-ordered operations ----------------------------------------------
+    def copy(self, dst_ptr: int, src_ptr: int, nbytes: int, stream: torch.cuda.Stream) -> None:
+        _lib.check(_lib.lib.mb_copy_async(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), C.c_uint64(nbytes),
+                                          C.c_void_p(stream.cuda_stream)), "mb_copy_async")
+
+    def signal(self, flag_ptr: int, value: int, stream: torch.cuda.Stream) -> None:
+        _lib.check(_lib.lib.mb_flag_signal(C.c_void_p(flag_ptr), C.c_int32(value), C.c_void_p(stream.cuda_stream)),
+                   "mb_flag_signal")
+
+    def wait_flag(self, flag_ptr: int, value: int, stream: torch.cuda.Stream, timeout_ns: Optional[int] = None) -> None:
+        _lib.check(_lib.lib.mb_flag_wait(C.c_void_p(flag_ptr), C.c_int32(value),
+                                         C.c_uint64(_FLAG_TIMEOUT_NS if timeout_ns is None else timeout_ns),
+                                         None, C.c_void_p(stream.cuda_stream)), "mb_flag_wait")
+
+    def check(self) -> None:
+        """Synchronise and raise if any device-side wait timed out since the last check."""
+        with torch.cuda.device(self.device):
+            _lib.raise_on_status(torch.cuda.current_stream().cuda_stream)
+
+    # -- channels for SendRecv ---------------------------------------------------------------
+    def acquire_channel(self, nbytes: int, owner) -> "_Channel":
+        slot = _align(nbytes)
+        idx = 0
+        while True:
+            ch = self._channels.get((slot, idx))
+            if ch is None:
+                ch = _Channel(self, slot)
+                self._channels[(slot, idx)] = ch
+            if ch.owner is None or ch.owner() is None:
+                ch.owner = weakref.ref(owner)
+                return ch
+            idx += 1
+
+
+class _Channel:
+    """Two inbox slots plus flags for one stream of same-sized messages.
+
+    Flag words (int32), all in the receiver's memory:
+      ready[slot]  raised by the sender after its copy into inbox[slot] landed
+      credit[slot] raised by the receiver when inbox[slot] may be overwritten
+    Message m of the channel uses slot m % 2 and flag value m + 1 (never reset).
+    """
+
+    FLAG_BYTES = 256
+
+    def __init__(self, ctx: PeerContext, slot_bytes: int):
+        self.ctx = ctx
+        self.slot_bytes = slot_bytes
+        self.buf = SymmetricBuffer(ctx, 2 * slot_bytes + self.FLAG_BYTES)
+        self.seq = 0
+        self.owner = None
+
+    def inbox_ptr(self, rank: int, slot: int) -> int:
+        return self.buf.ptr(rank, slot * self.slot_bytes)
+
+    def ready_ptr(self, rank: int, slot: int) -> int:
+        return self.buf.ptr(rank, 2 * self.slot_bytes + 4 * slot)
+
+    def credit_ptr(self, rank: int, slot: int) -> int:
+        return self.buf.ptr(rank, 2 * self.slot_bytes + 16 + 4 * slot)
+
+
+_default_ctx: Optional[PeerContext] = None
+
+
+def init_p2p(group=None, device=None) -> PeerContext:
+    """Create (once) the process-wide peer context; call after init_process_group."""
+    global _default_ctx
+    if _default_ctx is None:
+        _default_ctx = PeerContext(group=group, device=device)
+    return _default_ctx
+
+
+def default_context() -> PeerContext:
+    if _default_ctx is None:
+        return init_p2p()
+    return _default_ctx
+
+
+class SendRecv:
+    """Drop-in for the reference's SendRecv: a batched send + receive between ring neighbours.
+
+    send_recv() only records the exchange; commit() enqueues it on the transfer stream
+    (grant credit to the sender, wait for the receiver's credit, copy into its inbox slot,
+    raise its ready flag); wait() makes the caller's stream wait for the incoming message.
+    """
+
+    def __init__(self, ctx: Optional[PeerContext] = None):
+        self._ctx = ctx
+        self._ops: List[tuple] = []
+        self._pending: Optional[list] = None
+        self._channel: Optional[_Channel] = None
+
+    def send_recv(self, to_rank: int, from_rank: int, send_tensor: torch.Tensor,
+                  recv_tensor: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self._ctx is None:
+            self._ctx = default_context()
+        send_tensor = send_tensor.contiguous()
+        nbytes = send_tensor.numel() * send_tensor.element_size()
+        if self._channel is None or self._channel.slot_bytes != _align(nbytes):
+            self._channel = self._ctx.acquire_channel(nbytes, self)
+        ch = self._channel
+        seq = ch.seq
+        ch.seq += 1
+        slot = seq % 2
+        inbox = ch.buf.local.view(slot * ch.slot_bytes, send_tensor.shape, send_tensor.dtype)
+        self._ops.append((to_rank, from_rank, send_tensor, inbox, recv_tensor, seq, nbytes))
+        return inbox if recv_tensor is None else recv_tensor
+
+    def commit(self) -> None:
+        if self._pending is not None:
+            raise RuntimeError("commit called twice")
+        ctx = self._ctx or default_context()
+        main = torch.cuda.current_stream()
+        comm = ctx.comm_stream
+        comm.wait_stream(main)
+        pending = []
+        for to_rank, from_rank, send_tensor, inbox, recv_tensor, seq, nbytes in self._ops:
+            ch, slot, val = self._channel, seq % 2, seq + 1
+            # Grant my sender the slot (everything queued so far on my stream has run by now);
+            # the credit word lives in the SENDER's memory, so this store crosses NVLink.
+            ctx.signal(ch.credit_ptr(from_rank, slot), val, comm)
+            # Wait for the grant of the rank I send to (a word in my own memory).
+            ctx.wait_flag(ch.credit_ptr(ctx.rank, slot), val, comm)
+            ctx.copy(ch.inbox_ptr(to_rank, slot), send_tensor.data_ptr(), nbytes, comm)
+            ctx.signal(ch.ready_ptr(to_rank, slot), val, comm)
+            pending.append((ch, slot, val, inbox, recv_tensor, send_tensor))
+        self._pending = pending
+
+    def wait(self) -> None:
+        if self._pending is None:
+            raise RuntimeError("wait called before commit")
+        ctx = self._ctx or default_context()
+        comm = ctx.comm_stream
+        for ch, slot, val, inbox, recv_tensor, _send in self._pending:
+            ctx.wait_flag(ch.ready_ptr(ctx.rank, slot), val, comm)
+            if recv_tensor is not None:
+                with torch.cuda.stream(comm):
+                    recv_tensor.copy_(inbox)
+        torch.cuda.current_stream().wait_stream(comm)
+        self._pending = None
+        self._ops = []

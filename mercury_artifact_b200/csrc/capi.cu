@@ -47,6 +47,10 @@ int mb_attn_fwd(const mb_attn_fwd_args* args, void* cuda_stream) {
   return mb::launch_attn_fwd(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int mb_merge_out_lse(const mb_merge_args* args, void* cuda_stream) {
+  return mb::launch_merge(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int mb_status_fetch(int32_t* out, void* cuda_stream) {
   if (out == nullptr) return MB_E_INVALID;
   int* word = mb::default_status_word();

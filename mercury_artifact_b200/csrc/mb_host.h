@@ -17,5 +17,6 @@ int encode_tiled_bf16(CUtensorMap* map, void* base, int rank, const cuuint64_t* 
 int* default_status_word();
 
 int launch_attn_fwd(const mb_attn_fwd_args* args, cudaStream_t stream);
+int launch_merge(const mb_merge_args* args, cudaStream_t stream);
 
 }  // namespace mb

@@ -1,0 +1,115 @@
+// Running out/LSE merge of partial attention results (HBM-bound, element-wise).
+//
+// Replaces update_out_and_lse / _update_out_and_lse of the reference
+// (utils/flash_attn_dsl.py:31-71): the generated ring loop calls it once per
+// step on the fp32 state out[B,S,H,D], lse[B,S,H,1] with the block result
+// block_out[B,S,H,D] (input dtype) and block_lse[B,H,S] (fp32, note the
+// transposed layout).  The reference spends about eight eager element-wise
+// kernels per step on this; here it is one pass: 4+2 bytes read and 4 bytes
+// written per output element.
+#include <cuda_bf16.h>
+
+#include "mb_host.h"
+
+namespace mb {
+
+struct MergeArgs {
+  float* out;             // [B,S,H,D] contiguous
+  float* lse;             // [B,S,H] contiguous (the reference's [B,S,H,1])
+  const void* block_out;  // bf16 or fp32, strides in elements, D contiguous
+  long long bo_sb, bo_ss, bo_sh;
+  const float* block_lse;  // [B,H,S] contiguous
+  int B, S, H, D;
+  int first;         // 1: adopt the block (first ring step)
+  int block_is_f32;  // dtype of block_out
+};
+
+__device__ __forceinline__ float4 load4(const void* base, long long idx, int is_f32) {
+  if (is_f32) return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx);
+  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + idx);
+  float4 r;
+  r.x = __uint_as_float(raw.x << 16);
+  r.y = __uint_as_float(raw.x & 0xffff0000u);
+  r.z = __uint_as_float(raw.y << 16);
+  r.w = __uint_as_float(raw.y & 0xffff0000u);
+  return r;
+}
+
+// One warp per (b, s, h) row; each lane walks the row in float4 steps.
+__global__ void __launch_bounds__(256) merge_kernel(const MergeArgs a) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long rows = static_cast<long long>(a.B) * a.S * a.H;
+  for (long long row = warp0; row < rows; row += nwarps) {
+    const int h = static_cast<int>(row % a.H);
+    const long long bs = row / a.H;
+    const int s = static_cast<int>(bs % a.S);
+    const int b = static_cast<int>(bs / a.S);
+    const float bl = a.block_lse[(static_cast<long long>(b) * a.H + h) * a.S + s];
+    const float l = a.first ? -INFINITY : a.lse[row];
+    // weight of the block and the merged LSE
+    float w, new_l;
+    if (l == -INFINITY) {  // nothing accumulated yet for this row
+      w = 1.f;
+      new_l = bl;
+    } else if (bl == -INFINITY) {  // the block saw no key for this row
+      w = 0.f;
+      new_l = l;
+    } else {
+      const float x = bl - l;
+      w = 1.f / (1.f + expf(-x));                          // sigmoid(block_lse - lse)
+      new_l = l + fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));  // lse - logsigmoid(lse - block_lse)
+    }
+    float* orow = a.out + row * a.D;
+    const long long brow = b * a.bo_sb + s * a.bo_ss + h * a.bo_sh;
+    for (int d = lane * 4; d < a.D; d += 128) {
+      const float4 bo = load4(a.block_out, brow + d, a.block_is_f32);
+      float4 o;
+      if (w == 1.f) {
+        o = bo;
+      } else {
+        o = *reinterpret_cast<const float4*>(orow + d);
+        o.x -= w * (o.x - bo.x);
+        o.y -= w * (o.y - bo.y);
+        o.z -= w * (o.z - bo.z);
+        o.w -= w * (o.w - bo.w);
+      }
+      *reinterpret_cast<float4*>(orow + d) = o;
+    }
+    if (lane == 0) a.lse[row] = new_l;
+  }
+}
+
+int launch_merge(const mb_merge_args* x, cudaStream_t stream) {
+  if (x == nullptr || x->out == nullptr || x->lse == nullptr || x->block_out == nullptr || x->block_lse == nullptr)
+    return MB_E_INVALID;
+  if (x->batch < 0 || x->seq < 0 || x->heads < 0 || x->head_dim <= 0) return MB_E_INVALID;
+  if (x->head_dim % 4 != 0) return MB_E_UNSUPPORTED;
+  if (x->block_dtype != MB_DTYPE_BF16 && x->block_dtype != MB_DTYPE_F32) return MB_E_UNSUPPORTED;
+  const long long rows = static_cast<long long>(x->batch) * x->seq * x->heads;
+  if (rows == 0) return MB_SUCCESS;
+  MergeArgs a;
+  a.out = x->out;
+  a.lse = x->lse;
+  a.block_out = x->block_out;
+  a.bo_sb = x->block_stride_b;
+  a.bo_ss = x->block_stride_s;
+  a.bo_sh = x->block_stride_h;
+  a.block_lse = x->block_lse;
+  a.B = x->batch;
+  a.S = x->seq;
+  a.H = x->heads;
+  a.D = x->head_dim;
+  a.first = x->first ? 1 : 0;
+  a.block_is_f32 = x->block_dtype == MB_DTYPE_F32;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long want = (rows + 7) / 8;  // 8 warps per block
+  const long long cap = static_cast<long long>(sms) * 8;
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  merge_kernel<<<grid, 256, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+}
+
+}  // namespace mb

@@ -1,0 +1,81 @@
+"""Wiring the drop-in ops into the reference's code generator output.
+
+The generated program finds its ops in two ways (reference: example.py:153-156,
+mercury/backend/pytorch/codegen.py:219):
+  * free names looked up in the namespace given to exec():
+    _flash_attn_forward, _flash_attn_backward, get_default_args, update_out_and_lse
+  * `from mercury.backend import *` executed by the generated text itself:
+    SendRecv and the mesh index helpers.
+
+`namespace()` serves the first, `install_backend()` the second.
+"""
+from __future__ import annotations
+
+import sys
+import types
+from typing import Dict
+
+from . import mesh, ops
+
+
+def namespace(extra: Dict[str, object] | None = None) -> Dict[str, object]:
+    """Globals for exec(generated_code, ns): every free name the DSL bodies use."""
+    ns: Dict[str, object] = {
+        "_flash_attn_forward": ops._flash_attn_forward,
+        "get_default_args": ops.get_default_args,
+        "update_out_and_lse": ops.update_out_and_lse,
+    }
+    if hasattr(ops, "_flash_attn_backward"):
+        ns["_flash_attn_backward"] = ops._flash_attn_backward
+    if extra:
+        ns.update(extra)
+    return ns
+
+
+_RUNTIME_NAMES = ("one_dim_to_n_dim", "n_dim_to_one_dim", "shift_tuple_element", "get_src_dst_ranks")
+
+
+def install_backend(send_recv_cls=None, force_stub: bool = False) -> types.ModuleType:
+    """Make `from mercury.backend import *` hand out this package's SendRecv.
+
+    With the reference importable, only SendRecv is replaced (on mercury.backend,
+    mercury.backend.pytorch and mercury.backend.pytorch.utils) and everything else is the
+    reference's own.  Without it, a stand-in `mercury.backend` module is registered that
+    exports SendRecv and the mesh index helpers, which is all the generated text imports.
+    """
+    if send_recv_cls is None:
+        from .comm import SendRecv as send_recv_cls  # noqa: N813
+    if not force_stub:
+        try:
+            import mercury.backend as mb_backend  # type: ignore
+            import mercury.backend.pytorch as mb_pt  # type: ignore
+            import mercury.backend.pytorch.utils as mb_utils  # type: ignore
+
+            if not getattr(mb_backend, "__mercury_b200_stub__", False):
+                for mod in (mb_backend, mb_pt, mb_utils):
+                    setattr(mod, "SendRecv", send_recv_cls)
+                return mb_backend
+        except ImportError:
+            pass
+    pkg = sys.modules.get("mercury")
+    if pkg is None or not getattr(pkg, "__mercury_b200_stub__", False):
+        pkg = types.ModuleType("mercury")
+        pkg.__path__ = []  # type: ignore[attr-defined]
+        pkg.__mercury_b200_stub__ = True  # type: ignore[attr-defined]
+        sys.modules["mercury"] = pkg
+    backend = types.ModuleType("mercury.backend")
+    backend.__mercury_b200_stub__ = True  # type: ignore[attr-defined]
+    backend.SendRecv = send_recv_cls  # type: ignore[attr-defined]
+    for name in _RUNTIME_NAMES:
+        setattr(backend, name, getattr(mesh, name))
+    backend.__all__ = ["SendRecv", *_RUNTIME_NAMES]  # type: ignore[attr-defined]
+    sys.modules["mercury.backend"] = backend
+    pkg.backend = backend  # type: ignore[attr-defined]
+    return backend
+
+
+def load_generated(code: str, extra: Dict[str, object] | None = None) -> Dict[str, object]:
+    """exec() a program emitted by mercury.backend.generate_pytorch_code with the drop-in ops."""
+    ns = namespace(extra)
+    exec(compile(code, "<mercury generated>", "exec"), ns)
+    return ns

@@ -1,0 +1,67 @@
+"""Programs emitted by the reference's code generator, run with this package's drop-in ops.
+
+The program text in tests/golden/gpu_*.gen.txt was produced by the unmodified reference
+compiler (see tests/golden/make_golden.py).  It is exec'd here exactly as example.py of the
+reference does, for P virtual ranks on one device; only the transport is a test double.
+"""
+import pytest
+import torch
+
+from tests.helpers import golden_text, seeded_qkv, shard_inputs
+from tests.virtual_ranks import MailboxSendRecv, run_ranks
+
+pytestmark = pytest.mark.gpu
+
+O_TOL, LSE_TOL = 2e-2, 1e-3
+
+
+def _run_forward(name, fn_name, world, B, S, H, hkv):
+    import mercury_artifact_b200 as mb
+    from oracle import block
+
+    mb.install_backend(send_recv_cls=MailboxSendRecv, force_stub=True)
+    ns = mb.load_generated(golden_text(name))
+    fn = ns[fn_name]
+    q, k, v, _ = seeded_qkv(1234, B, S, H, hkv, 128)
+    qs, kvs = shard_inputs(q, k, v, world)
+    scale = 128 ** -0.5
+
+    def rank_body(r):
+        lq, lkv = qs[r].cuda(), kvs[r].cuda()
+        o = torch.zeros_like(lq)
+        lse = torch.zeros(B, H, S // world, device="cuda")
+        fn(lq, lkv, o, lse, scale)
+        return o.float().cpu(), lse.cpu()
+
+    res = run_ranks(world, rank_body)
+    fo, fl = block.full_attention(q, k, v, scale)
+    for r in range(world):
+        assert (res[r][0] - fo.chunk(world, 1)[r].float()).abs().max().item() <= O_TOL
+        assert (res[r][1] - fl.chunk(world, 2)[r]).abs().max().item() <= LSE_TOL
+    from mercury_artifact_b200 import _lib
+
+    assert _lib.status_fetch(torch.cuda.current_stream().cuda_stream) == 0
+
+
+def test_unsharded_program():
+    _run_forward("gpu_ring_p1", "flash_attn_pack_kv", 1, 1, 512, 4, 4)
+
+
+def test_ring_program_two_ranks():
+    _run_forward("gpu_ring_p2", "flash_attn_pack_kv", 2, 1, 1024, 4, 4)
+
+
+def test_ring_program_four_ranks():
+    _run_forward("gpu_ring_p4", "flash_attn_pack_kv", 4, 1, 2048, 4, 4)
+
+
+def test_gqa_ring_program():
+    _run_forward("gpu_gqa_p2", "gqa_pack_kv", 2, 2, 1024, 8, 2)
+
+
+def test_double_ring_program_2x2():
+    _run_forward("gpu_double_ring_2x2", "flash_attn_pack_split_kv", 4, 1, 2048, 4, 4)
+
+
+def test_double_ring_program_4x2():
+    _run_forward("gpu_double_ring_4x2", "flash_attn_pack_split_kv", 8, 1, 4096, 2, 2)

@@ -1,0 +1,141 @@
+"""CPU tests: mesh helpers, schedules, the exported C ABI, the drop-in namespace."""
+import ctypes
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol():
+    from mercury_artifact_b200 import _lib
+
+    header = (ROOT / "include" / "mercury_b200.h").read_text()
+    declared = set(re.findall(r"MB_API\s+\w[\w\s\*]*?\b(mb_\w+)\s*\(", header))
+    assert {"mb_attn_fwd", "mb_merge_out_lse", "mb_status_fetch", "mb_version", "mb_flag_wait"} <= declared
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in mercury_b200.h but not exported"
+    out = subprocess.run(["nm", "-D", "--defined-only", str(_lib.LIB_PATH)], capture_output=True, text=True).stdout
+    exported = {line.split()[-1] for line in out.splitlines() if " T " in line}
+    assert declared <= exported
+    assert _lib.lib.mb_version() >= 1000
+
+
+def test_argument_validation_needs_no_gpu():
+    from mercury_artifact_b200 import _lib
+
+    assert _lib.lib.mb_attn_fwd(None, None) == -1
+    a = _lib.AttnFwdArgs()
+    a.head_dim = 64
+    assert _lib.lib.mb_attn_fwd(ctypes.byref(a), None) == -2  # only head_dim 128 is built
+    a.head_dim, a.batch, a.hq, a.hkv, a.nseg = 128, 1, 3, 2, 1
+    assert _lib.lib.mb_attn_fwd(ctypes.byref(a), None) == -1  # hq not a multiple of hkv
+    a.hq, a.nseg = 4, 9
+    assert _lib.lib.mb_attn_fwd(ctypes.byref(a), None) == -1  # too many segments
+    assert _lib.lib.mb_merge_out_lse(None, None) == -1
+    assert _lib.lib.mb_flag_signal(None, 1, None) == -1
+
+
+def test_mesh_helpers_match_oracle_and_reference_semantics():
+    from mercury_artifact_b200 import mesh
+    from oracle import ring
+
+    for shape in [(2,), (8,), (2, 2), (4, 2), (2, 4), (2, 2, 2)]:
+        p = 1
+        for n in shape:
+            p *= n
+        for r in range(p):
+            c = mesh.one_dim_to_n_dim(r, shape)
+            assert c == ring.coords_of(r, shape) and mesh.n_dim_to_one_dim(c, shape) == r
+            assert mesh.kv_origin_schedule(r, shape) == ring.kv_origin_schedule(r, shape)
+            dims = tuple(range(len(shape)))
+            assert mesh.get_src_dst_ranks(c, shape, dims) == ring.writeback_src_dst(c, shape, list(dims))
+    assert mesh.one_dim_to_n_dim(5, (4, 2)) == (1, 1)
+    assert mesh.shift_tuple_element((0, 1), 0, -1, 4) == (3, 1)
+    assert mesh.shift_tuple_element((3, 1), 0, 1, 4) == (0, 1)
+
+
+@pytest.mark.skipif(not Path("/root/reference/mercury").exists(), reason="reference checkout not present")
+def test_mesh_helpers_equal_reference_functions():
+    sys.path.insert(0, "/root/reference")
+    sys.dont_write_bytecode = True
+    try:
+        from mercury.backend.pytorch import utils as ref
+    finally:
+        sys.path.pop(0)
+    from mercury_artifact_b200 import mesh
+
+    for shape in [(8,), (4, 2), (2, 2, 2)]:
+        p = 1
+        for n in shape:
+            p *= n
+        for r in range(p):
+            c = ref.one_dim_to_n_dim(r, shape)
+            assert mesh.one_dim_to_n_dim(r, shape) == c
+            assert mesh.n_dim_to_one_dim(c, shape) == ref.n_dim_to_one_dim(c, shape)
+            for d in range(len(shape)):
+                for delta in (-1, 1, -shape[d]):
+                    assert mesh.shift_tuple_element(c, d, delta, shape[d]) == ref.shift_tuple_element(c, d, delta, shape[d])
+            dims = list(range(len(shape)))
+            assert mesh.get_src_dst_ranks(c, shape, tuple(dims)) == ref.get_src_dst_ranks(c, shape, dims)
+
+
+def test_get_default_args_and_namespace():
+    import mercury_artifact_b200 as mb
+
+    d = mb.get_default_args(mb._flash_attn_forward)
+    assert list(d)[:6] == ["q", "k", "v", "dropout_p", "softmax_scale", "causal"]
+    assert d["softcap"] == 0.0 and d["q"] is None
+    ns = mb.namespace()
+    assert {"_flash_attn_forward", "get_default_args", "update_out_and_lse"} <= set(ns)
+    backend = mb.install_backend(force_stub=True)
+    scope = {}
+    exec("from mercury.backend import *", scope)
+    assert scope["SendRecv"] is backend.SendRecv and scope["one_dim_to_n_dim"](5, (4, 2)) == (1, 1)
+
+
+def test_cpu_tensors_are_rejected_loudly():
+    import mercury_artifact_b200 as mb
+
+    q = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="no CPU path"):
+        mb._flash_attn_forward(q, q, q, 0.0, 1.0, False)
+    with pytest.raises(ValueError, match="no CPU path"):
+        mb.update_out_and_lse(None, None, q, torch.zeros(1, 1, 128))
+
+
+def test_generated_programs_run_on_virtual_ranks_with_oracle_ops():
+    """The virtual-rank harness itself, on CPU: reference-emitted text + oracle ops == golden."""
+    import mercury_artifact_b200 as mb
+    from oracle import block, merge
+    from tests.helpers import golden_text, load_golden, shard_inputs
+    from tests.virtual_ranks import MailboxSendRecv, run_ranks
+
+    def fwd(q, k, v, dropout_p, softmax_scale, causal, window_size_left, window_size_right, softcap, alibi_slopes,
+            return_softmax):
+        o, l = block.block_attn_fwd(q, k, v, softmax_scale, causal=causal)
+        return o, l, None, None
+
+    mb.install_backend(send_recv_cls=MailboxSendRecv, force_stub=True)
+    for name, fn_name in [("ring_p2", "flash_attn_pack_kv"), ("double_ring_2x2", "flash_attn_pack_split_kv")]:
+        g = load_golden(name)
+        ns = {"_flash_attn_forward": fwd, "get_default_args": mb.get_default_args,
+              "update_out_and_lse": merge.update_out_and_lse}
+        exec(golden_text(name), ns)
+        qs, kvs = shard_inputs(g["t"]["q"], g["t"]["k"], g["t"]["v"], g["world"])
+
+        def body(r):
+            o = torch.zeros_like(qs[r])
+            lse = torch.zeros(g["B"], g["H"], g["S"] // g["world"])
+            ns[fn_name](qs[r], kvs[r], o, lse, g["D"] ** -0.5)
+            return o, lse
+
+        res = run_ranks(g["world"], body)
+        for r in range(g["world"]):
+            assert torch.allclose(res[r][0], g["t"][f"o_rank{r}"], atol=2e-6)
+            assert torch.allclose(res[r][1], g["t"][f"lse_rank{r}"], atol=2e-6)

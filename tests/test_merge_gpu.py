@@ -1,0 +1,60 @@
+"""The merge kernel against the oracle's restatement of update_out_and_lse."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(1, 128, 2, 128), (2, 333, 5, 64), (1, 4096, 32, 128)])
+def test_running_merge_matches_oracle(dtype, shape):
+    import mercury_artifact_b200 as mb
+    from oracle import merge
+
+    B, S, H, D = shape
+    g = torch.Generator().manual_seed(5)
+    parts = [((torch.randn(B, S, H, D, generator=g)).to(dtype), torch.randn(B, H, S, generator=g) * 4) for _ in range(4)]
+    out = lse = None
+    ro = rl = None
+    for po, pl in parts:
+        out, lse = mb.update_out_and_lse(out, lse, po.cuda(), pl.cuda())
+        ro, rl = merge.update_out_and_lse(ro, rl, po, pl)
+    assert out.dtype == torch.float32 and out.shape == (B, S, H, D) and lse.shape == (B, S, H, 1)
+    assert (out.cpu() - ro).abs().max().item() <= 1e-5
+    assert (lse.cpu() - rl).abs().max().item() <= 1e-5
+
+
+def test_merge_slice_and_errors():
+    import mercury_artifact_b200 as mb
+    from oracle import merge
+
+    B, S, H, D = 1, 256, 2, 128
+    g = torch.Generator().manual_seed(6)
+    o0, l0 = torch.randn(B, S, H, D, generator=g), torch.randn(B, H, S, generator=g)
+    o1, l1 = torch.randn(B, 128, H, D, generator=g), torch.randn(B, H, 128, generator=g)
+    with pytest.raises(RuntimeError):
+        mb.update_out_and_lse(None, None, o0.cuda(), l0.cuda(), slice_=(slice(None), slice(0, 128)))
+    sl = (slice(None), slice(128, 256))
+    out, lse = mb.update_out_and_lse(None, None, o0.cuda(), l0.cuda())
+    out, lse = mb.update_out_and_lse(out, lse, o1.cuda(), l1.cuda(), slice_=sl)
+    ro, rl = merge.update_out_and_lse(None, None, o0, l0)
+    ro, rl = merge.update_out_and_lse(ro, rl, o1, l1, slice_=sl)
+    assert (out.cpu() - ro).abs().max().item() <= 1e-5 and (lse.cpu() - rl).abs().max().item() <= 1e-5
+
+
+def test_merge_handles_rows_without_keys():
+    """-inf block LSE leaves a row untouched; -inf running LSE adopts the block (causal partials)."""
+    import mercury_artifact_b200 as mb
+
+    B, S, H, D = 1, 64, 1, 128
+    o0, o1 = torch.ones(B, S, H, D), torch.full((B, S, H, D), 3.0)
+    l0, l1 = torch.zeros(B, H, S), torch.zeros(B, H, S)
+    l1[..., :16] = float("-inf")
+    l0[..., 48:] = float("-inf")
+    out, lse = mb.update_out_and_lse(None, None, o0.cuda(), l0.cuda())
+    out, lse = mb.update_out_and_lse(out, lse, o1.cuda(), l1.cuda())
+    out, lse = out.cpu(), lse.cpu().squeeze(-1)
+    assert not torch.isnan(out).any() and not torch.isnan(lse).any()
+    assert (out[:, :16] == 1).all() and (out[:, 48:] == 3).all()
+    assert torch.allclose(out[:, 16:48], torch.full((B, 32, H, D), 2.0))
+    assert torch.allclose(lse[:, 16:48], torch.full((B, 32, H), 0.6931472))

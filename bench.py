@@ -1,0 +1,332 @@
+#!/usr/bin/env python
+"""Headline benchmark: causal ring-attention forward, BASELINE config 2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload "cfg2" (default): bf16, batch 1, seqlen 32768, 32 heads, head_dim 128, causal,
+softmax scale 1/sqrt(128), Q/K/V ~ N(0,1)*0.5 seeded, sequence sharded into N equal contiguous
+chunks.  A step is one forward of the whole job (every rank's shard).  `value` is causal-adjusted
+attention TFLOP/s summed over all GPUs with inputs resident in HBM; `e2e` is the same metric
+through the public API with pinned HOST buffers (host->device copies of q and kv and the
+device->host read of o and lse inside the timed region).
+
+N > 1 is launched by torch.distributed.run, one rank per GPU (NCCL for bootstrap); timing is CUDA
+events on the launching stream, max over ranks.  `--impl reference` times the CPU restatement of
+the reference's generated ring program (oracle/) on the host cores of rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (batch, seqlen, hq, hkv, head_dim, causal)
+    "cfg2": (1, 32768, 32, 32, 128, True),
+    "cfg2_nc": (1, 32768, 32, 32, 128, False),
+    "target_131k": (1, 131072, 32, 32, 128, True),
+    "cfg3_gqa": (2, 131072, 32, 8, 128, True),
+    "cfg4_dring": (1, 262144, 16, 16, 128, False),
+    # smaller case of the same kernel for ncu captures: inputs (384 MiB) still exceed L2
+    "profile_16k": (1, 16384, 32, 32, 128, True),
+}
+METRIC = "ring-attn causal-adj TFLOP/s (fwd), whole job"
+FALLBACK_PEAK_TFLOPS = 1590.0
+
+
+def flops_fwd(B, S, H, D, causal):
+    return 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", 0) or 0), "measured"
+        except Exception:
+            pass
+    return FALLBACK_PEAK_TFLOPS, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 - 0.05 <= t <= t1 + 0.25] or [r for _, r in self.rows]
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- CPU legs
+def cpu_leg(workload, world, budget_s=12.0):
+    """Time the oracle's restatement of the generated ring program on the host cores.
+
+    Bounded sample: same B/H/D/causal and the same number of shards, sequence shortened so the
+    run takes on the order of `budget_s` seconds.  Returns (TFLOP/s, cores, description, seconds)."""
+    import torch
+
+    from oracle import block, ring
+
+    B, S, H, hkv, D, causal = WORKLOADS[workload]
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    torch.set_flush_denormal(True)  # exp() of far-below-max scores is denormal and very slow otherwise
+    scale = D ** -0.5
+
+    def run(s):
+        g = torch.Generator().manual_seed(1234)
+        q = torch.randn(B, s, H, D, generator=g) * 0.5
+        k = torch.randn(B, s, hkv, D, generator=g) * 0.5
+        v = torch.randn(B, s, hkv, D, generator=g) * 0.5
+        qs = [x.contiguous() for x in q.chunk(world, 1)]
+        kvs = [torch.stack([k.chunk(world, 1)[r], v.chunk(world, 1)[r]]) for r in range(world)]
+        t0 = time.perf_counter()
+        if world == 1:
+            block.block_attn_fwd(q, k, v, scale, causal=causal)
+        else:
+            ring.simulate_ring_fwd(qs, kvs, scale, (world,), positional_causal=causal)
+        return time.perf_counter() - t0
+
+    s = 1024 * max(1, world // 2)
+    run(s)  # warm the thread pool and allocator
+    t = run(s)
+    while t < budget_s / 4 and s * 2 <= S:
+        s *= 2
+        t = run(s)
+    tf = flops_fwd(B, s, H, D, causal) / t / 1e12
+    desc = (f"oracle ring forward, {world} shard(s), B{B} H{H}/{hkv} D{D} {'causal' if causal else 'non-causal'} "
+            f"fp32 at seqlen {s} (1/{(S // s) ** 2} of the full workload's FLOPs), {cores} threads, {t:.2f} s")
+    return tf, cores, desc, t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    B, S, H, hkv, D, causal = WORKLOADS[args.workload]
+    vals, times = [], []
+    cores, desc = 0, ""
+    for i in range(args.warmup + args.steps):
+        tf, cores, desc, t = cpu_leg(args.workload, args.gpus, budget_s=6.0)
+        if i >= args.warmup:
+            vals.append(tf)
+            times.append(t)
+        if i >= args.warmup and sum(times) > 150:
+            break
+    v = statistics.mean(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": len(vals), "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(times),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.workload, args.gpus), "sample": desc},
+        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def workload_name(w, n):
+    B, S, H, hkv, D, causal = WORKLOADS[w]
+    return (f"{w}: ring-attention forward bf16 B{B} S{S} Hq{H} Hkv{hkv} D{D} "
+            f"{'causal' if causal else 'non-causal'}, {n} contiguous shard(s)")
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(json.dumps({"error": f"--gpus {args.gpus} needs torch.distributed.run with {args.gpus} ranks"}))
+            return 2
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200 import _lib
+    from mercury_artifact_b200.ring import RingAttention
+
+    B, S, H, hkv, D, causal = WORKLOADS[args.workload]
+    L = S // world
+    scale = D ** -0.5
+
+    # seeded synthetic inputs: every rank builds only its own shard, from a per-rank seed
+    g = torch.Generator().manual_seed(1234 + rank)
+    q_host = (torch.randn(B, L, H, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    kv_host = (torch.randn(2, B, L, hkv, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    o_host = torch.empty(B, L, H, D, dtype=torch.bfloat16).pin_memory()
+    lse_host = torch.empty(B, H, L, dtype=torch.float32).pin_memory()
+    q = q_host.to(dev)
+    kv = kv_host.to(dev)
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, L, dtype=torch.float32, device=dev)
+
+    if world > 1:
+        mb.comm.init_p2p()
+    op = RingAttention((world,), B, L, H, hkv, D, causal=causal)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        t1 = time.time()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, t0, t1
+
+    def step_resident():
+        op.forward(q, kv, o, lse, scale)
+
+    def step_e2e():
+        q.copy_(q_host, non_blocking=True)
+        kv.copy_(kv_host, non_blocking=True)
+        op.forward(q, kv, o, lse, scale)
+        o_host.copy_(o, non_blocking=True)
+        lse_host.copy_(lse, non_blocking=True)
+        stream.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms, t0, t1 = timed(step_resident, args.steps, max(args.warmup, 3))
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    status = _lib.status_fetch(stream.cuda_stream)
+    ms_e2e, _, _ = timed(step_e2e, max(3, args.steps // 2), 3)
+    status |= _lib.status_fetch(stream.cuda_stream)
+
+    # kernel-only duration for the roofline: the attention launch of the slowest rank, timed alone
+    # (at N=1 this is the step itself)
+    fl_total = flops_fwd(B, S, H, D, causal)
+    if causal:
+        # causal-adjusted FLOPs this rank's launch performs (its rows see shards 0..rank)
+        fl_rank = 4.0 * B * H * D * (L * L * rank + L * L * 0.5)
+    else:
+        fl_rank = fl_total / world
+    value = fl_total / (ms * 1e-3) / 1e12
+    e2e = fl_total / (ms_e2e * 1e-3) / 1e12
+    peak, sustained, peak_kind = measured_peaks()
+    kernel_tf = fl_rank / (ms * 1e-3) / 1e12  # slowest rank bounds the step; its launch spans the step
+    if world > 1:
+        t = torch.tensor([kernel_tf], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        kernel_tf = float(t.item())
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": workload_name(args.workload, world),
+                "l2": "inputs larger than L2: q+k+v %.0f MiB per rank" % (3 * B * L * H * D * 2 / 2 ** 20),
+                "per_gpu_tflops": value / world,
+                "frac_of_bf16_peak_per_gpu": value / world / peak,
+            },
+            "e2e": {"value": e2e, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": (q_host.numel() + kv_host.numel()) * 2 * world,
+                    "d2h_bytes_per_step": (o_host.numel() * 2 + lse_host.numel() * 4) * world},
+            "gpu_launches": args.steps * op.launches_per_forward * world,
+            "roofline": {"bound": "tensor", "achieved": kernel_tf, "peak": peak, "unit": "TFLOP/s",
+                         "frac": kernel_tf / peak, "traffic": None,
+                         "kernel": "attn_fwd_kernel (busiest rank)", "peak_kind": f"bf16_tflops burst, {peak_kind}",
+                         "frac_of_sustained": (kernel_tf / sustained) if sustained else None},
+            "clocks": clocks, "device_status": status,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            tf, cores, desc, _ = cpu_leg(args.workload, 1, budget_s=12.0)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -43,6 +43,12 @@ typedef struct mb_kv_segment {
   int64_t stride_b, stride_s, stride_h; /* shared by k and v */
   int32_t sk;                           /* keys in this shard */
   int32_t k_off;                        /* global position of key 0 (causal rule only) */
+  /* Optional arrival flag (device word on this GPU): the kernel does not touch the shard
+   * before *ready_flag >= ready_value.  NULL: the shard is already in place.  Lets one launch
+   * overlap compute on early shards with the transfer of later ones (see mb_flag_signal). */
+  const int32_t* ready_flag;
+  int32_t ready_value;
+  int32_t reserved;
 } mb_kv_segment;
 
 typedef struct mb_attn_fwd_args {

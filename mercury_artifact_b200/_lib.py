@@ -41,6 +41,9 @@ class KVSegment(C.Structure):
         ("stride_h", C.c_int64),
         ("sk", C.c_int32),
         ("k_off", C.c_int32),
+        ("ready_flag", C.c_void_p),
+        ("ready_value", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 

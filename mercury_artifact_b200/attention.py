@@ -29,7 +29,7 @@ def _check_bshd(t: torch.Tensor, name: str) -> None:
 
 def attn_fwd_segments(
     q: torch.Tensor,
-    segments: Sequence[Tuple[torch.Tensor, torch.Tensor, int]],
+    segments: Sequence[tuple],
     softmax_scale: float,
     causal: bool = False,
     q_off: int = 0,
@@ -38,10 +38,12 @@ def attn_fwd_segments(
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """softmax(scale * q k^T) v over the concatenation of `segments`.
 
-    segments: (k, v, k_off) with k, v of shape [batch, sk, hkv, head_dim]; k_off is the
-    global position of the shard's first key and matters only when `causal`
-    (key visible iff k_off + j <= q_off + i).  Returns (o bf16 [b, sq, hq, d],
-    lse fp32 [b, hq, sq]).
+    segments: (k, v, k_off) or (k, v, k_off, flag_ptr, flag_value) with k, v of shape
+    [batch, sk, hkv, head_dim]; k_off is the global position of the shard's first key and
+    matters only when `causal` (key visible iff k_off + j <= q_off + i); flag_ptr, when
+    given, is the address of a device int32 that reaches flag_value once the shard has
+    arrived (the kernel waits for it before reading the shard).  Returns
+    (o bf16 [b, sq, hq, d], lse fp32 [b, hq, sq]).
     """
     _check_bshd(q, "q")
     b, sq, hq, d = q.shape
@@ -69,7 +71,9 @@ def attn_fwd_segments(
     args.nseg = len(segments)
     args.status = None
     hkv = None
-    for i, (k, v, k_off) in enumerate(segments):
+    for i, segment in enumerate(segments):
+        k, v, k_off = segment[:3]
+        flag_ptr, flag_value = (segment[3], segment[4]) if len(segment) >= 5 and segment[3] else (None, 0)
         _check_bshd(k, "k")
         _check_bshd(v, "v")
         if k.shape != v.shape or k.stride() != v.stride():
@@ -85,6 +89,8 @@ def attn_fwd_segments(
         seg.stride_b, seg.stride_s, seg.stride_h = k.stride(0), k.stride(1), k.stride(2)
         seg.sk = k.shape[1]
         seg.k_off = int(k_off)
+        seg.ready_flag = flag_ptr
+        seg.ready_value = int(flag_value)
     args.hkv = hkv if hkv is not None else hq
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib.mb_attn_fwd(C.byref(args), C.c_void_p(_stream_ptr())), "mb_attn_fwd")

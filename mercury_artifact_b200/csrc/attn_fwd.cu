@@ -47,6 +47,8 @@ struct FwdArgs {
   int nseg;
   int seg_sk[MB_MAX_SEGMENTS];
   int seg_koff[MB_MAX_SEGMENTS];
+  const int* seg_flag[MB_MAX_SEGMENTS];  // arrival flag of a staged shard (nullptr: already in place)
+  int seg_flag_value[MB_MAX_SEGMENTS];
   int q_off;
   int causal;
   float scale;       // softmax scale
@@ -177,6 +179,12 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
       bool ok = true;
       for (int s = 0; s < a.nseg && ok; ++s) {
         const int nmax = max(ctl->n_tiles[0][s], ctl->n_tiles[1][s]);
+        if (nmax > 0 && a.seg_flag[s] != nullptr) {
+          // The shard is being staged by another stream: wait (bounded) for its arrival flag,
+          // then order the TMA reads (async proxy) after the flag read.
+          ok = flag_wait_ge(a.seg_flag[s], a.seg_flag_value[s], abort_word, MB_ERR_TIMEOUT_FLAG);
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int jt = 0; jt < nmax && ok; ++jt) {
           for (int which = 0; which < 2; ++which) {
             const int stage = n % kFwdStages;
@@ -504,6 +512,8 @@ int launch_attn_fwd(const mb_attn_fwd_args* x, cudaStream_t stream) {
       return MB_E_TENSORMAP;
     a.seg_sk[nseg] = g.sk;
     a.seg_koff[nseg] = g.k_off;
+    a.seg_flag[nseg] = g.ready_flag;
+    a.seg_flag_value[nseg] = g.ready_value;
     ++nseg;
   }
   a.nseg = nseg;

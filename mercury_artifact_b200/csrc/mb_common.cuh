@@ -100,6 +100,25 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
   return __all_sync(0xffffffffu, ok);
 }
 
+// Bounded wait until a device-memory flag word reaches `value` (acquire, GPU scope).
+__device__ __forceinline__ bool flag_wait_ge(const int* flag, int value, volatile int* abort_word, int code) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  for (;;) {
+    int seen;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (seen >= value) return true;
+    if (((++spins) & 15u) == 0u) {
+      if (*abort_word != 0) return false;
+      if (clock64() - t0 > kWaitCycleLimit) {
+        *abort_word = code;
+        return false;
+      }
+    }
+    __nanosleep(100);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // TMA (tiled bulk tensor loads, no multicast)
 // ---------------------------------------------------------------------------

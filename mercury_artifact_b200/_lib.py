@@ -29,6 +29,7 @@ STATUS_NAMES = {
     106: "output accumulation never completed",
     107: "staged shard chunk never became ready",
     108: "unspecified wait",
+    109: "a K/V shard's arrival flag never reached its value (in-kernel wait)",
 }
 
 

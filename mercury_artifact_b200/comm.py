@@ -115,7 +115,11 @@ class PeerContext:
             self.rank, self.world = 0, 1
         self.group = group
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.comm_stream = torch.cuda.Stream(device=self.device)
+        # Highest priority: the work distributor only starts blocks of a later grid once every block
+        # of an earlier same-priority grid has been dispatched, so at default priority the one-thread
+        # flag kernels would sit behind the pending CTAs of a running attention kernel that is itself
+        # waiting for them.
+        self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1)
         self._channels: Dict[Tuple[int, int], "_Channel"] = {}
 
     # -- primitive, stream-ordered operations ----------------------------------------------

@@ -105,7 +105,9 @@ __device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint3
   }
 }
 
-__global__ void __launch_bounds__(kFwdThreads, 1)
+// 160 registers/thread at launch (not the 168 that 384 threads would allow): the few warps' worth
+// left free on the SM let the transfer stream's one-thread flag kernels start beside a resident CTA.
+__global__ void __maxnreg__(160)
 attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -182,7 +184,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
         if (nmax > 0 && a.seg_flag[s] != nullptr) {
           // The shard is being staged by another stream: wait (bounded) for its arrival flag,
           // then order the TMA reads (async proxy) after the flag read.
-          ok = flag_wait_ge(a.seg_flag[s], a.seg_flag_value[s], abort_word, MB_ERR_TIMEOUT_FLAG);
+          ok = flag_wait_ge(a.seg_flag[s], a.seg_flag_value[s], abort_word, MB_ERR_TIMEOUT_SEGMENT);
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int jt = 0; jt < nmax && ok; ++jt) {
@@ -301,7 +303,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     }
   } else {
     // ------------------------------------------------------ softmax + epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // All control flow below is warp-uniform (the tensor-memory loads and
     // stores are warp-collective); only global stores are predicated per row.
     const int i = warp >> 2;                    // query tile

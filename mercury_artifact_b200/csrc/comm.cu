@@ -39,6 +39,20 @@ __global__ void flag_wait_kernel(const int* flag, int value, unsigned long long 
   }
 }
 
+// The flag kernels must be able to start while an attention kernel fills every SM.  An SM
+// only co-hosts kernels that agree on its shared-memory carve-out, and the attention
+// kernels run with the largest one, so the flag kernels ask for the same.
+static void prefer_max_smem_carveout_once() {
+  static bool done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
+  cudaFuncSetAttribute(flag_signal_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(flag_wait_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);
+  done[dev] = true;
+}
+
 }  // namespace mb
 
 extern "C" {
@@ -94,6 +108,7 @@ int mb_copy_async(void* dst, const void* src, uint64_t bytes, void* cuda_stream)
 
 int mb_flag_signal(int32_t* flag, int32_t value, void* cuda_stream) {
   if (flag == nullptr) return MB_E_INVALID;
+  mb::prefer_max_smem_carveout_once();
   mb::flag_signal_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(flag, value);
   return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
 }
@@ -101,6 +116,7 @@ int mb_flag_signal(int32_t* flag, int32_t value, void* cuda_stream) {
 int mb_flag_wait(const int32_t* flag, int32_t value, uint64_t timeout_ns, int32_t* status, void* cuda_stream) {
   if (flag == nullptr) return MB_E_INVALID;
   int* st = status ? status : mb::default_status_word();
+  mb::prefer_max_smem_carveout_once();
   mb::flag_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(flag, value, timeout_ns, st);
   return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
 }

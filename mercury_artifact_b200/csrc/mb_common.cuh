@@ -28,6 +28,7 @@ enum : int {
   MB_ERR_TIMEOUT_O = 106,        // output accumulation never completed
   MB_ERR_TIMEOUT_FLAG = 107,     // staged shard chunk never became ready
   MB_ERR_TIMEOUT_MISC = 108,
+  MB_ERR_TIMEOUT_SEGMENT = 109,  // a K/V shard's arrival flag never reached its value (in-kernel wait)
 };
 
 // About one second at 1.9 GHz.

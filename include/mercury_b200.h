@@ -76,6 +76,76 @@ typedef struct mb_attn_fwd_args {
  * A row that sees no key gets o = 0 and lse = -inf. */
 MB_API int mb_attn_fwd(const mb_attn_fwd_args* args, void* cuda_stream);
 
+/* ---- backward ------------------------------------------------------------------------- */
+
+typedef struct mb_bwd_preprocess_args {
+  const void* dout; /* [batch, sq, hq, head_dim] bf16 */
+  int64_t dout_stride_b, dout_stride_s, dout_stride_h;
+  const void* out; /* forward output, same shape */
+  int64_t out_stride_b, out_stride_s, out_stride_h;
+  const float* lse; /* [batch, hq, sq] fp32: the FINAL log-sum-exp of these query rows */
+  float* lse2;      /* [batch, hq, stat_pad] fp32, written: lse * log2(e), +inf for rows without keys and padding */
+  float* delta;     /* [batch, hq, stat_pad] fp32, written: rowsum(dout * out), 0 in the padding */
+  int32_t batch, sq, hq, head_dim;
+  int32_t stat_pad; /* sq rounded up to a multiple of 64 */
+} mb_bwd_preprocess_args;
+
+/* Per-row statistics the backward kernels need; run once per query shard (in a ring, once
+ * per rank: every block call of the generated loop receives the same out and softmax_lse,
+ * utils/attn_bwd_dsl.py:91-92). */
+MB_API int mb_attn_bwd_preprocess(const mb_bwd_preprocess_args* args, void* cuda_stream);
+
+#define MB_BWD_MODE_DKV 1 /* owner = one K/V shard, stream = query shards: writes dK (out1) and dV (out2) */
+#define MB_BWD_MODE_DQ 0  /* owner = one query shard, stream = K/V shards: writes dQ (out1) */
+#define MB_OUT_BF16 0
+#define MB_OUT_F32 1
+#define MB_OUT_F32_ACCUM 2 /* out += result (each element is owned by one CTA: no atomics) */
+
+/* One streamed shard.  Mode DKV: str = q, str_g = dout (hq heads) with that shard's lse2/delta;
+ * mode DQ: str = k, str_g = v (hkv heads), lse2/delta unused. */
+typedef struct mb_bwd_segment {
+  const void* str;
+  const void* str_g;
+  int64_t stride_b, stride_s, stride_h;
+  int32_t rows;
+  int32_t pos_off; /* global position of row 0 (causal rule) */
+  const float* lse2;
+  const float* delta;
+  int32_t stat_pad;
+  int32_t ready_value;
+  const int32_t* ready_flag; /* optional arrival flag, as in mb_kv_segment */
+} mb_bwd_segment;
+
+typedef struct mb_attn_bwd_args {
+  int32_t mode; /* MB_BWD_MODE_* */
+  int32_t out_mode; /* MB_OUT_* */
+  const void* own;   /* DKV: k; DQ: q      [batch, own_rows, heads, head_dim] */
+  const void* own_g; /* DKV: v; DQ: dout   same strides */
+  int64_t own_stride_b, own_stride_s, own_stride_h;
+  const float* own_lse2; /* DQ mode only: statistics of the owner's query rows */
+  const float* own_delta;
+  int32_t own_stat_pad;
+  int32_t own_rows;
+  int32_t own_off; /* global position of owner row 0 */
+  int32_t batch, hq, hkv, head_dim;
+  int32_t causal; /* key visible iff k_pos <= q_pos */
+  float softmax_scale;
+  void* out1; /* DKV: dk; DQ: dq   [batch, own_rows, heads, head_dim] */
+  void* out2; /* DKV: dv */
+  int64_t out_stride_b, out_stride_s, out_stride_h;
+  int32_t nseg;
+  int32_t reserved;
+  mb_bwd_segment seg[MB_MAX_SEGMENTS];
+  int32_t* status;
+} mb_attn_bwd_args;
+
+/* Gradients of one owner shard against nseg streamed shards.  One DQ call plus one DKV call
+ * with a single segment replace the block call
+ *   _flash_attn_backward(**params)           utils/attn_bwd_dsl.py:115
+ * and, with one segment per rank, the whole generated backward loop including its fp32
+ * accumulation and the rotating dK/dV buffer (mercury/backend/pytorch/codegen.py:99-190). */
+MB_API int mb_attn_bwd(const mb_attn_bwd_args* args, void* cuda_stream);
+
 #define MB_DTYPE_BF16 0
 #define MB_DTYPE_F32 1
 

@@ -1,5 +1,5 @@
 """B200-native ops for the attention code Mercury's CommIR PyTorch backend emits."""
 from . import _lib  # noqa: F401  (fails loudly when libmercury_b200.so is missing)
-from .attention import attn_fwd_segments  # noqa: F401
+from .attention import attn_bwd_dkv, attn_bwd_dq, attn_fwd_segments, bwd_preprocess  # noqa: F401
 from .integration import install_backend, load_generated, namespace  # noqa: F401
-from .ops import _flash_attn_forward, get_default_args, update_out_and_lse  # noqa: F401
+from .ops import _flash_attn_backward, _flash_attn_forward, get_default_args, update_out_and_lse  # noqa: F401

@@ -95,6 +95,83 @@ class MergeArgs(C.Structure):
     ]
 
 
+MB_BWD_MODE_DKV = 1
+MB_BWD_MODE_DQ = 0
+MB_OUT_BF16 = 0
+MB_OUT_F32 = 1
+MB_OUT_F32_ACCUM = 2
+
+
+class BwdPreprocessArgs(C.Structure):
+    _fields_ = [
+        ("dout", C.c_void_p),
+        ("dout_stride_b", C.c_int64),
+        ("dout_stride_s", C.c_int64),
+        ("dout_stride_h", C.c_int64),
+        ("out", C.c_void_p),
+        ("out_stride_b", C.c_int64),
+        ("out_stride_s", C.c_int64),
+        ("out_stride_h", C.c_int64),
+        ("lse", C.c_void_p),
+        ("lse2", C.c_void_p),
+        ("delta", C.c_void_p),
+        ("batch", C.c_int32),
+        ("sq", C.c_int32),
+        ("hq", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("stat_pad", C.c_int32),
+    ]
+
+
+class BwdSegment(C.Structure):
+    _fields_ = [
+        ("str", C.c_void_p),
+        ("str_g", C.c_void_p),
+        ("stride_b", C.c_int64),
+        ("stride_s", C.c_int64),
+        ("stride_h", C.c_int64),
+        ("rows", C.c_int32),
+        ("pos_off", C.c_int32),
+        ("lse2", C.c_void_p),
+        ("delta", C.c_void_p),
+        ("stat_pad", C.c_int32),
+        ("ready_value", C.c_int32),
+        ("ready_flag", C.c_void_p),
+    ]
+
+
+class AttnBwdArgs(C.Structure):
+    _fields_ = [
+        ("mode", C.c_int32),
+        ("out_mode", C.c_int32),
+        ("own", C.c_void_p),
+        ("own_g", C.c_void_p),
+        ("own_stride_b", C.c_int64),
+        ("own_stride_s", C.c_int64),
+        ("own_stride_h", C.c_int64),
+        ("own_lse2", C.c_void_p),
+        ("own_delta", C.c_void_p),
+        ("own_stat_pad", C.c_int32),
+        ("own_rows", C.c_int32),
+        ("own_off", C.c_int32),
+        ("batch", C.c_int32),
+        ("hq", C.c_int32),
+        ("hkv", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("causal", C.c_int32),
+        ("softmax_scale", C.c_float),
+        ("out1", C.c_void_p),
+        ("out2", C.c_void_p),
+        ("out_stride_b", C.c_int64),
+        ("out_stride_s", C.c_int64),
+        ("out_stride_h", C.c_int64),
+        ("nseg", C.c_int32),
+        ("reserved", C.c_int32),
+        ("seg", BwdSegment * MB_MAX_SEGMENTS),
+        ("status", C.c_void_p),
+    ]
+
+
 LIB_PATH = Path(__file__).resolve().parent / "libmercury_b200.so"
 
 
@@ -113,6 +190,10 @@ def _load() -> C.CDLL:
     lib.mb_version.argtypes = []
     lib.mb_attn_fwd.restype = C.c_int
     lib.mb_attn_fwd.argtypes = [C.POINTER(AttnFwdArgs), C.c_void_p]
+    lib.mb_attn_bwd_preprocess.restype = C.c_int
+    lib.mb_attn_bwd_preprocess.argtypes = [C.POINTER(BwdPreprocessArgs), C.c_void_p]
+    lib.mb_attn_bwd.restype = C.c_int
+    lib.mb_attn_bwd.argtypes = [C.POINTER(AttnBwdArgs), C.c_void_p]
     lib.mb_merge_out_lse.restype = C.c_int
     lib.mb_merge_out_lse.argtypes = [C.POINTER(MergeArgs), C.c_void_p]
     for name, argtypes in {

@@ -95,3 +95,135 @@ def attn_fwd_segments(
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib.mb_attn_fwd(C.byref(args), C.c_void_p(_stream_ptr())), "mb_attn_fwd")
     return out, lse
+
+
+# ------------------------------------------------------------------------------------------
+# backward
+# ------------------------------------------------------------------------------------------
+class RowStats:
+    """lse2 = lse*log2(e) and delta = rowsum(dout*out) of one query shard, padded to 64 rows."""
+
+    def __init__(self, lse2: torch.Tensor, delta: torch.Tensor, rows: int):
+        self.lse2, self.delta, self.rows = lse2, delta, rows
+        self.pad = lse2.shape[-1]
+
+
+def _pad64(n: int) -> int:
+    return max(64, (n + 63) // 64 * 64)
+
+
+def bwd_preprocess(dout: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
+                   workspace: Optional[torch.Tensor] = None) -> RowStats:
+    """Per-row statistics for the backward kernels.  `out` and `lse` are the FINAL forward results
+    of these query rows.  workspace: optional fp32 [2, batch, hq, pad64(sq)] to write into."""
+    _check_bshd(dout, "dout")
+    _check_bshd(out, "out")
+    b, sq, hq, d = dout.shape
+    pad = _pad64(sq)
+    if workspace is None:
+        workspace = torch.empty((2, b, hq, pad), dtype=torch.float32, device=dout.device)
+    elif tuple(workspace.shape) != (2, b, hq, pad) or workspace.dtype != torch.float32 or not workspace.is_contiguous():
+        raise ValueError(f"workspace must be contiguous fp32 {(2, b, hq, pad)}")
+    lse = lse.contiguous()
+    if tuple(lse.shape) != (b, hq, sq) or lse.dtype != torch.float32:
+        raise ValueError("lse must be fp32 [batch, hq, sq]")
+    a = _lib.BwdPreprocessArgs()
+    a.dout = dout.data_ptr()
+    a.dout_stride_b, a.dout_stride_s, a.dout_stride_h = dout.stride(0), dout.stride(1), dout.stride(2)
+    a.out = out.data_ptr()
+    a.out_stride_b, a.out_stride_s, a.out_stride_h = out.stride(0), out.stride(1), out.stride(2)
+    a.lse, a.lse2, a.delta = lse.data_ptr(), workspace[0].data_ptr(), workspace[1].data_ptr()
+    a.batch, a.sq, a.hq, a.head_dim, a.stat_pad = b, sq, hq, d, pad
+    with torch.cuda.device(dout.device):
+        _lib.check(_lib.lib.mb_attn_bwd_preprocess(C.byref(a), C.c_void_p(_stream_ptr())), "mb_attn_bwd_preprocess")
+    return RowStats(workspace[0], workspace[1], sq)
+
+
+_OUT_MODES = {torch.bfloat16: _lib.MB_OUT_BF16, torch.float32: _lib.MB_OUT_F32}
+
+
+def _bwd_launch(mode, own, own_g, own_off, segments, hq, hkv, scale, causal, out1, out2, accumulate, own_stats=None):
+    _check_bshd(own, "owner")
+    _check_bshd(own_g, "owner_g")
+    if own.shape != own_g.shape or own.stride() != own_g.stride():
+        raise ValueError("the two owner tensors must share shape and strides")
+    if len(segments) > _lib.MB_MAX_SEGMENTS:
+        raise ValueError(f"at most {_lib.MB_MAX_SEGMENTS} segments per call")
+    b, rows, _, d = own.shape
+    a = _lib.AttnBwdArgs()
+    a.mode = mode
+    if out1.dtype not in _OUT_MODES:
+        raise TypeError("gradient outputs must be bf16 or fp32")
+    if accumulate and out1.dtype != torch.float32:
+        raise TypeError("accumulation needs fp32 gradient buffers")
+    a.out_mode = _lib.MB_OUT_F32_ACCUM if accumulate else _OUT_MODES[out1.dtype]
+    a.own, a.own_g = own.data_ptr(), own_g.data_ptr()
+    a.own_stride_b, a.own_stride_s, a.own_stride_h = own.stride(0), own.stride(1), own.stride(2)
+    if own_stats is not None:
+        a.own_lse2, a.own_delta, a.own_stat_pad = own_stats.lse2.data_ptr(), own_stats.delta.data_ptr(), own_stats.pad
+    a.own_rows, a.own_off = rows, int(own_off)
+    a.batch, a.hq, a.hkv, a.head_dim = b, hq, hkv, d
+    a.causal = 1 if causal else 0
+    a.softmax_scale = float(scale)
+    a.out1 = out1.data_ptr()
+    if out2 is not None:
+        if out2.shape != out1.shape or out2.stride() != out1.stride() or out2.dtype != out1.dtype:
+            raise ValueError("dk and dv must share shape, strides and dtype")
+        a.out2 = out2.data_ptr()
+    if out1.stride(3) != 1 or tuple(out1.shape) != tuple(own.shape):
+        raise ValueError("gradient output must match the owner's shape with a contiguous head_dim")
+    a.out_stride_b, a.out_stride_s, a.out_stride_h = out1.stride(0), out1.stride(1), out1.stride(2)
+    a.nseg = len(segments)
+    for i, sg in enumerate(segments):
+        s, s_g, off = sg["str"], sg["str_g"], sg["off"]
+        _check_bshd(s, "stream")
+        _check_bshd(s_g, "stream_g")
+        if s.shape != s_g.shape or s.stride() != s_g.stride():
+            raise ValueError("the two stream tensors of a segment must share shape and strides")
+        seg = a.seg[i]
+        seg.str, seg.str_g = s.data_ptr(), s_g.data_ptr()
+        seg.stride_b, seg.stride_s, seg.stride_h = s.stride(0), s.stride(1), s.stride(2)
+        seg.rows, seg.pos_off = s.shape[1], int(off)
+        st = sg.get("stats")
+        if st is not None:
+            seg.lse2, seg.delta, seg.stat_pad = st.lse2.data_ptr(), st.delta.data_ptr(), st.pad
+        if sg.get("flag"):
+            seg.ready_flag, seg.ready_value = sg["flag"], int(sg["flag_value"])
+    with torch.cuda.device(own.device):
+        _lib.check(_lib.lib.mb_attn_bwd(C.byref(a), C.c_void_p(_stream_ptr())), "mb_attn_bwd")
+
+
+def attn_bwd_dq(q, dout, stats: RowStats, kv_segments, softmax_scale, causal=False, q_off=0, dq=None,
+                accumulate=False, hkv=None):
+    """dQ of one query shard against K/V segments [(k, v, k_off) or dicts]; dq bf16/fp32 like q."""
+    if dq is None:
+        dq = torch.empty_like(q)
+    segs = []
+    for sg in kv_segments:
+        if isinstance(sg, dict):
+            segs.append(sg)
+        else:
+            segs.append({"str": sg[0], "str_g": sg[1], "off": sg[2],
+                         "flag": sg[3] if len(sg) > 3 else None, "flag_value": sg[4] if len(sg) > 4 else 0})
+    hkv = hkv if hkv is not None else (segs[0]["str"].shape[2] if segs else q.shape[2])
+    _bwd_launch(_lib.MB_BWD_MODE_DQ, q, dout, q_off, segs, q.shape[2], hkv, softmax_scale, causal, dq, None,
+                accumulate, own_stats=stats)
+    return dq
+
+
+def attn_bwd_dkv(k, v, q_segments, softmax_scale, causal=False, k_off=0, dk=None, dv=None, accumulate=False, hq=None):
+    """dK, dV of one K/V shard against query segments [(q, dout, stats, q_off[, flag, value])]."""
+    if dk is None:
+        dk = torch.empty_like(k)
+    if dv is None:
+        dv = torch.empty_like(v)
+    segs = []
+    for sg in q_segments:
+        if isinstance(sg, dict):
+            segs.append(sg)
+        else:
+            segs.append({"str": sg[0], "str_g": sg[1], "stats": sg[2], "off": sg[3],
+                         "flag": sg[4] if len(sg) > 4 else None, "flag_value": sg[5] if len(sg) > 5 else 0})
+    hq = hq if hq is not None else (segs[0]["str"].shape[2] if segs else k.shape[2])
+    _bwd_launch(_lib.MB_BWD_MODE_DKV, k, v, k_off, segs, hq, k.shape[2], softmax_scale, causal, dk, dv, accumulate)
+    return dk, dv

@@ -1,0 +1,608 @@
+// Backward attention for sm_100a: dQ, dK, dV of one query shard against a list
+// of K/V shards (dQ) and of one K/V shard against a list of query shards (dK/dV).
+//
+// One kernel template runs in two modes.  An "owner" tile of 128 rows keeps its
+// accumulators in tensor memory while "stream" tiles of 64 rows pass by:
+//
+//   mode dKV: owner = K_j, V_j (128 keys); stream = Q, dO (64 query rows per step)
+//       X = K Q^T = S^T     Y = V dO^T = dP^T          (rows: keys, columns: queries)
+//       P^T = exp2(X*c - lse2[q]),  dS^T = P^T * (Y - delta[q])
+//       dV += P^T dO        dK += dS^T Q
+//   mode dQ:  owner = Q_i, dO_i (128 query rows); stream = K, V (64 keys per step)
+//       X = Q K^T = S       Y = dO V^T = dP
+//       P = exp2(X*c - lse2[q]),    dS = P * (Y - delta[q])
+//       dQ += dS K
+//
+// lse2 = lse * log2(e) (with -inf mapped to +inf so that rows without keys give
+// P = 0) and delta = rowsum(dO * O) come from a small preprocess kernel.  X and Y
+// are double-buffered in tensor memory (2 x 2 x 64 columns); the bf16 P and dS
+// overwrite them in place and feed the accumulating MMAs as the tensor-memory A
+// operand; the stream tile in shared memory is read once K-major (for X, Y) and
+// once MN-major (for the accumulation).  Scores are recomputed in both modes
+// (7 tile MMAs per 128x128 block instead of 5), which buys an atomic-free,
+// deterministic kernel with no fp32 dQ scratch.
+//
+// The stream is a list of segments (shards), each with an optional arrival flag,
+// exactly like the forward kernel: the backward of a whole ring for one rank is
+// two launches (dQ over all K/V shards, dK/dV over all query shards) and the
+// reference's rotating fp32 dK/dV accumulator (codegen.py:116-190) is not needed:
+// every gradient tile is owned by exactly one CTA.
+//
+// Replaces _flash_attn_backward(**params), utils/attn_bwd_dsl.py:115 of the reference.
+#include "mb_common.cuh"
+#include "mb_host.h"
+
+namespace mb {
+
+constexpr int kOwnRows = 128;
+constexpr int kStrRows = 64;
+constexpr int kBD = 128;                              // head dim
+constexpr int kOwnTileBytes = kOwnRows * kBD * 2;     // 32 KiB, two 64-column halves of 16 KiB
+constexpr int kOwnHalfBytes = kOwnTileBytes / 2;
+constexpr int kStrTileBytes = kStrRows * kBD * 2;     // 16 KiB, two halves of 8 KiB
+constexpr int kStrHalfBytes = kStrTileBytes / 2;
+constexpr int kStatBytes = 2 * kStrRows * 4;          // lse2[64] + delta[64]
+constexpr int kBwdStageBytes = 2 * kStrTileBytes + 1024;  // Str + StrG + stats (padded)
+constexpr int kBwdStages = 4;
+constexpr int kBwdThreads = 320;                      // 8 element-wise warps + MMA warp + loader warp
+
+struct BwdMaps {
+  CUtensorMap own, own_g;                 // box 128 rows
+  CUtensorMap str[MB_MAX_SEGMENTS];       // box 64 rows
+  CUtensorMap str_g[MB_MAX_SEGMENTS];
+};
+
+struct BwdArgs {
+  int mode_dkv;  // 1: owner = K/V, stream = Q/dO; 0: owner = Q/dO, stream = K/V
+  int B, own_rows, Hq, Hkv, group;
+  int own_off;  // global position of owner row 0
+  int causal;
+  float scale, scale_log2;
+  int nseg;
+  int seg_rows[MB_MAX_SEGMENTS];
+  int seg_off[MB_MAX_SEGMENTS];                 // global position of the segment's row 0
+  const float* seg_lse2[MB_MAX_SEGMENTS];       // dKV mode: stats of the segment's queries [B,Hq,pad]
+  const float* seg_delta[MB_MAX_SEGMENTS];
+  int seg_stat_pad[MB_MAX_SEGMENTS];            // padded row count of those arrays
+  const int* seg_flag[MB_MAX_SEGMENTS];
+  int seg_flag_value[MB_MAX_SEGMENTS];
+  const float* own_lse2;                        // dQ mode: stats of the owner's queries [B,Hq,own_pad]
+  const float* own_delta;
+  int own_stat_pad;
+  // outputs: acc1 -> (dK | dQ), acc2 -> dV.  [B, rows, heads, D], strides in elements.
+  void* out1;
+  void* out2;
+  long long o_sb, o_ss, o_sh;
+  int out_mode;  // 0 bf16 store, 1 fp32 store, 2 fp32 accumulate
+  int* status;
+};
+
+struct BwdSmem {
+  uint64_t own_full;
+  uint64_t str_full[kBwdStages];
+  uint64_t str_empty[kBwdStages];
+  uint64_t xy_full[2];
+  uint64_t pd_full[2];
+  uint64_t acc_full;
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_word;
+  int seg_first[MB_MAX_SEGMENTS];  // first and one-past-last 64-row step of each segment for this owner tile
+  int seg_last[MB_MAX_SEGMENTS];
+};
+
+constexpr int kBwdSmemBytes = 2 * kOwnTileBytes + kBwdStages * kBwdStageBytes + 1024 + 1024;
+
+// Range of 64-row stream steps of a segment that can interact with the owner tile.
+__device__ __forceinline__ void step_range(const BwdArgs& a, int own0, int s, int* first, int* last) {
+  const int rows = a.seg_rows[s];
+  int f = 0, l = (rows + kStrRows - 1) / kStrRows;
+  if (own0 >= a.own_rows || rows <= 0) {
+    *first = 0;
+    *last = 0;
+    return;
+  }
+  if (a.causal) {
+    const int own_lo = a.own_off + own0;
+    const int own_hi = a.own_off + min(own0 + kOwnRows, a.own_rows) - 1;
+    if (a.mode_dkv) {
+      // stream = queries: a query row sees the owner's keys iff q_pos >= k_pos; need q_pos >= own_lo
+      long long need = (long long)own_lo - a.seg_off[s];  // first local query row that can see key own_lo
+      if (need > 0) f = (int)min((long long)l, need / kStrRows);
+    } else {
+      // stream = keys: visible iff k_pos <= q_pos; need k_pos <= own_hi
+      long long maxk = (long long)own_hi - a.seg_off[s];
+      if (maxk < 0) l = 0;
+      else l = (int)min((long long)l, maxk / kStrRows + 1);
+    }
+  }
+  if (f > l) f = l;
+  *first = f;
+  *last = l;
+}
+
+template <int kDummy>
+__global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps maps, const BwdArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sOwn = smem;
+  uint8_t* sOwnG = smem + kOwnTileBytes;
+  uint8_t* sStage = smem + 2 * kOwnTileBytes;
+  BwdSmem* ctl = reinterpret_cast<BwdSmem*>(sStage + kBwdStages * kBwdStageBytes);
+  volatile int* abort_word = &ctl->abort_word;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int own0 = blockIdx.x * kOwnRows;
+  const int h_own = blockIdx.y;  // dKV: kv head; dQ: query head
+  const int b = blockIdx.z;
+  const int n_sub = a.mode_dkv ? a.group : 1;  // query heads streamed per segment
+  const int h_str_base = a.mode_dkv ? h_own * a.group : h_own / a.group;
+
+  if (tid == 0) {
+    mbar_init(&ctl->own_full, 1);
+    for (int s = 0; s < kBwdStages; ++s) {
+      mbar_init(&ctl->str_full[s], 1);
+      mbar_init(&ctl->str_empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ctl->xy_full[i], 1);
+      mbar_init(&ctl->pd_full[i], 256);
+    }
+    mbar_init(&ctl->acc_full, 1);
+    mbar_init(&ctl->drain, 1);
+    ctl->abort_word = 0;
+    for (int s = 0; s < MB_MAX_SEGMENTS; ++s) {
+      int f = 0, l = 0;
+      if (s < a.nseg) step_range(a, own0, s, &f, &l);
+      ctl->seg_first[s] = f;
+      ctl->seg_last[s] = l;
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 8) {
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;  // Acc1 [0,128) Acc2 [128,256) X0 [256,320) Y0 [320,384) X1 [384,448) Y1 [448,512)
+
+  int total_steps = 0;
+  for (int s = 0; s < a.nseg; ++s) total_steps += (ctl->seg_last[s] - ctl->seg_first[s]) * n_sub;
+
+  if (warp == 9) {
+    // ------------------------------------------------------------------ loader
+    if (lane == 0 && total_steps > 0) {
+      mbar_expect_tx(&ctl->own_full, 2 * kOwnTileBytes);
+      tma_load_4d(sOwn, &maps.own, &ctl->own_full, 0, h_own, own0, b);
+      tma_load_4d(sOwn + kOwnHalfBytes, &maps.own, &ctl->own_full, 64, h_own, own0, b);
+      tma_load_4d(sOwnG, &maps.own_g, &ctl->own_full, 0, h_own, own0, b);
+      tma_load_4d(sOwnG + kOwnHalfBytes, &maps.own_g, &ctl->own_full, 64, h_own, own0, b);
+      int n = 0;
+      bool ok = true;
+      for (int s = 0; s < a.nseg && ok; ++s) {
+        const int f = ctl->seg_first[s], l = ctl->seg_last[s];
+        if (l > f && a.seg_flag[s] != nullptr) {
+          ok = flag_wait_ge(a.seg_flag[s], a.seg_flag_value[s], abort_word, MB_ERR_TIMEOUT_SEGMENT);
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int g = 0; g < n_sub && ok; ++g) {
+          const int h_str = h_str_base + g;
+          for (int t = f; t < l; ++t) {
+            const int stage = n % kBwdStages, round = n / kBwdStages;
+            if (round > 0 &&
+                !mbar_wait(&ctl->str_empty[stage], (round - 1) & 1, abort_word, MB_ERR_TIMEOUT_KV_EMPTY)) {
+              ok = false;
+              break;
+            }
+            uint8_t* dst = sStage + stage * kBwdStageBytes;
+            mbar_expect_tx(&ctl->str_full[stage], 2 * kStrTileBytes + (a.mode_dkv ? kStatBytes : 0));
+            const int r0 = t * kStrRows;
+            tma_load_4d(dst, &maps.str[s], &ctl->str_full[stage], 0, h_str, r0, b);
+            tma_load_4d(dst + kStrHalfBytes, &maps.str[s], &ctl->str_full[stage], 64, h_str, r0, b);
+            tma_load_4d(dst + kStrTileBytes, &maps.str_g[s], &ctl->str_full[stage], 0, h_str, r0, b);
+            tma_load_4d(dst + kStrTileBytes + kStrHalfBytes, &maps.str_g[s], &ctl->str_full[stage], 64, h_str, r0, b);
+            if (a.mode_dkv) {
+              const long long soff = ((long long)b * a.Hq + h_str) * a.seg_stat_pad[s] + r0;
+              bulk_load(dst + 2 * kStrTileBytes, a.seg_lse2[s] + soff, kStrRows * 4, &ctl->str_full[stage]);
+              bulk_load(dst + 2 * kStrTileBytes + kStrRows * 4, a.seg_delta[s] + soff, kStrRows * 4,
+                        &ctl->str_full[stage]);
+            }
+            ++n;
+          }
+        }
+      }
+      if (!ok) {
+        const int first = n > kBwdStages ? n - kBwdStages : 0;
+        for (int m = first; m < n; ++m) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&ctl->str_full[m % kBwdStages], (m / kBwdStages) & 1) &&
+                 clock64() - t0 < kWaitCycleLimit / 16) {
+          }
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0 && total_steps > 0) {
+      constexpr uint32_t idesc_xy = umma_idesc_bf16(kOwnRows, kStrRows, false, false);  // 128 x 64, both K-major
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(kOwnRows, kBD, false, true);       // 128 x 128, B MN-major
+      const uint32_t own_s = smem_u32(sOwn), own_g_s = smem_u32(sOwnG), stage_s = smem_u32(sStage);
+      const int T = total_steps;
+      bool ok = mbar_wait(&ctl->own_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
+
+      auto issue_xy = [&](int t) {
+        const int stage = t % kBwdStages, buf = t & 1;
+        const uint32_t str_s = stage_s + stage * kBwdStageBytes;
+        const uint32_t tx = tmem + 256 + buf * 128, ty = tx + 64;
+#pragma unroll
+        for (int k = 0; k < kBD / 16; ++k) {
+          const uint32_t offo = (k >> 2) * kOwnHalfBytes + (k & 3) * 32;
+          const uint32_t offs = (k >> 2) * kStrHalfBytes + (k & 3) * 32;
+          umma_ss(tx, umma_smem_desc(own_s + offo, 16, 1024), umma_smem_desc(str_s + offs, 16, 1024), idesc_xy,
+                  k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < kBD / 16; ++k) {
+          const uint32_t offo = (k >> 2) * kOwnHalfBytes + (k & 3) * 32;
+          const uint32_t offs = (k >> 2) * kStrHalfBytes + (k & 3) * 32;
+          umma_ss(ty, umma_smem_desc(own_g_s + offo, 16, 1024),
+                  umma_smem_desc(str_s + kStrTileBytes + offs, 16, 1024), idesc_xy, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&ctl->xy_full[buf]);
+      };
+      auto issue_acc = [&](int t) {
+        const int stage = t % kBwdStages, buf = t & 1;
+        const uint32_t str_s = stage_s + stage * kBwdStageBytes;
+        const uint32_t tx = tmem + 256 + buf * 128, ty = tx + 64;
+        // dS (overlaying Y) times the stream tile read MN-major: 16 stream rows per instruction.
+        // P/dS columns: rows 0..31 of the step sit in columns [0,16), rows 32..63 in [32,48).
+#pragma unroll
+        for (int k = 0; k < kStrRows / 16; ++k) {
+          const uint32_t acol = (k >> 1) * 32 + (k & 1) * 8;
+          umma_ts(tmem + 0, ty + acol, umma_smem_desc(str_s + k * 2048, kStrHalfBytes, 1024), idesc_acc,
+                  (t > 0 || k > 0) ? 1u : 0u);
+        }
+        if (a.mode_dkv) {
+#pragma unroll
+          for (int k = 0; k < kStrRows / 16; ++k) {
+            const uint32_t acol = (k >> 1) * 32 + (k & 1) * 8;
+            umma_ts(tmem + 128, tx + acol, umma_smem_desc(str_s + kStrTileBytes + k * 2048, kStrHalfBytes, 1024),
+                    idesc_acc, (t > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(&ctl->str_empty[stage]);
+      };
+
+      for (int t = 0; t < 2 && t < T && ok; ++t) {
+        ok = mbar_wait(&ctl->str_full[t % kBwdStages], 0, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+        if (ok) {
+          tc_fence_after();
+          issue_xy(t);
+        }
+      }
+      for (int t = 0; t < T && ok; ++t) {
+        ok = mbar_wait(&ctl->pd_full[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_P);
+        if (!ok) break;
+        tc_fence_after();
+        issue_acc(t);
+        if (t + 2 < T) {
+          const int n = t + 2;
+          ok = mbar_wait(&ctl->str_full[n % kBwdStages], (n / kBwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          issue_xy(n);
+        }
+      }
+      if (ok) {
+        umma_commit(&ctl->acc_full);
+      } else {
+        umma_commit(&ctl->drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&ctl->drain, 0) && clock64() - t0 < kWaitCycleLimit / 16) {
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------ element-wise warps (0..7) + epilogue
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = (quarter << 5) | lane;  // owner row == tensor-memory lane
+    const uint32_t lane_field = static_cast<uint32_t>(quarter << 5) << 16;
+    const int own_pos = a.own_off + own0 + row;
+    bool ok = true;
+
+    float row_lse2 = 0.f, row_delta = 0.f;
+    if (!a.mode_dkv) {
+      const int r = min(own0 + row, a.own_stat_pad - 1);
+      const long long soff = ((long long)b * a.Hq + h_own) * a.own_stat_pad + r;
+      row_lse2 = a.own_lse2[soff];
+      row_delta = a.own_delta[soff];
+    }
+
+    int t = 0;
+    for (int s = 0; s < a.nseg && ok; ++s) {
+      const int f = ctl->seg_first[s], l = ctl->seg_last[s];
+      const int seg_off = a.seg_off[s];
+      for (int g = 0; g < n_sub && ok; ++g) {
+        for (int st = f; st < l; ++st, ++t) {
+          const int buf = t & 1, stage = t % kBwdStages;
+          ok = mbar_wait_warp(&ctl->xy_full[buf], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_S);
+          if (!ok) break;
+          // the stage's statistics arrived with the stream tile (completed long ago; cheap re-check)
+          if (a.mode_dkv) {
+            ok = mbar_wait_warp(&ctl->str_full[stage], (t / kBwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          const uint32_t tx = tmem + 256 + buf * 128 + lane_field, ty = tx + 64;
+          uint32_t xr[32], yr[32];
+          tmem_ld32(tx + half * 32, xr);
+          tmem_ld32(ty + half * 32, yr);
+          tmem_wait_ld();
+
+          const int c0 = st * kStrRows + half * 32;  // first stream row (local to the segment) of my columns
+          // causal limits on my 32 columns: dKV mode masks queries before the key, dQ mode keys after the query
+          int lo = 0, hi = 32;
+          if (a.causal) {
+            if (a.mode_dkv) lo = own_pos - (seg_off + c0);        // query c visible iff seg_off+c0+c >= own_pos
+            else hi = own_pos - (seg_off + c0) + 1;               // key c visible iff seg_off+c0+c <= own_pos
+          }
+          const float* stats = reinterpret_cast<const float*>(sStage + stage * kBwdStageBytes + 2 * kStrTileBytes);
+          uint32_t pk[16], dk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float l0, l1, d0, d1;
+            if (a.mode_dkv) {
+              const float2 lv = *reinterpret_cast<const float2*>(stats + half * 32 + e);
+              const float2 dv = *reinterpret_cast<const float2*>(stats + kStrRows + half * 32 + e);
+              l0 = lv.x; l1 = lv.y; d0 = dv.x; d1 = dv.y;
+            } else {
+              l0 = l1 = row_lse2;
+              d0 = d1 = row_delta;
+            }
+            float p0 = fast_exp2(fmaf(__uint_as_float(xr[e]), a.scale_log2, -l0));
+            float p1 = fast_exp2(fmaf(__uint_as_float(xr[e + 1]), a.scale_log2, -l1));
+            if (e < lo || e >= hi) p0 = 0.f;
+            if (e + 1 < lo || e + 1 >= hi) p1 = 0.f;
+            const float s0 = p0 * (__uint_as_float(yr[e]) - d0);
+            const float s1 = p1 * (__uint_as_float(yr[e + 1]) - d1);
+            pk[e >> 1] = pack_bf16x2(p0, p1);
+            dk[e >> 1] = pack_bf16x2(s0, s1);
+          }
+          tmem_st16(tx + half * 32, pk);
+          tmem_st16(ty + half * 32, dk);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&ctl->pd_full[buf]);
+        }
+      }
+    }
+
+    // epilogue: each warp stores its lane quarter x column half of the accumulators
+    if (ok && own0 < a.own_rows) {
+      const bool have = total_steps > 0;
+      if (have) ok = mbar_wait_warp(&ctl->acc_full, 0, abort_word, MB_ERR_TIMEOUT_O);
+      if (ok) {
+        if (have) tc_fence_after();
+        const bool store = own0 + row < a.own_rows;
+        const int n_out = a.mode_dkv ? 2 : 1;
+        for (int which = 0; which < n_out; ++which) {
+          void* base = which ? a.out2 : a.out1;
+          const float mul = which ? 1.f : a.scale;  // dK and dQ carry the softmax scale, dV does not
+          const long long off = (long long)b * a.o_sb + (long long)(own0 + row) * a.o_ss + (long long)h_own * a.o_sh;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t acc[32];
+            if (have) {
+              tmem_ld32(tmem + which * 128 + lane_field + half * 64 + c * 32, acc);
+              tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) acc[e] = 0u;
+            }
+            if (!store) continue;
+            const int col = half * 64 + c * 32;
+            if (a.out_mode == 0) {
+              uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(base) + off + col);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 w;
+                w.x = pack_bf16x2(__uint_as_float(acc[v * 8 + 0]) * mul, __uint_as_float(acc[v * 8 + 1]) * mul);
+                w.y = pack_bf16x2(__uint_as_float(acc[v * 8 + 2]) * mul, __uint_as_float(acc[v * 8 + 3]) * mul);
+                w.z = pack_bf16x2(__uint_as_float(acc[v * 8 + 4]) * mul, __uint_as_float(acc[v * 8 + 5]) * mul);
+                w.w = pack_bf16x2(__uint_as_float(acc[v * 8 + 6]) * mul, __uint_as_float(acc[v * 8 + 7]) * mul);
+                dst[v] = w;
+              }
+            } else {
+              float4* dst = reinterpret_cast<float4*>(static_cast<float*>(base) + off + col);
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 w = make_float4(__uint_as_float(acc[v * 4 + 0]) * mul, __uint_as_float(acc[v * 4 + 1]) * mul,
+                                       __uint_as_float(acc[v * 4 + 2]) * mul, __uint_as_float(acc[v * 4 + 3]) * mul);
+                if (a.out_mode == 2) {
+                  const float4 old = dst[v];
+                  w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w;
+                }
+                dst[v] = w;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+  if (tid == 0 && ctl->abort_word != 0 && a.status != nullptr) atomicCAS(a.status, 0, ctl->abort_word);
+}
+
+// ---------------------------------------------------------------------------
+// preprocess: delta = rowsum(dO * O), lse2 = lse * log2(e)  ->  [B, Hq, pad] fp32 each
+// ---------------------------------------------------------------------------
+struct PreArgs {
+  const __nv_bfloat16* dout;
+  const __nv_bfloat16* out;
+  long long do_sb, do_ss, do_sh, o_sb, o_ss, o_sh;
+  const float* lse;  // [B,Hq,Sq]
+  float* lse2;       // [B,Hq,pad]
+  float* delta;      // [B,Hq,pad]
+  int B, Sq, Hq, pad;
+};
+
+// One warp per (b, h, row); a block covers 8 consecutive rows of one (b, h).
+__global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreArgs a) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int row = blockIdx.x * 8 + w;
+  const int h = blockIdx.y, b = blockIdx.z;
+  if (row >= a.pad) return;
+  const long long sidx = ((long long)b * a.Hq + h) * a.pad + row;
+  if (row >= a.Sq) {
+    if (lane == 0) {
+      a.lse2[sidx] = INFINITY;
+      a.delta[sidx] = 0.f;
+    }
+    return;
+  }
+  const uint2 dv = *reinterpret_cast<const uint2*>(a.dout + b * a.do_sb + row * a.do_ss + h * a.do_sh + lane * 4);
+  const uint2 ov = *reinterpret_cast<const uint2*>(a.out + b * a.o_sb + row * a.o_ss + h * a.o_sh + lane * 4);
+  float acc = __uint_as_float(dv.x << 16) * __uint_as_float(ov.x << 16) +
+              __uint_as_float(dv.x & 0xffff0000u) * __uint_as_float(ov.x & 0xffff0000u) +
+              __uint_as_float(dv.y << 16) * __uint_as_float(ov.y << 16) +
+              __uint_as_float(dv.y & 0xffff0000u) * __uint_as_float(ov.y & 0xffff0000u);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    const float l = a.lse[((long long)b * a.Hq + h) * a.Sq + row];
+    a.lse2[sidx] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+    a.delta[sidx] = acc;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+static int make_map(CUtensorMap* map, const void* ptr, int H, int S, int B, long long sb, long long ss, long long sh,
+                    int box_rows) {
+  cuuint64_t dims[4] = {(cuuint64_t)kBD, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)ss * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return encode_tiled_bf16(map, const_cast<void*>(ptr), 4, dims, strides, box, estr);
+}
+
+static int set_smem_attr_once() {
+  static bool done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return MB_E_CUDA;
+  if (dev >= 0 && dev < 64 && !done[dev]) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmemBytes) !=
+        cudaSuccess)
+      return MB_E_CUDA;
+    done[dev] = true;
+  }
+  return MB_SUCCESS;
+}
+
+int launch_bwd_preprocess(const mb_bwd_preprocess_args* x, cudaStream_t stream) {
+  if (x == nullptr || x->dout == nullptr || x->out == nullptr || x->lse == nullptr || x->lse2 == nullptr ||
+      x->delta == nullptr)
+    return MB_E_INVALID;
+  if (x->head_dim != kBD) return MB_E_UNSUPPORTED;
+  if (x->batch <= 0 || x->hq <= 0 || x->sq < 0 || x->stat_pad < x->sq || x->stat_pad % kStrRows != 0)
+    return MB_E_INVALID;
+  if (x->stat_pad == 0) return MB_SUCCESS;
+  PreArgs a;
+  a.dout = static_cast<const __nv_bfloat16*>(x->dout);
+  a.out = static_cast<const __nv_bfloat16*>(x->out);
+  a.do_sb = x->dout_stride_b; a.do_ss = x->dout_stride_s; a.do_sh = x->dout_stride_h;
+  a.o_sb = x->out_stride_b; a.o_ss = x->out_stride_s; a.o_sh = x->out_stride_h;
+  a.lse = x->lse; a.lse2 = x->lse2; a.delta = x->delta;
+  a.B = x->batch; a.Sq = x->sq; a.Hq = x->hq; a.pad = x->stat_pad;
+  dim3 grid((x->stat_pad + 7) / 8, x->hq, x->batch);
+  bwd_preprocess_kernel<<<grid, 256, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+}
+
+int launch_attn_bwd(const mb_attn_bwd_args* x, cudaStream_t stream) {
+  if (x == nullptr) return MB_E_INVALID;
+  if (x->head_dim != kBD) return MB_E_UNSUPPORTED;
+  if (x->batch <= 0 || x->hq <= 0 || x->hkv <= 0 || x->hq % x->hkv != 0) return MB_E_INVALID;
+  if (x->nseg < 0 || x->nseg > MB_MAX_SEGMENTS || x->own_rows < 0) return MB_E_INVALID;
+  if (x->out_mode < 0 || x->out_mode > 2) return MB_E_INVALID;
+  if (x->own_rows == 0) return MB_SUCCESS;
+  if (x->own == nullptr || x->own_g == nullptr || x->out1 == nullptr) return MB_E_INVALID;
+  const bool dkv = x->mode == MB_BWD_MODE_DKV;
+  if (!dkv && x->mode != MB_BWD_MODE_DQ) return MB_E_INVALID;
+  if (dkv && x->out2 == nullptr) return MB_E_INVALID;
+  if (!dkv && (x->own_lse2 == nullptr || x->own_delta == nullptr || x->own_stat_pad < x->own_rows))
+    return MB_E_INVALID;
+  int rc = set_smem_attr_once();
+  if (rc != MB_SUCCESS) return rc;
+
+  BwdMaps maps;
+  BwdArgs a;
+  memset(&maps, 0, sizeof(maps));
+  memset(&a, 0, sizeof(a));
+  const int h_own = dkv ? x->hkv : x->hq;
+  const int h_str = dkv ? x->hq : x->hkv;
+  if (make_map(&maps.own, x->own, h_own, x->own_rows, x->batch, x->own_stride_b, x->own_stride_s, x->own_stride_h,
+               kOwnRows) ||
+      make_map(&maps.own_g, x->own_g, h_own, x->own_rows, x->batch, x->own_stride_b, x->own_stride_s,
+               x->own_stride_h, kOwnRows))
+    return MB_E_TENSORMAP;
+  int nseg = 0;
+  for (int s = 0; s < x->nseg; ++s) {
+    const mb_bwd_segment& g = x->seg[s];
+    if (g.rows < 0) return MB_E_INVALID;
+    if (g.rows == 0) continue;
+    if (g.str == nullptr || g.str_g == nullptr) return MB_E_INVALID;
+    if (dkv && (g.lse2 == nullptr || g.delta == nullptr || g.stat_pad < g.rows || g.stat_pad % kStrRows != 0))
+      return MB_E_INVALID;
+    if (make_map(&maps.str[nseg], g.str, h_str, g.rows, x->batch, g.stride_b, g.stride_s, g.stride_h, kStrRows) ||
+        make_map(&maps.str_g[nseg], g.str_g, h_str, g.rows, x->batch, g.stride_b, g.stride_s, g.stride_h, kStrRows))
+      return MB_E_TENSORMAP;
+    a.seg_rows[nseg] = g.rows;
+    a.seg_off[nseg] = g.pos_off;
+    a.seg_lse2[nseg] = g.lse2;
+    a.seg_delta[nseg] = g.delta;
+    a.seg_stat_pad[nseg] = g.stat_pad;
+    a.seg_flag[nseg] = g.ready_flag;
+    a.seg_flag_value[nseg] = g.ready_value;
+    ++nseg;
+  }
+  a.nseg = nseg;
+  a.mode_dkv = dkv ? 1 : 0;
+  a.B = x->batch;
+  a.own_rows = x->own_rows;
+  a.Hq = x->hq;
+  a.Hkv = x->hkv;
+  a.group = x->hq / x->hkv;
+  a.own_off = x->own_off;
+  a.causal = x->causal ? 1 : 0;
+  a.scale = x->softmax_scale;
+  a.scale_log2 = x->softmax_scale * 1.4426950408889634f;
+  a.own_lse2 = x->own_lse2;
+  a.own_delta = x->own_delta;
+  a.own_stat_pad = x->own_stat_pad;
+  a.out1 = x->out1;
+  a.out2 = x->out2;
+  a.o_sb = x->out_stride_b;
+  a.o_ss = x->out_stride_s;
+  a.o_sh = x->out_stride_h;
+  a.out_mode = x->out_mode;
+  a.status = x->status ? x->status : default_status_word();
+  if (a.status == nullptr) return MB_E_CUDA;
+
+  dim3 grid((x->own_rows + kOwnRows - 1) / kOwnRows, h_own, x->batch);
+  attn_bwd_kernel<0><<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(maps, a);
+  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+}
+
+}  // namespace mb

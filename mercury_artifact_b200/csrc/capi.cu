@@ -47,6 +47,14 @@ int mb_attn_fwd(const mb_attn_fwd_args* args, void* cuda_stream) {
   return mb::launch_attn_fwd(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int mb_attn_bwd_preprocess(const mb_bwd_preprocess_args* args, void* cuda_stream) {
+  return mb::launch_bwd_preprocess(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int mb_attn_bwd(const mb_attn_bwd_args* args, void* cuda_stream) {
+  return mb::launch_attn_bwd(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int mb_merge_out_lse(const mb_merge_args* args, void* cuda_stream) {
   return mb::launch_merge(args, static_cast<cudaStream_t>(cuda_stream));
 }

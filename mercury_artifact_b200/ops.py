@@ -16,7 +16,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from .attention import attn_fwd_segments, _stream_ptr
+from .attention import _stream_ptr, attn_bwd_dkv, attn_bwd_dq, attn_fwd_segments, bwd_preprocess
 
 
 # -- get_default_args -----------------------------------------------------------------------
@@ -77,6 +77,48 @@ def _flash_attn_forward(
     q_off = k.shape[1] - q.shape[1] if causal else 0
     out, lse = attn_fwd_segments(q, [(k, v, 0)], softmax_scale, causal=bool(causal), q_off=q_off)
     return out, lse, None, None
+
+
+# -- block backward -------------------------------------------------------------------------
+def _flash_attn_backward(
+    dout: torch.Tensor,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    softmax_lse: torch.Tensor,
+    dq: Optional[torch.Tensor],
+    dk: Optional[torch.Tensor],
+    dv: Optional[torch.Tensor],
+    dropout_p: float,
+    softmax_scale: float,
+    causal: bool,
+    window_size_left: int = -1,
+    window_size_right: int = -1,
+    softcap: float = 0.0,
+    alibi_slopes: Optional[torch.Tensor] = None,
+    deterministic: bool = False,
+    rng_state: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Block attention backward, the per-step call of the generated backward loop
+    (utils/attn_bwd_dsl.py:115).  Writes dq, dk, dv IN PLACE (dk/dv may be the two halves of
+    a packed [2,...] buffer) and returns softmax_d = rowsum(dout * out) as [B, Hq, pad64(Sq)].
+    `out` and `softmax_lse` are the final forward results of the query rows, which need not come
+    from this K/V block alone.  Always deterministic (no atomics)."""
+    _reject_unsupported(dropout_p, window_size_left, window_size_right, softcap, alibi_slopes)
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** -0.5
+    if dq is None:
+        dq = torch.empty_like(q)
+    if dk is None:
+        dk = torch.empty_like(k)
+    if dv is None:
+        dv = torch.empty_like(v)
+    q_off = k.shape[1] - q.shape[1] if causal else 0
+    stats = bwd_preprocess(dout, out, softmax_lse)
+    attn_bwd_dq(q, dout, stats, [(k, v, 0)], softmax_scale, causal=bool(causal), q_off=q_off, dq=dq)
+    attn_bwd_dkv(k, v, [(q, dout, stats, q_off)], softmax_scale, causal=bool(causal), k_off=0, dk=dk, dv=dv)
+    return stats.delta
 
 
 # -- merge ----------------------------------------------------------------------------------

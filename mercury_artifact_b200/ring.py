@@ -1,19 +1,25 @@
-"""Fused ring / double-ring / GQA attention forward for one rank (public API).
+"""Fused ring / double-ring / GQA attention for one rank: forward and backward (public API).
 
 `RingAttention.forward` computes what the generated per-rank loop computes
 (mercury/backend/pytorch/codegen.py:443-494 + utils/flash_attn_dsl.py:160-179 of
 the reference) with ONE attention launch: the K/V shards of all ranks are the
 segments of a single mb_attn_fwd call in the rank's arrival order, so the
 online-softmax state stays on chip and no out/LSE merge kernel runs.
+`RingAttention.backward` replaces the generated backward loop
+(codegen.py:99-190, utils/attn_bwd_dsl.py:70-134) with two launches: dQ of the
+local queries over all K/V shards, and dK/dV of the local keys over all query
+shards.  Every gradient tile is owned by one CTA, so the reference's rotating
+fp32 dK/dV accumulator and its write-back hop have no counterpart here.
 
 Transport.  On an NVSwitch box every peer is one hop away, so a shard is pulled
 straight from the rank that owns it instead of being relayed around the ring;
 the order in which a rank consumes shards is still the reference's (single ring:
 (r - t) mod P; nested rings: mesh.kv_origin_schedule).  The copy engines move
-each remote shard over NVLink into a local staging buffer on a side stream and a
-per-segment flag is raised behind it; the kernel's loader waits (bounded) on
-that flag before its first TMA load of the segment, so compute on the shards
-already here overlaps the transfers of the later ones inside one launch.
+each remote shard over NVLink into a local staging buffer on a high-priority
+side stream and a per-segment flag is raised behind it; the kernel's loader
+waits (bounded) on that flag before its first TMA load of the segment, so
+compute on the shards already here overlaps the transfers of the later ones
+inside one launch.
 
 World size 1 is the unsharded program: one segment, no transport.
 """
@@ -24,14 +30,100 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from . import mesh
-from .attention import attn_fwd_segments
-from .comm import PeerContext, SymmetricBuffer, default_context
+from .attention import (RowStats, _pad64, attn_bwd_dkv, attn_bwd_dq, attn_fwd_segments, bwd_preprocess)
+from .comm import PeerContext, SymmetricBuffer, _align, default_context
 
 _FLAG_REGION = 4096
 
 
+class _ShardExchange:
+    """Publish one byte-slot per rank and epoch; pull peers' slots into local staging.
+
+    Symmetric memory per rank: two slots (epoch parity) + flag words
+        ready[origin] at +0     raised on every peer once `origin` has published its slot
+        done[reader]  at +1024  raised on the owner once `reader` no longer needs the slot
+    Local memory: world-1 staging slots and one arrival flag per staging slot.
+    All flag values are epoch numbers, which only grow.
+    """
+
+    def __init__(self, ctx: PeerContext, slot_bytes: int):
+        self.ctx = ctx
+        self.world, self.rank = ctx.world, ctx.rank
+        self.slot_bytes = _align(slot_bytes, 1024)
+        self.sym = SymmetricBuffer(ctx, 2 * self.slot_bytes + _FLAG_REGION)
+        self._flag_off = 2 * self.slot_bytes
+        self.staging = torch.empty((max(self.world - 1, 1), self.slot_bytes), dtype=torch.uint8, device=ctx.device)
+        self.seg_flags = torch.zeros(64, dtype=torch.int32, device=ctx.device)
+        self.epoch = 0
+        self._next_stage = 0
+        torch.cuda.synchronize(ctx.device)
+
+    def _ready_ptr(self, on_rank: int, origin: int) -> int:
+        return self.sym.ptr(on_rank, self._flag_off + 4 * origin)
+
+    def _done_ptr(self, on_rank: int, reader: int) -> int:
+        return self.sym.ptr(on_rank, self._flag_off + 1024 + 4 * reader)
+
+    def local_slot(self) -> torch.Tensor:
+        off = (self.epoch % 2) * self.slot_bytes
+        return self.sym.local.bytes()[off:off + self.slot_bytes]
+
+    def begin(self, main: torch.cuda.Stream) -> torch.Tensor:
+        """Start a new epoch; returns this rank's byte slot to fill on the transfer stream."""
+        ctx, comm = self.ctx, self.ctx.comm_stream
+        self.epoch += 1
+        self._next_stage = 0
+        e = self.epoch
+        comm.wait_stream(main)
+        if e > 2:  # the slot was last used at epoch e-2: every peer has released it by now or soon
+            for p in range(self.world):
+                if p != self.rank:
+                    ctx.wait_flag(self._done_ptr(self.rank, p), e - 2, comm)
+        return self.local_slot()
+
+    def publish(self) -> torch.cuda.Event:
+        """Announce the filled slot to every peer; the event fires once the local copy is in place."""
+        ctx, comm = self.ctx, self.ctx.comm_stream
+        ev = torch.cuda.Event()
+        ev.record(comm)
+        for p in range(self.world):
+            if p != self.rank:
+                ctx.signal(self._ready_ptr(p, self.rank), self.epoch, comm)
+        return ev
+
+    def pull(self, origin: int, ranges: Optional[Sequence[Tuple[int, int]]] = None) -> Tuple[torch.Tensor, int]:
+        """Copy `origin`'s slot of this epoch (or the given (offset, nbytes) ranges of it) into the
+        next staging slot (copy engines over NVLink).  Returns (staging bytes, address of the
+        arrival flag that reaches `epoch` behind the copy)."""
+        ctx, comm = self.ctx, self.ctx.comm_stream
+        e = self.epoch
+        idx = self._next_stage
+        self._next_stage += 1
+        ctx.wait_flag(self._ready_ptr(self.rank, origin), e, comm)
+        dst = self.staging[idx]
+        base = (e % 2) * self.slot_bytes
+        for off, nbytes in (ranges if ranges is not None else [(0, self.slot_bytes)]):
+            ctx.copy(dst.data_ptr() + off, self.sym.ptr(origin, base + off), nbytes, comm)
+        flag_ptr = self.seg_flags.data_ptr() + 4 * idx
+        ctx.signal(flag_ptr, e, comm)
+        ctx.signal(self._done_ptr(origin, self.rank), e, comm)
+        return dst, flag_ptr
+
+    def release(self, origin: int) -> None:
+        """Tell `origin` that this rank will not read its slot of this epoch."""
+        self.ctx.signal(self._done_ptr(origin, self.rank), self.epoch, self.ctx.comm_stream)
+
+
+def _carve(buf: torch.Tensor, offset: int, shape, dtype) -> Tuple[torch.Tensor, int]:
+    n = 1
+    for s in shape:
+        n *= int(s)
+    nbytes = n * torch.empty((), dtype=dtype).element_size()
+    return buf[offset:offset + nbytes].view(dtype).view(*shape), offset + _align(nbytes, 256)
+
+
 class RingAttention:
-    """Forward attention of one rank of a sequence-sharded job.
+    """Attention of one rank of a sequence-sharded job.
 
     mesh_shape (P,) is the single ring, (n_inner, n_outer) the double ring (inner ring over
     mesh dimension 0, rank = inner + n_inner * outer).  Shard k of the sequence lives on rank k.
@@ -51,35 +143,26 @@ class RingAttention:
         if self.ctx is not None and self.ctx.world != self.world:
             raise ValueError(f"mesh {self.mesh_shape} needs {self.world} ranks, the process group has {self.ctx.world}")
         self.order = mesh.kv_origin_schedule(self.rank, self.mesh_shape)
+        self.q_shape = (batch, seq_local, hq, head_dim)
         self.kv_shape = (2, batch, seq_local, hkv, head_dim)
-        self.kv_bytes = 2 * batch * seq_local * hkv * head_dim * 2
-        self.epoch = 0
+        self.stat_pad = _pad64(seq_local)
+        self.stat_shape = (2, batch, hq, self.stat_pad)
         self.launches_per_forward = 1
-        if self.world > 1:
-            # symmetric: two epochs of this rank's shard, then flag words:
-            #   ready[origin] at +0     raised on every peer once `origin` has published its shard
-            #   done[reader]  at +1024  raised on the owner once `reader` has pulled the shard
-            self.sym = SymmetricBuffer(self.ctx, 2 * self.kv_bytes + _FLAG_REGION)
-            self._flag_off = 2 * self.kv_bytes
-            dev = self.ctx.device
-            self.staging = [torch.empty(self.kv_shape, dtype=torch.bfloat16, device=dev) for _ in range(self.world - 1)]
-            self.seg_flags = torch.zeros(64, dtype=torch.int32, device=dev)
-            torch.cuda.synchronize(dev)
+        self.launches_per_backward = 3
+        self._fwd_x: Optional[_ShardExchange] = None
+        self._bwd_x: Optional[_ShardExchange] = None
 
-    # ------------------------------------------------------------------ addresses
-    def _ready_ptr(self, on_rank: int, origin: int) -> int:
-        return self.sym.ptr(on_rank, self._flag_off + 4 * origin)
-
-    def _done_ptr(self, on_rank: int, reader: int) -> int:
-        return self.sym.ptr(on_rank, self._flag_off + 1024 + 4 * reader)
-
-    def shard_slot(self, epoch: int) -> torch.Tensor:
-        """This rank's published K/V slot for `epoch`."""
-        return self.sym.local.view((epoch % 2) * self.kv_bytes, self.kv_shape, torch.bfloat16)
-
-    def needed(self, origin: int) -> bool:
+    # ------------------------------------------------------------------ helpers
+    def _sees_keys_of(self, origin: int) -> bool:
         """Whether this rank's queries can see any key of `origin`'s shard."""
         return (not self.causal) or origin <= self.rank
+
+    def _seen_by_queries_of(self, origin: int) -> bool:
+        """Whether `origin`'s queries can see any key of this rank's shard."""
+        return (not self.causal) or origin >= self.rank
+
+    def _kv_bytes(self) -> int:
+        return 2 * self.batch * self.seq_local * self.hkv * self.head_dim * 2
 
     # ------------------------------------------------------------------ forward
     def forward(self, q: torch.Tensor, kv: torch.Tensor, o: Optional[torch.Tensor] = None,
@@ -94,46 +177,107 @@ class RingAttention:
         if self.world == 1:
             return attn_fwd_segments(q, [(kv[0], kv[1], 0)], softmax_scale, causal=self.causal, q_off=0, out=o, lse=lse)
 
-        ctx = self.ctx
+        if self._fwd_x is None:
+            self._fwd_x = _ShardExchange(self.ctx, self._kv_bytes())
+        x = self._fwd_x
         main = torch.cuda.current_stream()
-        comm = ctx.comm_stream
-        self.epoch += 1
-        e = self.epoch
-        slot = self.shard_slot(e)
+        comm = self.ctx.comm_stream
         me = self.rank
 
-        # 1. publish my shard.  The slot was last used at epoch e-2: every peer has raised
-        #    done >= e-2 on me once it no longer reads it.
-        comm.wait_stream(main)
-        if e > 2:
-            for p in range(self.world):
-                if p != me:
-                    ctx.wait_flag(self._done_ptr(me, p), e - 2, comm)
+        slot_bytes = x.begin(main)
+        slot, _ = _carve(slot_bytes, 0, self.kv_shape, torch.bfloat16)
         with torch.cuda.stream(comm):
             slot.copy_(kv, non_blocking=True)
-        local_ready = torch.cuda.Event()
-        local_ready.record(comm)
-        for p in range(self.world):
-            if p != me:
-                ctx.signal(self._ready_ptr(p, me), e, comm)
+        local_ready = x.publish()
 
-        # 2. pull the remote shards in arrival order; raise a local flag behind each one
         segs: List[tuple] = [(slot[0], slot[1], me * L)]
         for t in range(1, self.world):
             origin = self.order[t]
-            if self.needed(origin):
-                ctx.wait_flag(self._ready_ptr(me, origin), e, comm)
-                dst = self.staging[t - 1]
-                ctx.copy(dst.data_ptr(), self.sym.ptr(origin, (e % 2) * self.kv_bytes), self.kv_bytes, comm)
-                ctx.signal(self.seg_flags.data_ptr() + 4 * t, e, comm)
-                segs.append((dst[0], dst[1], origin * L, self.seg_flags.data_ptr() + 4 * t, e))
-            ctx.signal(self._done_ptr(origin, me), e, comm)
+            if self._sees_keys_of(origin):
+                buf, flag_ptr = x.pull(origin)
+                rkv, _ = _carve(buf, 0, self.kv_shape, torch.bfloat16)
+                segs.append((rkv[0], rkv[1], origin * L, flag_ptr, x.epoch))
+            else:
+                x.release(origin)
 
-        # 3. one fused launch on the caller's stream once my own shard is in its slot
         main.wait_event(local_ready)
-        out = attn_fwd_segments(q, segs, softmax_scale, causal=self.causal, q_off=me * L, out=o, lse=lse)
-        # the next forward's first transfer must not overwrite staging this launch still reads
-        return out
+        return attn_fwd_segments(q, segs, softmax_scale, causal=self.causal, q_off=me * L, out=o, lse=lse)
+
+    # ------------------------------------------------------------------ backward
+    def backward(self, dout: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
+                 dq: Optional[torch.Tensor] = None, dkv: Optional[torch.Tensor] = None,
+                 softmax_scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Gradients of this rank's shard: dq like q, dkv like kv ([2,B,S/P,Hkv,D]).
+        o and lse are this rank's forward results (lse [B,Hq,S/P])."""
+        if tuple(kv.shape) != self.kv_shape or tuple(q.shape) != self.q_shape:
+            raise ValueError("q/kv do not match the shapes this object was built for")
+        if softmax_scale is None:
+            softmax_scale = self.head_dim ** -0.5
+        if dq is None:
+            dq = torch.empty_like(q)
+        if dkv is None:
+            dkv = torch.empty_like(kv)
+        L = self.seq_local
+        me = self.rank
+        if self.world == 1:
+            stats = bwd_preprocess(dout, o, lse)
+            attn_bwd_dq(q, dout, stats, [(kv[0], kv[1], 0)], softmax_scale, causal=self.causal, q_off=0, dq=dq)
+            attn_bwd_dkv(kv[0], kv[1], [(q, dout, stats, 0)], softmax_scale, causal=self.causal, k_off=0,
+                         dk=dkv[0], dv=dkv[1])
+            return dq, dkv
+
+        kv_b = self._kv_bytes()
+        q_b = self.batch * L * self.hq * self.head_dim * 2
+        st_b = 2 * self.batch * self.hq * self.stat_pad * 4
+        off_kv, off_q = 0, _align(kv_b, 256)
+        off_do = off_q + _align(q_b, 256)
+        off_st = off_do + _align(q_b, 256)
+        if self._bwd_x is None:
+            self._bwd_x = _ShardExchange(self.ctx, off_st + _align(st_b, 256))
+        x = self._bwd_x
+        main = torch.cuda.current_stream()
+        comm = self.ctx.comm_stream
+
+        def views(buf):
+            v_kv, _ = _carve(buf, off_kv, self.kv_shape, torch.bfloat16)
+            v_q, _ = _carve(buf, off_q, self.q_shape, torch.bfloat16)
+            v_do, _ = _carve(buf, off_do, self.q_shape, torch.bfloat16)
+            v_st, _ = _carve(buf, off_st, self.stat_shape, torch.float32)
+            return v_kv, v_q, v_do, v_st
+
+        # statistics of my rows go straight into my slot (main stream), the tensors are copied beside them
+        slot_bytes = x.begin(main)
+        s_kv, s_q, s_do, s_st = views(slot_bytes)
+        with torch.cuda.stream(comm):
+            stats = bwd_preprocess(dout, o, lse, workspace=s_st)
+            s_kv.copy_(kv, non_blocking=True)
+            s_q.copy_(q, non_blocking=True)
+            s_do.copy_(dout, non_blocking=True)
+        local_ready = x.publish()
+
+        kv_segs = [{"str": s_kv[0], "str_g": s_kv[1], "off": me * L}]
+        q_segs = [{"str": s_q, "str_g": s_do, "stats": stats, "off": me * L}]
+        for t in range(1, self.world):
+            origin = self.order[t]
+            need_kv, need_q = self._sees_keys_of(origin), self._seen_by_queries_of(origin)
+            if not (need_kv or need_q):
+                x.release(origin)
+                continue
+            ranges = ([(off_kv, kv_b)] if need_kv else []) + ([(off_q, off_st + st_b - off_q)] if need_q else [])
+            buf, flag_ptr = x.pull(origin, ranges)
+            r_kv, r_q, r_do, r_st = views(buf)
+            if need_kv:
+                kv_segs.append({"str": r_kv[0], "str_g": r_kv[1], "off": origin * L,
+                                "flag": flag_ptr, "flag_value": x.epoch})
+            if need_q:
+                q_segs.append({"str": r_q, "str_g": r_do, "stats": RowStats(r_st[0], r_st[1], L), "off": origin * L,
+                               "flag": flag_ptr, "flag_value": x.epoch})
+
+        main.wait_event(local_ready)
+        attn_bwd_dq(q, dout, stats, kv_segs, softmax_scale, causal=self.causal, q_off=me * L, dq=dq, hkv=self.hkv)
+        attn_bwd_dkv(kv[0], kv[1], q_segs, softmax_scale, causal=self.causal, k_off=me * L, dk=dkv[0], dv=dkv[1],
+                     hq=self.hq)
+        return dq, dkv
 
     def check(self) -> None:
         """Synchronise and raise if a device-side wait timed out."""

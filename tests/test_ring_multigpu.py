@@ -16,7 +16,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret):
+def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=False):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
@@ -29,14 +29,19 @@ def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret):
     from tests.helpers import seeded_qkv, shard_inputs
 
     init_p2p(device=torch.device("cuda", rank))
-    q, k, v, _ = seeded_qkv(1234, B, S, H, hkv, 128)
+    q, k, v, do = seeded_qkv(1234, B, S, H, hkv, 128)
     qs, kvs = shard_inputs(q, k, v, world)
     op = RingAttention(mesh_shape, B, S // world, H, hkv, 128, causal=causal)
     lq, lkv = qs[rank].cuda(), kvs[rank].cuda()
+    ldo = do.chunk(world, 1)[rank].contiguous().cuda()
     outs = []
     for it in range(3):  # three epochs: exercises slot reuse and the done/ready flags
         o, lse = op.forward(lq, lkv)
-        outs.append((o.float().cpu(), lse.cpu()))
+        if with_bwd:
+            dq, dkv = op.backward(ldo, lq, lkv, o, lse)
+            outs.append((o.float().cpu(), lse.cpu(), dq.float().cpu(), dkv.float().cpu()))
+        else:
+            outs.append((o.float().cpu(), lse.cpu()))
     op.check()
     ret[rank] = outs
     dist.barrier()
@@ -78,3 +83,27 @@ def test_double_ring_forward_four_gpus():
         for o, lse in ret[r]:
             assert (o - fo.chunk(world, 1)[r].float()).abs().max().item() <= 2e-2
             assert (lse - fl.chunk(world, 2)[r]).abs().max().item() <= 1e-3
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_ring_backward_two_gpus(causal):
+    """Forward + backward of the fused ring on two GPUs against single-device fp32 gradients."""
+    import torch.multiprocessing as mp
+    from oracle import block
+    from tests.helpers import seeded_qkv
+
+    world = min(torch.cuda.device_count(), 2)
+    B, S, H, hkv = 1, 2048, 4, 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, True), nprocs=world, join=True)
+    q, k, v, do = seeded_qkv(1234, B, S, H, hkv, 128)
+    scale = 128 ** -0.5
+    fo, fl = block.full_attention(q, k, v, scale, causal=causal)
+    gq, gk, gv = block.block_attn_bwd(do, q, k, v, fo, fl, scale, causal=causal, q_off=0, k_off=0)
+    for r in range(world):
+        for o, lse, dq, dkv in ret[r]:
+            assert (o - fo.chunk(world, 1)[r].float()).abs().max().item() <= 2e-2
+            assert (dq - gq.chunk(world, 1)[r]).abs().max().item() <= 2e-2
+            assert (dkv[0] - gk.chunk(world, 1)[r]).abs().max().item() <= 2e-2
+            assert (dkv[1] - gv.chunk(world, 1)[r]).abs().max().item() <= 2e-2

@@ -33,6 +33,7 @@ extern "C" {
 #define MB_E_CUDA (-3)        /* a CUDA runtime call failed */
 #define MB_E_TENSORMAP (-4)   /* a TMA descriptor could not be encoded (alignment/stride) */
 #define MB_E_DEVICE (-5)      /* the status word reported a device-side timeout */
+#define MB_E_TOO_LARGE (-6)   /* problem exceeds the fixed scratch of an allocation-free entry point */
 
 #define MB_MAX_SEGMENTS 8
 
@@ -145,6 +146,48 @@ typedef struct mb_attn_bwd_args {
  * and, with one segment per rank, the whole generated backward loop including its fp32
  * accumulation and the rotating dK/dV buffer (mercury/backend/pytorch/codegen.py:99-190). */
 MB_API int mb_attn_bwd(const mb_attn_bwd_args* args, void* cuda_stream);
+
+typedef struct mb_attn_bwd_block_args {
+  const void* dout; /* [batch, sq, hq, head_dim] bf16; dout and out use q's strides */
+  const void* q;
+  const void* out;
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  const void* k; /* [batch, sk, hkv, head_dim] bf16 */
+  const void* v;
+  int64_t kv_stride_b, kv_stride_s, kv_stride_h;
+  const float* lse; /* [batch, hq, sq] fp32, final log-sum-exp of the query rows */
+  void* dq;         /* like q, written */
+  int64_t dq_stride_b, dq_stride_s, dq_stride_h;
+  void* dk; /* like k, written; dk and dv share strides */
+  void* dv;
+  int64_t dkv_stride_b, dkv_stride_s, dkv_stride_h;
+  int32_t batch, sq, sk, hq, hkv, head_dim;
+  int32_t q_off, k_off; /* global positions of query row 0 / key 0 (causal rule) */
+  int32_t causal;
+  int32_t out_mode; /* MB_OUT_BF16 or MB_OUT_F32 */
+  float softmax_scale;
+  int32_t* status;
+} mb_attn_bwd_block_args;
+
+/* Block backward (dq, dk, dv of one query shard against one K/V shard) that performs no
+ * allocation of any kind.  It has no counterpart in the reference.
+ *
+ * Who needs it: callers that are not allowed to obtain device memory at the point where they
+ * run the backward -- code executing under a memory pool that is already fully planned, inside
+ * a framework's allocator callback, or in a serving process whose memory budget is fixed at
+ * start-up -- and that therefore cannot provide the per-row statistics workspace
+ * (2 x batch x hq x pad64(sq) floats) that mb_attn_bwd_preprocess / mb_attn_bwd expect from
+ * the caller.  Here that workspace is a fixed 8 MiB array inside the library, resident on every
+ * GPU that loads it until the process exits.
+ *
+ * Limit: batch * hq * pad64(sq) <= 1 048 576 rows (for example batch 1, 32 heads, 32 768 query
+ * rows); anything larger is refused with MB_E_TOO_LARGE and nothing is launched.
+ * The first call on a device looks up the array's device address and sets kernel attributes;
+ * make that first call before any stream capture begins.  Every call uses the same array and
+ * overwrites all of the part it needs (nothing has to be cleared beforehand), so two calls whose
+ * kernels overlap on the GPU -- different streams, or different host threads -- race on it;
+ * calls queued on one stream are safe.  Inputs and outputs are the caller's, as elsewhere. */
+MB_API int mb_attn_bwd_block_noalloc(const mb_attn_bwd_block_args* args, void* cuda_stream);
 
 #define MB_DTYPE_BF16 0
 #define MB_DTYPE_F32 1

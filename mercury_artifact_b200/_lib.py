@@ -18,6 +18,7 @@ ERROR_NAMES = {
     -3: "MB_E_CUDA (a CUDA runtime call failed)",
     -4: "MB_E_TENSORMAP (TMA descriptor rejected: check 16-byte alignment of pointers and strides)",
     -5: "MB_E_DEVICE (device-side wait timed out)",
+    -6: "MB_E_TOO_LARGE (exceeds the fixed scratch of the allocation-free entry point: batch*hq*pad64(sq) > 1048576)",
 }
 
 STATUS_NAMES = {
@@ -172,6 +173,44 @@ class AttnBwdArgs(C.Structure):
     ]
 
 
+class AttnBwdBlockArgs(C.Structure):
+    _fields_ = [
+        ("dout", C.c_void_p),
+        ("q", C.c_void_p),
+        ("out", C.c_void_p),
+        ("q_stride_b", C.c_int64),
+        ("q_stride_s", C.c_int64),
+        ("q_stride_h", C.c_int64),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("kv_stride_b", C.c_int64),
+        ("kv_stride_s", C.c_int64),
+        ("kv_stride_h", C.c_int64),
+        ("lse", C.c_void_p),
+        ("dq", C.c_void_p),
+        ("dq_stride_b", C.c_int64),
+        ("dq_stride_s", C.c_int64),
+        ("dq_stride_h", C.c_int64),
+        ("dk", C.c_void_p),
+        ("dv", C.c_void_p),
+        ("dkv_stride_b", C.c_int64),
+        ("dkv_stride_s", C.c_int64),
+        ("dkv_stride_h", C.c_int64),
+        ("batch", C.c_int32),
+        ("sq", C.c_int32),
+        ("sk", C.c_int32),
+        ("hq", C.c_int32),
+        ("hkv", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("q_off", C.c_int32),
+        ("k_off", C.c_int32),
+        ("causal", C.c_int32),
+        ("out_mode", C.c_int32),
+        ("softmax_scale", C.c_float),
+        ("status", C.c_void_p),
+    ]
+
+
 LIB_PATH = Path(__file__).resolve().parent / "libmercury_b200.so"
 
 
@@ -179,40 +218,57 @@ class MercuryB200Error(RuntimeError):
     pass
 
 
+_SIGNATURES = {
+    "mb_version": [],
+    "mb_attn_fwd": [C.POINTER(AttnFwdArgs), C.c_void_p],
+    "mb_attn_bwd_preprocess": [C.POINTER(BwdPreprocessArgs), C.c_void_p],
+    "mb_attn_bwd": [C.POINTER(AttnBwdArgs), C.c_void_p],
+    "mb_attn_bwd_block_noalloc": [C.POINTER(AttnBwdBlockArgs), C.c_void_p],
+    "mb_merge_out_lse": [C.POINTER(MergeArgs), C.c_void_p],
+    "mb_mem_alloc": [C.POINTER(C.c_void_p), C.c_uint64],
+    "mb_mem_free": [C.c_void_p],
+    "mb_mem_zero": [C.c_void_p, C.c_uint64, C.c_void_p],
+    "mb_ipc_export": [C.c_void_p, C.POINTER(C.c_ubyte)],
+    "mb_ipc_import": [C.POINTER(C.c_ubyte), C.POINTER(C.c_void_p)],
+    "mb_ipc_release": [C.c_void_p],
+    "mb_copy_async": [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p],
+    "mb_flag_signal": [C.c_void_p, C.c_int32, C.c_void_p],
+    "mb_flag_wait": [C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p],
+    "mb_status_fetch": [C.POINTER(C.c_int32), C.c_void_p],
+}
+
+
+def _bind(path: Path) -> C.CDLL:
+    handle = C.CDLL(str(path))
+    try:
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError: the shared object predates this binding
+            fn.restype = C.c_int
+            fn.argtypes = argtypes
+    except AttributeError:
+        import _ctypes
+
+        _ctypes.dlclose(handle._handle)  # otherwise a rebuilt file at the same path maps to the old image
+        raise
+    return handle
+
+
 def _load() -> C.CDLL:
-    if not LIB_PATH.exists():
-        raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m mercury_artifact_b200.build` "
-            "(there is no fallback path)"
-        )
-    lib = C.CDLL(str(LIB_PATH))
-    lib.mb_version.restype = C.c_int
-    lib.mb_version.argtypes = []
-    lib.mb_attn_fwd.restype = C.c_int
-    lib.mb_attn_fwd.argtypes = [C.POINTER(AttnFwdArgs), C.c_void_p]
-    lib.mb_attn_bwd_preprocess.restype = C.c_int
-    lib.mb_attn_bwd_preprocess.argtypes = [C.POINTER(BwdPreprocessArgs), C.c_void_p]
-    lib.mb_attn_bwd.restype = C.c_int
-    lib.mb_attn_bwd.argtypes = [C.POINTER(AttnBwdArgs), C.c_void_p]
-    lib.mb_merge_out_lse.restype = C.c_int
-    lib.mb_merge_out_lse.argtypes = [C.POINTER(MergeArgs), C.c_void_p]
-    for name, argtypes in {
-        "mb_mem_alloc": [C.POINTER(C.c_void_p), C.c_uint64],
-        "mb_mem_free": [C.c_void_p],
-        "mb_mem_zero": [C.c_void_p, C.c_uint64, C.c_void_p],
-        "mb_ipc_export": [C.c_void_p, C.POINTER(C.c_ubyte)],
-        "mb_ipc_import": [C.POINTER(C.c_ubyte), C.POINTER(C.c_void_p)],
-        "mb_ipc_release": [C.c_void_p],
-        "mb_copy_async": [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p],
-        "mb_flag_signal": [C.c_void_p, C.c_int32, C.c_void_p],
-        "mb_flag_wait": [C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p],
-    }.items():
-        fn = getattr(lib, name)
-        fn.restype = C.c_int
-        fn.argtypes = argtypes
-    lib.mb_status_fetch.restype = C.c_int
-    lib.mb_status_fetch.argtypes = [C.POINTER(C.c_int32), C.c_void_p]
-    return lib
+    """Load libmercury_b200.so; if it is missing or older than this binding, rebuild it once
+    with nvcc.  There is no other path: without the library the import fails."""
+    from . import build as _build
+
+    try:
+        if LIB_PATH.exists():
+            return _bind(LIB_PATH)
+        reason = f"{LIB_PATH} is missing"
+    except AttributeError as e:
+        reason = f"{LIB_PATH} is stale ({e})"
+    if _build.find_nvcc() is None:
+        raise ImportError(f"{reason} and nvcc is not available to build it "
+                          "(python -m mercury_artifact_b200.build); there is no fallback path")
+    _build.build(force=True)
+    return _bind(LIB_PATH)
 
 
 lib = _load()

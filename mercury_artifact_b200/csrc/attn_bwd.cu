@@ -605,4 +605,97 @@ int launch_attn_bwd(const mb_attn_bwd_args* x, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
 }
 
+// ---------------------------------------------------------------------------
+// allocation-free block backward
+// ---------------------------------------------------------------------------
+// Row statistics (lse2, delta) for the allocation-free entry point live in this fixed array
+// instead of caller-provided memory: 2 x 1 Mi floats = 8 MiB, held by every GPU that loads
+// the library until the process exits.
+constexpr long long kStaticStatRows = 1ll << 20;  // batch * hq * pad64(sq) must not exceed this
+static __device__ __align__(256) float g_bwd_static_stats[2 * kStaticStatRows];
+
+// Host code cannot use the array's name as an address (it is only a stand-in on the host side):
+// look the device address up once per device, with that device current.
+static float* static_stats_address(int* rc) {
+  static float* cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *rc = MB_E_CUDA;
+    return nullptr;
+  }
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_bwd_static_stats) != cudaSuccess || p == nullptr) {
+      *rc = MB_E_CUDA;
+      return nullptr;
+    }
+    cached[dev] = static_cast<float*>(p);
+  }
+  *rc = MB_SUCCESS;
+  return cached[dev];
+}
+
+int launch_bwd_block_noalloc(const mb_attn_bwd_block_args* x, cudaStream_t stream) {
+  if (x == nullptr) return MB_E_INVALID;
+  if (x->head_dim != kBD) return MB_E_UNSUPPORTED;
+  if (x->batch <= 0 || x->hq <= 0 || x->hkv <= 0 || x->hq % x->hkv != 0 || x->sq < 0 || x->sk < 0) return MB_E_INVALID;
+  if (x->out_mode != MB_OUT_BF16 && x->out_mode != MB_OUT_F32) return MB_E_INVALID;
+  if (x->dout == nullptr || x->q == nullptr || x->k == nullptr || x->v == nullptr || x->out == nullptr ||
+      x->lse == nullptr || x->dq == nullptr || x->dk == nullptr || x->dv == nullptr)
+    return MB_E_INVALID;
+  const long long pad = (x->sq + kStrRows - 1) / kStrRows * (long long)kStrRows;
+  const long long rows = (long long)x->batch * x->hq * (pad > 0 ? pad : kStrRows);
+  if (rows > kStaticStatRows) return MB_E_TOO_LARGE;
+  if (x->sq == 0 && x->sk == 0) return MB_SUCCESS;
+  int rc = MB_SUCCESS;
+  float* stats = static_stats_address(&rc);
+  if (stats == nullptr) return rc;
+  const int stat_pad = static_cast<int>(pad > 0 ? pad : kStrRows);
+  float* lse2 = stats;
+  float* delta = stats + kStaticStatRows;
+
+  if (x->sq > 0) {
+    mb_bwd_preprocess_args p;
+    memset(&p, 0, sizeof(p));
+    p.dout = x->dout; p.dout_stride_b = x->q_stride_b; p.dout_stride_s = x->q_stride_s; p.dout_stride_h = x->q_stride_h;
+    p.out = x->out; p.out_stride_b = x->q_stride_b; p.out_stride_s = x->q_stride_s; p.out_stride_h = x->q_stride_h;
+    p.lse = x->lse; p.lse2 = lse2; p.delta = delta;
+    p.batch = x->batch; p.sq = x->sq; p.hq = x->hq; p.head_dim = x->head_dim; p.stat_pad = stat_pad;
+    rc = launch_bwd_preprocess(&p, stream);
+    if (rc != MB_SUCCESS) return rc;
+  }
+
+  mb_attn_bwd_args a;
+  memset(&a, 0, sizeof(a));
+  a.batch = x->batch; a.hq = x->hq; a.hkv = x->hkv; a.head_dim = x->head_dim;
+  a.causal = x->causal; a.softmax_scale = x->softmax_scale; a.out_mode = x->out_mode; a.status = x->status;
+  // dQ: owner = q/dout, stream = k/v
+  a.mode = MB_BWD_MODE_DQ;
+  a.own = x->q; a.own_g = x->dout;
+  a.own_stride_b = x->q_stride_b; a.own_stride_s = x->q_stride_s; a.own_stride_h = x->q_stride_h;
+  a.own_lse2 = lse2; a.own_delta = delta; a.own_stat_pad = stat_pad;
+  a.own_rows = x->sq; a.own_off = x->q_off;
+  a.out1 = x->dq; a.out2 = nullptr;
+  a.out_stride_b = x->dq_stride_b; a.out_stride_s = x->dq_stride_s; a.out_stride_h = x->dq_stride_h;
+  a.nseg = 1;
+  a.seg[0].str = x->k; a.seg[0].str_g = x->v;
+  a.seg[0].stride_b = x->kv_stride_b; a.seg[0].stride_s = x->kv_stride_s; a.seg[0].stride_h = x->kv_stride_h;
+  a.seg[0].rows = x->sk; a.seg[0].pos_off = x->k_off;
+  rc = launch_attn_bwd(&a, stream);
+  if (rc != MB_SUCCESS) return rc;
+  // dK/dV: owner = k/v, stream = q/dout with the statistics just computed
+  a.mode = MB_BWD_MODE_DKV;
+  a.own = x->k; a.own_g = x->v;
+  a.own_stride_b = x->kv_stride_b; a.own_stride_s = x->kv_stride_s; a.own_stride_h = x->kv_stride_h;
+  a.own_lse2 = nullptr; a.own_delta = nullptr; a.own_stat_pad = 0;
+  a.own_rows = x->sk; a.own_off = x->k_off;
+  a.out1 = x->dk; a.out2 = x->dv;
+  a.out_stride_b = x->dkv_stride_b; a.out_stride_s = x->dkv_stride_s; a.out_stride_h = x->dkv_stride_h;
+  a.seg[0].str = x->q; a.seg[0].str_g = x->dout;
+  a.seg[0].stride_b = x->q_stride_b; a.seg[0].stride_s = x->q_stride_s; a.seg[0].stride_h = x->q_stride_h;
+  a.seg[0].rows = x->sq; a.seg[0].pos_off = x->q_off;
+  a.seg[0].lse2 = lse2; a.seg[0].delta = delta; a.seg[0].stat_pad = stat_pad;
+  return launch_attn_bwd(&a, stream);
+}
+
 }  // namespace mb

@@ -55,6 +55,10 @@ int mb_attn_bwd(const mb_attn_bwd_args* args, void* cuda_stream) {
   return mb::launch_attn_bwd(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int mb_attn_bwd_block_noalloc(const mb_attn_bwd_block_args* args, void* cuda_stream) {
+  return mb::launch_bwd_block_noalloc(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int mb_merge_out_lse(const mb_merge_args* args, void* cuda_stream) {
   return mb::launch_merge(args, static_cast<cudaStream_t>(cuda_stream));
 }

@@ -107,3 +107,60 @@ def test_ring_backward_two_gpus(causal):
             assert (dq - gq.chunk(world, 1)[r]).abs().max().item() <= 2e-2
             assert (dkv[0] - gk.chunk(world, 1)[r]).abs().max().item() <= 2e-2
             assert (dkv[1] - gv.chunk(world, 1)[r]).abs().max().item() <= 2e-2
+
+
+def _generated_worker(rank, world, port, ret):
+    """The reference-emitted per-step programs with the real peer transport (SendRecv over NVLink)."""
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200.comm import init_p2p
+    from tests.helpers import golden_text, seeded_qkv, shard_inputs
+
+    ctx = init_p2p(device=torch.device("cuda", rank))
+    mb.install_backend(force_stub=True)  # mercury.backend.SendRecv -> the peer-memory transport
+    B, S, H = 1, 1024, 4
+    q, k, v, do = seeded_qkv(1234, B, S, H, H, 128)
+    qs, kvs = shard_inputs(q, k, v, world)
+    lq, lkv = qs[rank].cuda(), kvs[rank].cuda()
+    scale = 128 ** -0.5
+    fwd = mb.load_generated(golden_text("gpu_ring_p2"))["flash_attn_pack_kv"]
+    bwd = mb.load_generated(golden_text("gpu_bwd_p2"))["flash_attn_backward"]
+    outs = []
+    for _ in range(2):
+        o = torch.zeros_like(lq)
+        lse = torch.zeros(B, H, S // world, device="cuda")
+        fwd(lq, lkv, o, lse, scale)
+        dq, dkv = torch.zeros_like(lq), torch.zeros_like(lkv)
+        bwd(lq, lkv, o, lse, do.chunk(world, 1)[rank].contiguous().cuda(), dq, dkv, scale)
+        outs.append((o.float().cpu(), lse.cpu(), dq.float().cpu(), dkv.float().cpu()))
+    ctx.check()
+    ret[rank] = outs
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_generated_programs_with_peer_transport_two_gpus():
+    import torch.multiprocessing as mp
+    from oracle import block
+    from tests.helpers import seeded_qkv
+
+    world, B, S, H = 2, 1, 1024, 4
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_generated_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    q, k, v, do = seeded_qkv(1234, B, S, H, H, 128)
+    scale = 128 ** -0.5
+    fo, fl = block.full_attention(q, k, v, scale)
+    gq, gk, gv = block.block_attn_bwd(do, q, k, v, fo, fl, scale, causal=False)
+    for r in range(world):
+        for o, lse, dq, dkv in ret[r]:
+            assert (o - fo.chunk(world, 1)[r].float()).abs().max().item() <= 2e-2
+            assert (lse - fl.chunk(world, 2)[r]).abs().max().item() <= 1e-3
+            assert (dq - gq.chunk(world, 1)[r]).abs().max().item() <= 2e-2
+            assert (dkv[0] - gk.chunk(world, 1)[r]).abs().max().item() <= 2e-2
+            assert (dkv[1] - gv.chunk(world, 1)[r]).abs().max().item() <= 2e-2

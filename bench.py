@@ -153,7 +153,7 @@ def run_reference(args):
     vals, times = [], []
     cores, desc = 0, ""
     for i in range(args.warmup + args.steps):
-        tf, cores, desc, t = cpu_leg(args.workload, args.gpus, budget_s=6.0)
+        tf, cores, desc, t = cpu_leg(args.workload, args.gpus, budget_s=float(os.environ.get("MB_CPU_BUDGET_S", "6")))
         if i >= args.warmup:
             vals.append(tf)
             times.append(t)

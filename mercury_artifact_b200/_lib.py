@@ -211,7 +211,10 @@ class AttnBwdBlockArgs(C.Structure):
     ]
 
 
-LIB_PATH = Path(__file__).resolve().parent / "libmercury_b200.so"
+import os as _os
+
+# MERCURY_B200_LIB selects another build of the same library (kernel tuning experiments).
+LIB_PATH = Path(_os.environ.get("MERCURY_B200_LIB") or (Path(__file__).resolve().parent / "libmercury_b200.so"))
 
 
 class MercuryB200Error(RuntimeError):

@@ -13,9 +13,11 @@
 // Roles inside the CTA (384 threads, three warpgroups):
 //   warps 0-3  softmax + epilogue for query tile 0 (one thread per row)
 //   warps 4-7  softmax + epilogue for query tile 1
-//   warp  8    tcgen05.mma issuer (lane 0) and tensor-memory owner
+//   warp  8    tcgen05.mma issuer for query tile 0 (lane 0) and tensor-memory owner
 //   warp  9    TMA loader (lane 0)
-//   warps 10-11 idle; their registers go to the softmax warps (setmaxnreg)
+//   warp 10    tcgen05.mma issuer for query tile 1 (lane 0); one issuing thread for both tiles
+//              cannot feed the tensor pipe (measured ~95 cycles per MMA instruction issued)
+//   warp 11    idle; the auxiliary warpgroup's registers go to the softmax warps (setmaxnreg)
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  The
 // bf16 probabilities overwrite the first 64 columns of their score tile and are
 // consumed from tensor memory as the A operand of the P.V product.
@@ -32,6 +34,30 @@ constexpr int kHalfBytes = kTileBytes / 2;
 constexpr int kFwdStages = 4;
 constexpr int kFwdThreads = 384;  // 8 softmax warps + one auxiliary warpgroup (MMA, loader, 2 idle)
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: tolerate p up to 2^8
+#ifndef MB_POLY_EVERY
+#define MB_POLY_EVERY 2
+#endif
+constexpr int kPolyEvery = MB_POLY_EVERY;
+#ifndef MB_TAKE_TURNS
+#define MB_TAKE_TURNS 1
+#endif
+constexpr bool kTakeTurns = MB_TAKE_TURNS != 0;  // every n-th pair of exponentials goes to the FMA pipe (0: none)
+
+// Optional timeline capture for kernel tuning (compiled in only with -DMB_TRACE): CTA (0,0,0)
+// records clock64() at fixed points of the first kTraceIters K/V iterations.
+#ifdef MB_TRACE
+constexpr int kTraceIters = 24;
+__device__ long long g_fwd_trace[3][kTraceIters][12];
+#define MB_TRACE_AT(role, it, ev)                                                              \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < kTraceIters)           \
+      g_fwd_trace[role][it][ev] = clock64();                                                   \
+  } while (0)
+#else
+#define MB_TRACE_AT(role, it, ev) \
+  do {                            \
+  } while (0)
+#endif
 
 struct FwdMaps {
   CUtensorMap q;
@@ -61,8 +87,9 @@ struct FwdSmem {
   uint64_t kv_full[kFwdStages];
   uint64_t kv_empty[kFwdStages];
   uint64_t s_full[2];
-  uint64_t p_full[2];
+  uint64_t p_full[2][2];  // [query tile][half of the keys of a K/V tile]
   uint64_t o_full[2];
+  uint64_t turn[2];  // exp2-phase token passed between the two softmax warpgroups
   uint64_t drain;
   uint32_t tmem_base;
   int abort_word;
@@ -86,23 +113,64 @@ __device__ __forceinline__ int visible_tiles(int q0, int Sq, int q_off, int caus
   return nt;
 }
 
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_saddr, uint32_t k_saddr, uint32_t idesc) {
-#pragma unroll
-  for (int k = 0; k < kD / 16; ++k) {
-    const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-    umma_ss(d_tmem, umma_smem_desc(q_saddr + off, 16, 1024), umma_smem_desc(k_saddr + off, 16, 1024), idesc,
-            k > 0 ? 1u : 0u);
-  }
-}
+// One asm block per group of MMAs keeps the single issuing thread's instruction count low: the
+// shared-memory descriptors of the k-steps differ from the first one only in the start-address
+// field (bits 0-13, in 16-byte units), so each is one 64-bit add away.
 
-__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_saddr, uint32_t idesc,
-                                         bool accumulate) {
-#pragma unroll
-  for (int k = 0; k < kBN / 16; ++k) {
-    // 16 keys per instruction: 16 rows of 128 B in each 64-column half of the V tile.
-    umma_ts(d_tmem, p_tmem + k * 8, umma_smem_desc(v_saddr + k * 2048, kHalfBytes, 1024), idesc,
-            (accumulate || k > 0) ? 1u : 0u);
-  }
+// S = Q K^T for one 128x128 tile: 8 MMAs (K = 16 each) over the two 64-column halves of Q and K.
+// Offsets in 16-byte units: k-step k -> (k >> 2) * (kHalfBytes / 16) + (k & 3) * 2.
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint64_t q_desc, uint64_t k_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pt, pf;\n\t"
+      ".reg .b64 qa, kb;\n\t"
+      "setp.eq.u32 pt, 0, 0;\n\t"
+      "setp.ne.u32 pf, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+      "add.s64 qa, %1, 2;\n\t add.s64 kb, %2, 2;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 4;\n\t add.s64 kb, %2, 4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 6;\n\t add.s64 kb, %2, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 1024;\n\t add.s64 kb, %2, 1024;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 1026;\n\t add.s64 kb, %2, 1026;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 1028;\n\t add.s64 kb, %2, 1028;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 1030;\n\t add.s64 kb, %2, 1030;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "l"(q_desc), "l"(k_desc), "r"(idesc)
+      : "memory");
+}
+static_assert(kHalfBytes / 16 == 1024, "issue_qk hard-codes the half-tile pitch");
+
+// O (+)= P V for 64 keys (half of a K/V tile): 4 MMAs of 16 keys.  P comes from tensor memory
+// (8 columns per 16 keys); V is read MN-major, 16 keys = 2048 bytes = 128 descriptor units apart.
+// p_tmem and v_desc already point at the half to process.
+__device__ __forceinline__ void issue_pv_half(uint32_t d_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t idesc,
+                                              uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pt, p0;\n\t"
+      ".reg .b64 vb;\n\t"
+      ".reg .b32 pa;\n\t"
+      "setp.eq.u32 pt, 0, 0;\n\t"
+      "setp.ne.u32 p0, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "add.s64 vb, %2, 128;\n\t add.u32 pa, %1, 8;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
+      "add.s64 vb, %2, 256;\n\t add.u32 pa, %1, 16;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
+      "add.s64 vb, %2, 384;\n\t add.u32 pa, %1, 24;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "r"(p_tmem), "l"(v_desc), "r"(idesc), "r"(accumulate_first)
+      : "memory");
 }
 
 // 160 registers/thread at launch (not the 168 that 384 threads would allow): the few warps' worth
@@ -131,14 +199,16 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     mbar_init(&ctl->q_full, 1);
     for (int s = 0; s < kFwdStages; ++s) {
       mbar_init(&ctl->kv_full[s], 1);
-      mbar_init(&ctl->kv_empty[s], 1);
+      mbar_init(&ctl->kv_empty[s], 2);  // one arrival from each of the two MMA-issuing warps
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ctl->s_full[i], 1);
-      mbar_init(&ctl->p_full[i], 128);
+      mbar_init(&ctl->p_full[i][0], 128);
+      mbar_init(&ctl->p_full[i][1], 128);
       mbar_init(&ctl->o_full[i], 1);
+      mbar_init(&ctl->turn[i], 128);
     }
-    mbar_init(&ctl->drain, 1);
+    mbar_init(&ctl->drain, 2);
     ctl->abort_word = 0;
     for (int i = 0; i < 2; ++i)
       for (int s = 0; s < MB_MAX_SEGMENTS; ++s)
@@ -162,11 +232,11 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
 
   // Registers move from the auxiliary warpgroup (warps 8-11) to the two softmax
   // warpgroups; each role changes its own budget as the first thing it does.
-  if (warp >= 10) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+  if (warp == 11) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
   } else if (warp == 9) {
     // ------------------------------------------------------------------ loader
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
     if (lane == 0 && any_work) {
       tma_prefetch_desc(&maps.q);
       const int act0 = q0 < a.Sq, act1 = q0 + kBM < a.Sq;
@@ -215,83 +285,78 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
         }
       }
     }
-  } else if (warp == 8) {
-    // -------------------------------------------------------------- MMA issuer
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+  } else if (warp == 8 || warp == 10) {
+    // ------------------------------------------- MMA issuers: warp 8 -> query tile 0, warp 10 -> tile 1
+    // Each walks every K/V stage in load order (K0 V0 K1 V1 ...): it waits for the stage, uses it if
+    // its query tile takes part in that K/V tile, and arrives on the stage's "empty" barrier either
+    // way, so the barrier always sees one arrival per issuing warp.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
     if (lane == 0 && any_work) {
+      const int i = (warp - 8) >> 1;
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kBM, kBN, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kBM, kD, false, true);
-      const uint32_t q_saddr = smem_u32(sQ);
-      const uint32_t kv_saddr = smem_u32(sKV);
-      int cntP0 = 0, cntP1 = 0;
-      int n = 0;  // index of the next K/V tile to consume, in load order K0 V0 K1 V1 ...
-
-      // flat iteration over (segment, tile)
-      int s = 0, jt = 0;
-      auto seg_max = [&](int ss) { return max(ctl->n_tiles[0][ss], ctl->n_tiles[1][ss]); };
-      while (s < a.nseg && seg_max(s) == 0) ++s;
-      bool valid = s < a.nseg;
-
+      const uint32_t tSi = tmem + i * 128, tOi = tmem + 256 + i * 128;
+      const uint64_t q_desc = umma_smem_desc(smem_u32(sQ) + i * kTileBytes, 16, 1024);
+      const uint64_t k_desc0 = umma_smem_desc(smem_u32(sKV), 16, 1024);          // K-major view of stage 0
+      const uint64_t v_desc0 = umma_smem_desc(smem_u32(sKV), kHalfBytes, 1024);  // MN-major view of stage 0
+      constexpr uint32_t kStageUnits = kTileBytes / 16;
+      uint64_t* p_full0 = &ctl->p_full[i][0];
+      uint64_t* p_full1 = &ctl->p_full[i][1];
+      int cnt = 0;   // tiles this query tile has taken part in
+      int n = 0;     // next stage index in load order
       bool ok = mbar_wait(&ctl->q_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
-      if (ok && valid) ok = mbar_wait(&ctl->kv_full[0], 0, abort_word, MB_ERR_TIMEOUT_KV_FULL);
-      if (ok && valid) {
-        tc_fence_after();
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          if (jt < ctl->n_tiles[i][s]) {
-            issue_qk(tmem + i * 128, q_saddr + i * kTileBytes, kv_saddr, idesc_qk);
-            umma_commit(&ctl->s_full[i]);
-          }
-        }
-        umma_commit(&ctl->kv_empty[0]);
-        n = 1;
-      }
-      while (valid && ok) {
-        // successor of (s, jt)
-        int s2 = s, jt2 = jt + 1;
-        if (jt2 >= seg_max(s2)) {
-          ++s2;
-          jt2 = 0;
-          while (s2 < a.nseg && seg_max(s2) == 0) ++s2;
-        }
-        const bool valid2 = s2 < a.nseg;
-        const int vstage = n % kFwdStages, vpar = (n / kFwdStages) & 1;
-        const int kstage = (n + 1) % kFwdStages, kpar = ((n + 1) / kFwdStages) & 1;
-        bool v_ready = false, k_ready = false;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          if (!ok) break;
-          int& cntP = i ? cntP1 : cntP0;
-          if (jt < ctl->n_tiles[i][s]) {
-            ok = mbar_wait(&ctl->p_full[i], cntP & 1, abort_word, MB_ERR_TIMEOUT_P);
-            if (ok && !v_ready) {
-              ok = mbar_wait(&ctl->kv_full[vstage], vpar, abort_word, MB_ERR_TIMEOUT_KV_FULL);
-              v_ready = true;
-            }
+      bool first = true;
+      for (int s = 0; s < a.nseg && ok; ++s) {
+        const int mine = ctl->n_tiles[i][s];
+        const int nmax = max(ctl->n_tiles[0][s], ctl->n_tiles[1][s]);
+        for (int jt = 0; jt < nmax; ++jt) {
+          const bool part = jt < mine;
+          // ---- K tile of this iteration
+          {
+            const int stage = n % kFwdStages;
+            ok = mbar_wait(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
             if (!ok) break;
-            tc_fence_after();
-            issue_pv(tmem + 256 + i * 128, tmem + i * 128, kv_saddr + vstage * kTileBytes, idesc_pv, cntP > 0);
-            umma_commit(&ctl->o_full[i]);
-            ++cntP;
-          }
-          if (valid2 && jt2 < ctl->n_tiles[i][s2]) {
-            if (!k_ready) {
-              ok = mbar_wait(&ctl->kv_full[kstage], kpar, abort_word, MB_ERR_TIMEOUT_KV_FULL);
-              k_ready = true;
-              if (!ok) break;
+            if (part) {
               tc_fence_after();
+              issue_qk(tSi, q_desc, k_desc0 + stage * kStageUnits, idesc_qk);
+              umma_commit(&ctl->s_full[i]);
+              umma_commit(&ctl->kv_empty[stage]);
+              MB_TRACE_AT(2, cnt, i * 6 + 5);
+            } else {
+              mbar_arrive(&ctl->kv_empty[stage]);
             }
-            issue_qk(tmem + i * 128, q_saddr + i * kTileBytes, kv_saddr + kstage * kTileBytes, idesc_qk);
-            umma_commit(&ctl->s_full[i]);
+            ++n;
+          }
+          // ---- V tile of this iteration
+          {
+            const int stage = n % kFwdStages;
+            ok = mbar_wait(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+            if (!ok) break;
+            if (part) {
+              const uint64_t v_desc = v_desc0 + stage * kStageUnits;
+              MB_TRACE_AT(2, cnt, i * 6 + 0);
+              ok = mbar_wait(p_full0, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+              if (!ok) break;
+              MB_TRACE_AT(2, cnt, i * 6 + 1);
+              tc_fence_after();
+              issue_pv_half(tOi, tSi, v_desc, idesc_pv, first ? 0u : 1u);
+              MB_TRACE_AT(2, cnt, i * 6 + 2);
+              ok = mbar_wait(p_full1, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+              if (!ok) break;
+              MB_TRACE_AT(2, cnt, i * 6 + 3);
+              tc_fence_after();
+              issue_pv_half(tOi, tSi + 32, v_desc + 4 * 128, idesc_pv, 1u);
+              umma_commit(&ctl->o_full[i]);
+              umma_commit(&ctl->kv_empty[stage]);
+              MB_TRACE_AT(2, cnt, i * 6 + 4);
+              first = false;
+              ++cnt;
+            } else {
+              mbar_arrive(&ctl->kv_empty[stage]);
+            }
+            ++n;
           }
         }
-        if (!ok) break;
-        umma_commit(&ctl->kv_empty[vstage]);
-        if (valid2) umma_commit(&ctl->kv_empty[kstage]);
-        n += valid2 ? 2 : 1;
-        s = s2;
-        jt = jt2;
-        valid = valid2;
       }
       if (!ok) {
         // Let tensor-core work already issued finish (bounded) before tensor memory is released.
@@ -303,7 +368,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     }
   } else {
     // ------------------------------------------------------ softmax + epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // All control flow below is warp-uniform (the tensor-memory loads and
     // stores are warp-collective); only global stores are predicated per row.
     const int i = warp >> 2;                    // query tile
@@ -317,15 +382,19 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     float m_ref = -INFINITY;  // reference max (raw score units)
     float l = 0.f;            // running sum of exp2
     int cnt = 0;
+    int shared_cnt = 0;       // K/V tiles both query tiles took part in so far
     bool ok = true;
 
     for (int s = 0; s < a.nseg && ok; ++s) {
       const int nt = ctl->n_tiles[i][s];
+      const int nt_both = min(ctl->n_tiles[0][s], ctl->n_tiles[1][s]);
       const int sk = a.seg_sk[s];
       const int koff = a.seg_koff[s];
       for (int jt = 0; jt < nt; ++jt) {
+        if (row == 0) MB_TRACE_AT(i, cnt, 0);
         ok = mbar_wait_warp(&ctl->s_full[i], cnt & 1, abort_word, MB_ERR_TIMEOUT_S);
         if (!ok) break;
+        if (row == 0) MB_TRACE_AT(i, cnt, 1);
         tc_fence_after();
         uint32_t sr[4][32];
         tmem_ld32(tSi + 0, sr[0]);
@@ -333,6 +402,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
         tmem_ld32(tSi + 64, sr[2]);
         tmem_ld32(tSi + 96, sr[3]);
         tmem_wait_ld();
+        if (row == 0) MB_TRACE_AT(i, cnt, 2);
 
         // masking: only tiles that cross the segment end or the causal diagonal
         const int k0 = jt * kBN;
@@ -350,13 +420,14 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
 
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[0][e]));
-          mx1 = fmaxf(mx1, __uint_as_float(sr[1][e]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[2][e]));
-          mx3 = fmaxf(mx3, __uint_as_float(sr[3][e]));
+        for (int e = 0; e < 32; e += 2) {
+          mx0 = max3(mx0, __uint_as_float(sr[0][e]), __uint_as_float(sr[0][e + 1]));
+          mx1 = max3(mx1, __uint_as_float(sr[1][e]), __uint_as_float(sr[1][e + 1]));
+          mx2 = max3(mx2, __uint_as_float(sr[2][e]), __uint_as_float(sr[2][e + 1]));
+          mx3 = max3(mx3, __uint_as_float(sr[3][e]), __uint_as_float(sr[3][e + 1]));
         }
         const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        if (row == 0) MB_TRACE_AT(i, cnt, 3);
 
         if (cnt == 0) {
           m_ref = m_tile;
@@ -386,8 +457,23 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
           }
         }
 
+        // The two warpgroups take turns in the exp2 phase: the 16-lane MUFU is the scarce unit, and
+        // if both tiles reach this phase together they share it, finish together and then leave it
+        // idle while both wait for the tensor pipe.  Alternating keeps one tile in its MUFU phase
+        // while the other tile's MMAs run.  Only K/V tiles that both query tiles process take part,
+        // so the two warpgroups always agree on the turn count.
+        const bool take_turns = kTakeTurns && jt < nt_both;
+        if (take_turns) {
+          ok = mbar_wait_warp(&ctl->turn[i], (shared_cnt & 1) ^ (i == 0 ? 1 : 0), abort_word, MB_ERR_TIMEOUT_MISC);
+          if (!ok) break;
+        }
+
+        // p = exp2(s * c - m * c): the scale/subtract and the row sum run as packed pairs; every
+        // kPolyEvery-th pair of exponentials is evaluated on the FMA pipe, the rest on the MUFU.
         const float m_scaled = (m_ref == -INFINITY) ? 0.f : m_ref * a.scale_log2;
-        float sum0 = 0.f, sum1 = 0.f;
+        const uint64_t c2 = pack2(a.scale_log2, a.scale_log2);
+        const uint64_t nm2 = pack2(-m_scaled, -m_scaled);
+        uint64_t sum_a = pack2(0.f, 0.f), sum_b = pack2(0.f, 0.f);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t pk[32];
@@ -396,19 +482,37 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
             const int c = half * 2 + cc;
 #pragma unroll
             for (int e = 0; e < 32; e += 2) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][e]), a.scale_log2, -m_scaled));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][e + 1]), a.scale_log2, -m_scaled));
-              sum0 += p0;
-              sum1 += p1;
+              const uint64_t x2 = fma2(pack2(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1])), c2, nm2);
+              uint64_t p2;
+              if (kPolyEvery > 0 && ((e >> 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) {
+                p2 = exp2_poly2(x2);
+              } else {
+                float x0, x1;
+                unpack2(x2, x0, x1);
+                p2 = pack2(fast_exp2(x0), fast_exp2(x1));
+              }
+              if ((e >> 1) & 1) sum_b = add2(sum_b, p2);
+              else sum_a = add2(sum_a, p2);
+              float p0, p1;
+              unpack2(p2, p0, p1);
               pk[cc * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
             }
           }
+          if (half == 1 && take_turns) {
+            mbar_arrive(&ctl->turn[i ^ 1]);  // my exponentials are issued: the other warpgroup's turn
+            ++shared_cnt;
+          }
           tmem_st32(tSi + half * 32, pk);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&ctl->p_full[i][half]);
+          if (row == 0) MB_TRACE_AT(i, cnt, 4 + half);
         }
-        l += sum0 + sum1;
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&ctl->p_full[i]);
+        {
+          float s0, s1;
+          unpack2(add2(sum_a, sum_b), s0, s1);
+          l += s0 + s1;
+        }
         ++cnt;
       }
     }
@@ -541,3 +645,9 @@ int launch_attn_fwd(const mb_attn_fwd_args* x, cudaStream_t stream) {
 }
 
 }  // namespace mb
+
+#ifdef MB_TRACE
+extern "C" __attribute__((visibility("default"))) int mb_debug_fetch_fwd_trace(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, mb::g_fwd_trace, sizeof(mb::g_fwd_trace)) == cudaSuccess ? 0 : -3;
+}
+#endif

@@ -1,0 +1,88 @@
+"""world_size-2 runs on CPU/gloo: the oracle's per-rank ring, the reference arm of bench.py,
+and the rank-dependent host logic of the fused ring (schedules, causal pull sets)."""
+import json
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_worker(rank, world, port, name, ret):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    from oracle import ring
+    from tests.helpers import load_golden, shard_inputs
+
+    g = load_golden(name)
+    qs, kvs = shard_inputs(g["t"]["q"], g["t"]["k"], g["t"]["v"], world)
+    o, lse = ring.rank_ring_fwd(qs[rank], kvs[rank], g["D"] ** -0.5, g["mesh"])
+    ret[rank] = (o, lse)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name", ["ring_p2", "gqa_p2"])
+def test_oracle_rank_ring_over_gloo_matches_reference_vectors(name):
+    import torch.multiprocessing as mp
+    from tests.helpers import load_golden
+
+    g = load_golden(name)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rank_worker, args=(g["world"], _free_port(), name, ret), nprocs=g["world"], join=True)
+    for r in range(g["world"]):
+        assert torch.allclose(ret[r][0], g["t"][f"o_rank{r}"], atol=2e-6)
+        assert torch.allclose(ret[r][1], g["t"][f"lse_rank{r}"], atol=2e-6)
+
+
+def test_bench_reference_arm_under_two_ranks():
+    """`bench.py --impl reference --gpus 2` as the driver launches it: rank 0 prints one JSON line,
+    the other rank exits 0 silently."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE="2", MB_CPU_BUDGET_S="1")
+    outs = []
+    for rank in (0, 1):
+        e = dict(env, RANK=str(rank), LOCAL_RANK=str(rank))
+        outs.append(subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2",
+                                    "--steps", "1", "--warmup", "0"], env=e, capture_output=True, text=True, timeout=600))
+    assert outs[0].returncode == 0 and outs[1].returncode == 0
+    assert outs[1].stdout.strip() == ""
+    line = json.loads(outs[0].stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
+    assert line["unit"] == "TFLOP/s" and line["higher_is_better"] is True
+
+
+def test_causal_pull_sets_cover_exactly_the_visible_shards():
+    """Which shards a rank pulls in the fused ring (forward: keys it can see; backward: also the query
+    shards that can see its keys) -- pure host logic, checked for every rank of 2- and 8-rank rings."""
+    from mercury_artifact_b200 import mesh
+
+    for shape in [(2,), (8,), (4, 2)]:
+        p = 1
+        for n in shape:
+            p *= n
+        for r in range(p):
+            order = mesh.kv_origin_schedule(r, shape)
+            sees = [o for o in order[1:] if o <= r]
+            seen_by = [o for o in order[1:] if o >= r]
+            assert sorted(sees + [r]) == list(range(r + 1))
+            assert sorted(seen_by + [r]) == list(range(r, p))
+            # every unordered pair of ranks exchanges at least one direction under the causal rule
+            assert set(sees) | set(seen_by) == set(range(p)) - {r}

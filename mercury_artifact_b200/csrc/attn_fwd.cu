@@ -35,7 +35,7 @@ constexpr int kFwdStages = 4;
 constexpr int kFwdThreads = 384;  // 8 softmax warps + one auxiliary warpgroup (MMA, loader, 2 idle)
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: tolerate p up to 2^8
 #ifndef MB_POLY_EVERY
-#define MB_POLY_EVERY 2
+#define MB_POLY_EVERY 0
 #endif
 constexpr int kPolyEvery = MB_POLY_EVERY;
 #ifndef MB_TAKE_TURNS
@@ -113,7 +113,9 @@ __device__ __forceinline__ int visible_tiles(int q0, int Sq, int q_off, int caus
   return nt;
 }
 
-// One asm block per group of MMAs keeps the single issuing thread's instruction count low: the
+// Called by a converged warp; one elected lane issues.  Keeping the warp converged lets the
+// descriptor arithmetic run on the uniform datapath (tcgen05.mma takes its descriptors from uniform
+// registers), and one asm block per group of MMAs keeps the instruction count low: the
 // shared-memory descriptors of the k-steps differ from the first one only in the start-address
 // field (bits 0-13, in 16-byte units), so each is one 64-bit add away.
 
@@ -122,25 +124,26 @@ __device__ __forceinline__ int visible_tiles(int q0, int Sq, int q_off, int caus
 __device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint64_t q_desc, uint64_t k_desc, uint32_t idesc) {
   asm volatile(
       "{\n\t"
-      ".reg .pred pt, pf;\n\t"
+      ".reg .pred pe, pt, pf;\n\t"
       ".reg .b64 qa, kb;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
       "setp.eq.u32 pt, 0, 0;\n\t"
       "setp.ne.u32 pf, 0, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
       "add.s64 qa, %1, 2;\n\t add.s64 kb, %2, 2;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
       "add.s64 qa, %1, 4;\n\t add.s64 kb, %2, 4;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
       "add.s64 qa, %1, 6;\n\t add.s64 kb, %2, 6;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
       "add.s64 qa, %1, 1024;\n\t add.s64 kb, %2, 1024;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
       "add.s64 qa, %1, 1026;\n\t add.s64 kb, %2, 1026;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
       "add.s64 qa, %1, 1028;\n\t add.s64 kb, %2, 1028;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
       "add.s64 qa, %1, 1030;\n\t add.s64 kb, %2, 1030;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
       "}"
       :
       : "r"(d_tmem), "l"(q_desc), "l"(k_desc), "r"(idesc)
@@ -155,18 +158,19 @@ __device__ __forceinline__ void issue_pv_half(uint32_t d_tmem, uint32_t p_tmem, 
                                               uint32_t accumulate_first) {
   asm volatile(
       "{\n\t"
-      ".reg .pred pt, p0;\n\t"
+      ".reg .pred pe, pt, p0;\n\t"
       ".reg .b64 vb;\n\t"
       ".reg .b32 pa;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
       "setp.eq.u32 pt, 0, 0;\n\t"
       "setp.ne.u32 p0, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
       "add.s64 vb, %2, 128;\n\t add.u32 pa, %1, 8;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
       "add.s64 vb, %2, 256;\n\t add.u32 pa, %1, 16;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
       "add.s64 vb, %2, 384;\n\t add.u32 pa, %1, 24;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
       "}"
       :
       : "r"(d_tmem), "r"(p_tmem), "l"(v_desc), "r"(idesc), "r"(accumulate_first)
@@ -291,7 +295,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     // its query tile takes part in that K/V tile, and arrives on the stage's "empty" barrier either
     // way, so the barrier always sees one arrival per issuing warp.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
-    if (lane == 0 && any_work) {
+    if (any_work) {  // whole warp, converged
       const int i = (warp - 8) >> 1;
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kBM, kBN, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kBM, kD, false, true);
@@ -304,7 +308,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
       uint64_t* p_full1 = &ctl->p_full[i][1];
       int cnt = 0;   // tiles this query tile has taken part in
       int n = 0;     // next stage index in load order
-      bool ok = mbar_wait(&ctl->q_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
+      bool ok = mbar_wait_warp(&ctl->q_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
       bool first = true;
       for (int s = 0; s < a.nseg && ok; ++s) {
         const int mine = ctl->n_tiles[i][s];
@@ -314,45 +318,45 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
           // ---- K tile of this iteration
           {
             const int stage = n % kFwdStages;
-            ok = mbar_wait(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+            ok = mbar_wait_warp(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
             if (!ok) break;
             if (part) {
               tc_fence_after();
               issue_qk(tSi, q_desc, k_desc0 + stage * kStageUnits, idesc_qk);
-              umma_commit(&ctl->s_full[i]);
-              umma_commit(&ctl->kv_empty[stage]);
+              umma_commit_elect(&ctl->s_full[i]);
+              umma_commit_elect(&ctl->kv_empty[stage]);
               MB_TRACE_AT(2, cnt, i * 6 + 5);
             } else {
-              mbar_arrive(&ctl->kv_empty[stage]);
+              mbar_arrive_elect(&ctl->kv_empty[stage]);
             }
             ++n;
           }
           // ---- V tile of this iteration
           {
             const int stage = n % kFwdStages;
-            ok = mbar_wait(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+            ok = mbar_wait_warp(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
             if (!ok) break;
             if (part) {
               const uint64_t v_desc = v_desc0 + stage * kStageUnits;
               MB_TRACE_AT(2, cnt, i * 6 + 0);
-              ok = mbar_wait(p_full0, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+              ok = mbar_wait_warp(p_full0, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
               if (!ok) break;
               MB_TRACE_AT(2, cnt, i * 6 + 1);
               tc_fence_after();
               issue_pv_half(tOi, tSi, v_desc, idesc_pv, first ? 0u : 1u);
               MB_TRACE_AT(2, cnt, i * 6 + 2);
-              ok = mbar_wait(p_full1, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+              ok = mbar_wait_warp(p_full1, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
               if (!ok) break;
               MB_TRACE_AT(2, cnt, i * 6 + 3);
               tc_fence_after();
               issue_pv_half(tOi, tSi + 32, v_desc + 4 * 128, idesc_pv, 1u);
-              umma_commit(&ctl->o_full[i]);
-              umma_commit(&ctl->kv_empty[stage]);
+              umma_commit_elect(&ctl->o_full[i]);
+              umma_commit_elect(&ctl->kv_empty[stage]);
               MB_TRACE_AT(2, cnt, i * 6 + 4);
               first = false;
               ++cnt;
             } else {
-              mbar_arrive(&ctl->kv_empty[stage]);
+              mbar_arrive_elect(&ctl->kv_empty[stage]);
             }
             ++n;
           }
@@ -360,10 +364,11 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
       }
       if (!ok) {
         // Let tensor-core work already issued finish (bounded) before tensor memory is released.
-        umma_commit(&ctl->drain);
+        umma_commit_elect(&ctl->drain);
         const long long t0 = clock64();
         while (!mbar_try_wait(&ctl->drain, 0) && clock64() - t0 < kWaitCycleLimit / 16) {
         }
+        __syncwarp();
       }
     }
   } else {

@@ -269,7 +269,7 @@ def run_ours(args):
     # kernel-only duration for the roofline: the attention launch of the slowest rank, timed alone
     # (at N=1 this is the step itself)
     fl_total = flops_fwd(B, S, H, D, causal)
-    if causal:
+    if causal and not getattr(op, "balanced", False):
         # causal-adjusted FLOPs this rank's launch performs (its rows see shards 0..rank)
         fl_rank = 4.0 * B * H * D * (L * L * rank + L * L * 0.5)
     else:
@@ -292,6 +292,7 @@ def run_ours(args):
                 "workload": workload_name(args.workload, world),
                 "l2": "inputs larger than L2: q+k+v %.0f MiB per rank" % (3 * B * L * H * D * 2 / 2 ** 20),
                 "per_gpu_tflops": value / world,
+                "causal_balance": bool(getattr(op, "balanced", False)),
                 "frac_of_bf16_peak_per_gpu": value / world / peak,
             },
             "e2e": {"value": e2e, "unit": "TFLOP/s", "ms_per_step": ms_e2e,

@@ -57,7 +57,8 @@ typedef struct mb_attn_fwd_args {
   int64_t q_stride_b, q_stride_s, q_stride_h;
   void* o; /* [batch, sq, hq, head_dim] bf16, written */
   int64_t o_stride_b, o_stride_s, o_stride_h;
-  float* lse; /* [batch, hq, sq] fp32 contiguous, written: ln sum exp(scale * q.k) */
+  float* lse; /* [batch, hq, sq] fp32, written: ln sum exp(scale * q.k); sq contiguous */
+  int64_t lse_stride_b, lse_stride_h; /* element strides; 0, 0 selects the contiguous layout */
   int32_t batch, sq, hq, hkv, head_dim;
   int32_t q_off;  /* global position of query row 0 (causal rule only) */
   int32_t causal; /* key visible iff k_off + j <= q_off + i */

@@ -60,6 +60,8 @@ class AttnFwdArgs(C.Structure):
         ("o_stride_s", C.c_int64),
         ("o_stride_h", C.c_int64),
         ("lse", C.c_void_p),
+        ("lse_stride_b", C.c_int64),
+        ("lse_stride_h", C.c_int64),
         ("batch", C.c_int32),
         ("sq", C.c_int32),
         ("hq", C.c_int32),

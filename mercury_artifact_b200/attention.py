@@ -35,8 +35,14 @@ def attn_fwd_segments(
     q_off: int = 0,
     out: Optional[torch.Tensor] = None,
     lse: Optional[torch.Tensor] = None,
+    out_raw: Optional[tuple] = None,
+    lse_raw: Optional[tuple] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """softmax(scale * q k^T) v over the concatenation of `segments`.
+
+    out_raw = (address, stride_b, stride_s, stride_h) and lse_raw = (address, stride_b, stride_h)
+    direct the results to raw device addresses instead of tensors (for example another rank's
+    memory mapped into this process); the function then returns (None, None).
 
     segments: (k, v, k_off) or (k, v, k_off, flag_ptr, flag_value) with k, v of shape
     [batch, sk, hkv, head_dim]; k_off is the global position of the shard's first key and
@@ -49,21 +55,26 @@ def attn_fwd_segments(
     b, sq, hq, d = q.shape
     if len(segments) > _lib.MB_MAX_SEGMENTS:
         raise ValueError(f"at most {_lib.MB_MAX_SEGMENTS} K/V segments per call")
-    if out is None:
-        out = torch.empty_like(q)
-    else:
-        _check_bshd(out, "out")
-    if lse is None:
-        lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
-    elif lse.dtype != torch.float32 or not lse.is_contiguous() or tuple(lse.shape) != (b, hq, sq):
-        raise ValueError("lse must be a contiguous fp32 [batch, hq, sq] tensor")
+    raw = out_raw is not None
+    if raw != (lse_raw is not None):
+        raise ValueError("out_raw and lse_raw go together")
+    if not raw:
+        if out is None:
+            out = torch.empty_like(q)
+        else:
+            _check_bshd(out, "out")
+        if lse is None:
+            lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+        elif lse.dtype != torch.float32 or lse.stride(2) != 1 or tuple(lse.shape) != (b, hq, sq):
+            raise ValueError("lse must be an fp32 [batch, hq, sq] tensor with contiguous rows")
+        out_raw = (out.data_ptr(), out.stride(0), out.stride(1), out.stride(2))
+        lse_raw = (lse.data_ptr(), lse.stride(0), lse.stride(1))
 
     args = _lib.AttnFwdArgs()
     args.q = q.data_ptr()
     args.q_stride_b, args.q_stride_s, args.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
-    args.o = out.data_ptr()
-    args.o_stride_b, args.o_stride_s, args.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
-    args.lse = lse.data_ptr()
+    args.o, args.o_stride_b, args.o_stride_s, args.o_stride_h = out_raw
+    args.lse, args.lse_stride_b, args.lse_stride_h = lse_raw
     args.batch, args.sq, args.hq, args.head_dim = b, sq, hq, d
     args.q_off = int(q_off)
     args.causal = 1 if causal else 0
@@ -94,7 +105,7 @@ def attn_fwd_segments(
     args.hkv = hkv if hkv is not None else hq
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib.mb_attn_fwd(C.byref(args), C.c_void_p(_stream_ptr())), "mb_attn_fwd")
-    return out, lse
+    return (None, None) if raw else (out, lse)
 
 
 # ------------------------------------------------------------------------------------------

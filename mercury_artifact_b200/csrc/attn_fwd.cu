@@ -68,7 +68,8 @@ struct FwdMaps {
 struct FwdArgs {
   __nv_bfloat16* o;
   long long o_sb, o_ss, o_sh;  // element strides
-  float* lse;                  // [B, Hq, Sq]
+  float* lse;                  // [B, Hq, Sq], row-contiguous
+  long long lse_sb, lse_sh;    // element strides of lse
   int B, Sq, Hq, group;
   int nseg;
   int seg_sk[MB_MAX_SEGMENTS];
@@ -559,7 +560,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
         }
         if (store) {
           const float lse = (have && l > 0.f) ? (m_ref * a.scale + __logf(l)) : -INFINITY;
-          a.lse[((long long)b * a.Hq + h) * a.Sq + qrow] = lse;
+          a.lse[(long long)b * a.lse_sb + (long long)h * a.lse_sh + qrow] = lse;
         }
       }
     }
@@ -633,6 +634,8 @@ int launch_attn_fwd(const mb_attn_fwd_args* x, cudaStream_t stream) {
   a.o_ss = x->o_stride_s;
   a.o_sh = x->o_stride_h;
   a.lse = x->lse;
+  a.lse_sh = x->lse_stride_h ? x->lse_stride_h : x->sq;
+  a.lse_sb = x->lse_stride_b ? x->lse_stride_b : (long long)x->hq * x->sq;
   a.B = x->batch;
   a.Sq = x->sq;
   a.Hq = x->hq;

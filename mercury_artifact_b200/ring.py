@@ -56,6 +56,7 @@ class _ShardExchange:
         self.seg_flags = torch.zeros(64, dtype=torch.int32, device=ctx.device)
         self.epoch = 0
         self._next_stage = 0
+        self._stage_of = {}
         torch.cuda.synchronize(ctx.device)
 
     def _ready_ptr(self, on_rank: int, origin: int) -> int:
@@ -73,6 +74,7 @@ class _ShardExchange:
         ctx, comm = self.ctx, self.ctx.comm_stream
         self.epoch += 1
         self._next_stage = 0
+        self._stage_of = {}
         e = self.epoch
         comm.wait_stream(main)
         if e > 2:  # the slot was last used at epoch e-2: every peer has released it by now or soon
@@ -91,22 +93,29 @@ class _ShardExchange:
                 ctx.signal(self._ready_ptr(p, self.rank), self.epoch, comm)
         return ev
 
-    def pull(self, origin: int, ranges: Optional[Sequence[Tuple[int, int]]] = None) -> Tuple[torch.Tensor, int]:
-        """Copy `origin`'s slot of this epoch (or the given (offset, nbytes) ranges of it) into the
-        next staging slot (copy engines over NVLink).  Returns (staging bytes, address of the
-        arrival flag that reaches `epoch` behind the copy)."""
+    def pull(self, origin: int, ranges: Optional[Sequence[Tuple[int, int]]] = None, final: bool = True,
+             raise_flag: bool = True) -> Tuple[torch.Tensor, int]:
+        """Copy `origin`'s slot of this epoch (or the given (offset, nbytes) ranges of it) into that
+        origin's staging slot (copy engines over NVLink).  Returns (staging bytes, address of the
+        arrival flag that reaches `epoch` behind the copy).  final=False keeps the owner's slot
+        reserved for a later pull of the same epoch; raise_flag=False leaves the arrival flag alone
+        (the caller orders its consumers with a stream event instead)."""
         ctx, comm = self.ctx, self.ctx.comm_stream
         e = self.epoch
-        idx = self._next_stage
-        self._next_stage += 1
-        ctx.wait_flag(self._ready_ptr(self.rank, origin), e, comm)
+        if origin not in self._stage_of:
+            self._stage_of[origin] = self._next_stage
+            self._next_stage += 1
+            ctx.wait_flag(self._ready_ptr(self.rank, origin), e, comm)
+        idx = self._stage_of[origin]
         dst = self.staging[idx]
         base = (e % 2) * self.slot_bytes
         for off, nbytes in (ranges if ranges is not None else [(0, self.slot_bytes)]):
             ctx.copy(dst.data_ptr() + off, self.sym.ptr(origin, base + off), nbytes, comm)
         flag_ptr = self.seg_flags.data_ptr() + 4 * idx
-        ctx.signal(flag_ptr, e, comm)
-        ctx.signal(self._done_ptr(origin, self.rank), e, comm)
+        if raise_flag:
+            ctx.signal(flag_ptr, e, comm)
+        if final:
+            ctx.signal(self._done_ptr(origin, self.rank), e, comm)
         return dst, flag_ptr
 
     def release(self, origin: int) -> None:
@@ -131,7 +140,8 @@ class RingAttention:
     """
 
     def __init__(self, mesh_shape: Sequence[int], batch: int, seq_local: int, hq: int, hkv: int,
-                 head_dim: int = 128, causal: bool = False, ctx: Optional[PeerContext] = None):
+                 head_dim: int = 128, causal: bool = False, ctx: Optional[PeerContext] = None,
+                 balance_causal: bool = True):
         self.mesh_shape = tuple(int(n) for n in mesh_shape)
         self.world = 1
         for n in self.mesh_shape:
@@ -151,6 +161,14 @@ class RingAttention:
         self.launches_per_backward = 3
         self._fwd_x: Optional[_ShardExchange] = None
         self._bwd_x: Optional[_ShardExchange] = None
+        self._bal_x: Optional[_ShardExchange] = None
+        self._bal_inbox: Optional[SymmetricBuffer] = None
+        # Causal attention over contiguous shards gives rank r (r + 1/2) blocks of work.  With
+        # balancing, the forward re-assigns query half-shards so that every rank computes the same
+        # amount (see _forward_balanced); inputs and outputs keep the contiguous layout.
+        self.balanced = bool(balance_causal) and self.causal and self.world > 1 and seq_local % 2 == 0
+        if self.balanced:
+            self.launches_per_forward = 2
 
     # ------------------------------------------------------------------ helpers
     def _sees_keys_of(self, origin: int) -> bool:
@@ -177,6 +195,9 @@ class RingAttention:
         if self.world == 1:
             return attn_fwd_segments(q, [(kv[0], kv[1], 0)], softmax_scale, causal=self.causal, q_off=0, out=o, lse=lse)
 
+        if self.balanced:
+            return self._forward_balanced(q, kv, o, lse, softmax_scale)
+
         if self._fwd_x is None:
             self._fwd_x = _ShardExchange(self.ctx, self._kv_bytes())
         x = self._fwd_x
@@ -202,6 +223,113 @@ class RingAttention:
 
         main.wait_event(local_ready)
         return attn_fwd_segments(q, segs, softmax_scale, causal=self.causal, q_off=me * L, out=o, lse=lse)
+
+    # ------------------------------------------------------------------ balanced causal forward
+    def _forward_balanced(self, q, kv, o, lse, softmax_scale):
+        """Causal forward with equal work per rank.
+
+        The sequence is cut into 2P half-shards; rank r computes the queries of half-shards r and
+        2P-1-r (work (r + 1/2) + (2P-1-r + 1/2) = 2P units on every rank).  A rank pulls the query
+        half-shards it computes and the K/V shards they can see, and its kernels write o and lse
+        straight into the owning rank's result inbox through the peer mapping (stores over NVLink);
+        a flag per half tells the owner when its rows are complete.  Layout seen by the caller is
+        unchanged: shard k of q, kv, o, lse lives on rank k.
+        """
+        ctx, P, me, L = self.ctx, self.world, self.rank, self.seq_local
+        Lh = L // 2
+        B, Hq, D = self.batch, self.hq, self.head_dim
+        kv_b = self._kv_bytes()
+        q_b = B * L * Hq * D * 2
+        lse_b = B * Hq * L * 4
+        off_q = _align(kv_b, 256)
+        if self._bal_x is None:
+            self._bal_x = _ShardExchange(ctx, off_q + _align(q_b, 256))
+            self._res_bytes = _align(q_b, 256) + _align(lse_b, 256)
+            self._bal_inbox = SymmetricBuffer(ctx, 2 * self._res_bytes + _FLAG_REGION)
+        x, inbox = self._bal_x, self._bal_inbox
+        main = torch.cuda.current_stream()
+        comm = ctx.comm_stream
+
+        slot = x.begin(main)
+        s_kv, _ = _carve(slot, 0, self.kv_shape, torch.bfloat16)
+        s_q, _ = _carve(slot, off_q, self.q_shape, torch.bfloat16)
+        with torch.cuda.stream(comm):
+            s_kv.copy_(kv, non_blocking=True)
+            s_q.copy_(q, non_blocking=True)
+        local_ready = x.publish()
+        e = x.epoch
+        par = e % 2
+
+        chunks = [2 * P - 1 - me, me]          # heavier half-shard first; its first segment is local
+        max_shard = chunks[0] // 2               # K/V shards 0..max_shard are needed
+        owners = {c: c // 2 for c in chunks}
+
+        def q_ranges(c):
+            half = c % 2
+            row_b = Hq * D * 2
+            return [(off_q + (b * L + half * Lh) * row_b, Lh * row_b) for b in range(B)]
+
+        # 1. the query half-shards first (small), ordered before the kernels by a stream event
+        for c in chunks:
+            if owners[c] != me:
+                x.pull(owners[c], q_ranges(c), final=False, raise_flag=False)
+        q_ready = torch.cuda.Event()
+        q_ready.record(comm)
+        # 2. the K/V shards, staggered so that ranks start on different sources
+        kv_of = {me: (s_kv, None)}
+        for t in range(1, P):
+            origin = (me - t) % P
+            if origin <= max_shard:
+                buf, flag_ptr = x.pull(origin, [(0, kv_b)])
+                rkv, _ = _carve(buf, 0, self.kv_shape, torch.bfloat16)
+                kv_of[origin] = (rkv, flag_ptr)
+            elif origin in x._stage_of:
+                x.release(origin)   # only its queries were needed
+            else:
+                x.release(origin)
+        pull_order = [me] + [(me - t) % P for t in range(1, P)]
+
+        res_o_off = par * self._res_bytes
+        res_l_off = res_o_off + _align(q_b, 256)
+
+        def res_flag(rank, half):
+            return inbox.ptr(rank, 2 * self._res_bytes + 8 * par + 4 * half)
+
+        main.wait_event(local_ready)
+        main.wait_event(q_ready)
+        for c in chunks:
+            owner, half = owners[c], c % 2
+            rows = slice(half * Lh, (half + 1) * Lh)
+            if owner == me:
+                qc = q[:, rows]
+            else:
+                stage = x.staging[x._stage_of[owner]]
+                qc = _carve(stage, off_q, self.q_shape, torch.bfloat16)[0][:, rows]
+            segs = []
+            for origin in pull_order:
+                if origin <= c // 2 and origin in kv_of:
+                    rkv, flag_ptr = kv_of[origin]
+                    segs.append((rkv[0], rkv[1], origin * L) if flag_ptr is None
+                                else (rkv[0], rkv[1], origin * L, flag_ptr, e))
+            # results go straight into the owner's inbox (its memory is mapped here): raw addresses
+            attn_fwd_segments(
+                qc, segs, softmax_scale, causal=True, q_off=c * Lh,
+                out_raw=(inbox.ptr(owner, res_o_off + half * Lh * Hq * D * 2), L * Hq * D, Hq * D, D),
+                lse_raw=(inbox.ptr(owner, res_l_off + half * Lh * 4), Hq * L, L))
+            ctx.signal(res_flag(owner, half), e, main)
+
+        # 3. my own rows: wait for whoever computed them, then hand them to the caller
+        my_o, _ = _carve(inbox.local.bytes(), res_o_off, self.q_shape, torch.bfloat16)
+        my_lse, _ = _carve(inbox.local.bytes(), res_l_off, (B, Hq, L), torch.float32)
+        ctx.wait_flag(res_flag(me, 0), e, main)
+        ctx.wait_flag(res_flag(me, 1), e, main)
+        if o is None:
+            o = torch.empty_like(q)
+        if lse is None:
+            lse = torch.empty((B, Hq, L), dtype=torch.float32, device=q.device)
+        o.copy_(my_o, non_blocking=True)
+        lse.copy_(my_lse, non_blocking=True)
+        return o, lse
 
     # ------------------------------------------------------------------ backward
     def backward(self, dout: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,

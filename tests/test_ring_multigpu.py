@@ -16,7 +16,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=False):
+def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=False, balance=True):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
@@ -31,7 +31,7 @@ def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=F
     init_p2p(device=torch.device("cuda", rank))
     q, k, v, do = seeded_qkv(1234, B, S, H, hkv, 128)
     qs, kvs = shard_inputs(q, k, v, world)
-    op = RingAttention(mesh_shape, B, S // world, H, hkv, 128, causal=causal)
+    op = RingAttention(mesh_shape, B, S // world, H, hkv, 128, causal=causal, balance_causal=balance)
     lq, lkv = qs[rank].cuda(), kvs[rank].cuda()
     ldo = do.chunk(world, 1)[rank].contiguous().cuda()
     outs = []
@@ -48,17 +48,20 @@ def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=F
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("causal", [False, True])
-def test_ring_forward_two_gpus(causal):
+@pytest.mark.parametrize("causal,balance", [(False, True), (True, False), (True, True)])
+def test_ring_forward_two_gpus(causal, balance):
+    """balance=True with causal: query half-shards are re-assigned across ranks and results are
+    written into the owner's memory over NVLink; B=2 exercises the strided half-shard pulls."""
     import torch.multiprocessing as mp
     from oracle import block
     from tests.helpers import seeded_qkv
 
     world = min(torch.cuda.device_count(), 2)
-    B, S, H, hkv = 1, 2048, 4, 2
+    B, S, H, hkv = 2, 2048, 4, 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, False, balance), nprocs=world,
+             join=True)
     q, k, v, _ = seeded_qkv(1234, B, S, H, hkv, 128)
     fo, fl = block.full_attention(q, k, v, 128 ** -0.5, causal=causal)
     for r in range(world):
@@ -164,3 +167,32 @@ def test_generated_programs_with_peer_transport_two_gpus():
             assert (dq - gq.chunk(world, 1)[r]).abs().max().item() <= 2e-2
             assert (dkv[0] - gk.chunk(world, 1)[r]).abs().max().item() <= 2e-2
             assert (dkv[1] - gv.chunk(world, 1)[r]).abs().max().item() <= 2e-2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+@pytest.mark.parametrize("mesh_shape,causal,with_bwd", [((4, 2), False, False), ((8,), True, True)])
+def test_eight_gpus(mesh_shape, causal, with_bwd):
+    """8 ranks: the double ring of BASELINE config 4 (inner ring of 4, two groups) and the causal
+    single ring with balanced forward plus backward."""
+    import torch.multiprocessing as mp
+    from oracle import block
+    from tests.helpers import seeded_qkv
+
+    world, B, S, H, hkv = 8, 1, 4096, 4, 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), mesh_shape, B, S, H, hkv, causal, ret, with_bwd), nprocs=world,
+             join=True)
+    q, k, v, do = seeded_qkv(1234, B, S, H, hkv, 128)
+    scale = 128 ** -0.5
+    fo, fl = block.full_attention(q, k, v, scale, causal=causal)
+    if with_bwd:
+        gq, gk, gv = block.block_attn_bwd(do, q, k, v, fo, fl, scale, causal=causal, q_off=0, k_off=0)
+    for r in range(world):
+        for res in ret[r]:
+            assert (res[0] - fo.chunk(world, 1)[r].float()).abs().max().item() <= 2e-2
+            assert (res[1] - fl.chunk(world, 2)[r]).abs().max().item() <= 1e-3
+            if with_bwd:
+                assert (res[2] - gq.chunk(world, 1)[r]).abs().max().item() <= 2e-2
+                assert (res[3][0] - gk.chunk(world, 1)[r]).abs().max().item() <= 2e-2
+                assert (res[3][1] - gv.chunk(world, 1)[r]).abs().max().item() <= 2e-2

@@ -86,7 +86,7 @@ typedef struct mb_bwd_preprocess_args {
   const void* out; /* forward output, same shape */
   int64_t out_stride_b, out_stride_s, out_stride_h;
   const float* lse; /* [batch, hq, sq] fp32: the FINAL log-sum-exp of these query rows */
-  float* lse2;      /* [batch, hq, stat_pad] fp32, written: lse * log2(e), +inf for rows without keys and padding */
+  float* lse2;      /* [batch, hq, stat_pad] fp32, written: -lse * log2(e); -inf for rows without keys and padding */
   float* delta;     /* [batch, hq, stat_pad] fp32, written: rowsum(dout * out), 0 in the padding */
   int32_t batch, sq, hq, head_dim;
   int32_t stat_pad; /* sq rounded up to a multiple of 64 */

@@ -112,7 +112,7 @@ def attn_fwd_segments(
 # backward
 # ------------------------------------------------------------------------------------------
 class RowStats:
-    """lse2 = lse*log2(e) and delta = rowsum(dout*out) of one query shard, padded to 64 rows."""
+    """lse2 = -lse*log2(e) (stored negated) and delta = rowsum(dout*out) of one query shard, padded to 64 rows."""
 
     def __init__(self, lse2: torch.Tensor, delta: torch.Tensor, rows: int):
         self.lse2, self.delta, self.rows = lse2, delta, rows

@@ -6,15 +6,16 @@
 //
 //   mode dKV: owner = K_j, V_j (128 keys); stream = Q, dO (64 query rows per step)
 //       X = K Q^T = S^T     Y = V dO^T = dP^T          (rows: keys, columns: queries)
-//       P^T = exp2(X*c - lse2[q]),  dS^T = P^T * (Y - delta[q])
+//       P^T = exp2(X*c + lse2[q]),  dS^T = P^T * (Y - delta[q])
 //       dV += P^T dO        dK += dS^T Q
 //   mode dQ:  owner = Q_i, dO_i (128 query rows); stream = K, V (64 keys per step)
 //       X = Q K^T = S       Y = dO V^T = dP
-//       P = exp2(X*c - lse2[q]),    dS = P * (Y - delta[q])
+//       P = exp2(X*c + lse2[q]),    dS = P * (Y - delta[q])
 //       dQ += dS K
 //
-// lse2 = lse * log2(e) (with -inf mapped to +inf so that rows without keys give
-// P = 0) and delta = rowsum(dO * O) come from a small preprocess kernel.  X and Y
+// lse2 is stored NEGATED, -lse * log2(e) (and -inf for rows without keys and for padding, so
+// that P = exp2(X*c + lse2) = 0 there); it and delta = rowsum(dO * O) come from a small
+// preprocess kernel.  X and Y
 // are double-buffered in tensor memory (2 x 2 x 64 columns); the bf16 P and dS
 // overwrite them in place and feed the accumulating MMAs as the tensor-memory A
 // operand; the stream tile in shared memory is read once K-major (for X, Y) and
@@ -119,6 +120,69 @@ __device__ __forceinline__ void step_range(const BwdArgs& a, int own0, int s, in
   if (f > l) f = l;
   *first = f;
   *last = l;
+}
+
+// Groups of MMAs issued from one asm block by a converged warp (one elected lane issues): the
+// descriptors of the k-steps differ only in the start-address field (16-byte units), so each is
+// one 64-bit add away, and a converged warp lets that arithmetic run on the uniform datapath.
+
+// X (or Y) = Own * Stream^T for a 128 x 64 tile: 8 MMAs (K = 16) over the two 64-column halves.
+// Offsets: owner tile half pitch 16 KiB (1024 units), stream tile half pitch 8 KiB (512 units).
+__device__ __forceinline__ void issue_xy_group(uint32_t d_tmem, uint64_t own_desc, uint64_t str_desc,
+                                               uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe, pt, pf;\n\t"
+      ".reg .b64 oa, sb;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.eq.u32 pt, 0, 0;\n\t"
+      "setp.ne.u32 pf, 0, 0;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+      "add.s64 oa, %1, 2;\n\t add.s64 sb, %2, 2;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], oa, sb, %3, pt;\n\t"
+      "add.s64 oa, %1, 4;\n\t add.s64 sb, %2, 4;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], oa, sb, %3, pt;\n\t"
+      "add.s64 oa, %1, 6;\n\t add.s64 sb, %2, 6;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], oa, sb, %3, pt;\n\t"
+      "add.s64 oa, %1, 1024;\n\t add.s64 sb, %2, 512;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], oa, sb, %3, pt;\n\t"
+      "add.s64 oa, %1, 1026;\n\t add.s64 sb, %2, 514;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], oa, sb, %3, pt;\n\t"
+      "add.s64 oa, %1, 1028;\n\t add.s64 sb, %2, 516;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], oa, sb, %3, pt;\n\t"
+      "add.s64 oa, %1, 1030;\n\t add.s64 sb, %2, 518;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], oa, sb, %3, pt;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "l"(own_desc), "l"(str_desc), "r"(idesc)
+      : "memory");
+}
+static_assert(kOwnHalfBytes / 16 == 1024 && kStrHalfBytes / 16 == 512, "issue_xy_group hard-codes the tile pitches");
+
+// Acc (+)= A[tmem] * Stream for the 64 stream rows of a step: 4 MMAs of 16 rows.  The bf16 A
+// operand sits in columns [0,16) (rows 0..31) and [32,48) (rows 32..63) of its 64-column buffer;
+// the stream tile is read MN-major, 16 rows = 2048 bytes = 128 descriptor units apart.
+__device__ __forceinline__ void issue_acc_group(uint32_t d_tmem, uint32_t a_tmem, uint64_t str_desc, uint32_t idesc,
+                                                uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe, pt, p0;\n\t"
+      ".reg .b64 sb;\n\t"
+      ".reg .b32 pa;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.eq.u32 pt, 0, 0;\n\t"
+      "setp.ne.u32 p0, %4, 0;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "add.s64 sb, %2, 128;\n\t add.u32 pa, %1, 8;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], sb, %3, pt;\n\t"
+      "add.s64 sb, %2, 256;\n\t add.u32 pa, %1, 32;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], sb, %3, pt;\n\t"
+      "add.s64 sb, %2, 384;\n\t add.u32 pa, %1, 40;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], sb, %3, pt;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(str_desc), "r"(idesc), "r"(accumulate_first)
+      : "memory");
 }
 
 template <int kDummy>
@@ -226,83 +290,64 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
     }
   } else if (warp == 8) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0 && total_steps > 0) {
+    if (total_steps > 0) {  // whole warp, converged; one elected lane issues
       constexpr uint32_t idesc_xy = umma_idesc_bf16(kOwnRows, kStrRows, false, false);  // 128 x 64, both K-major
       constexpr uint32_t idesc_acc = umma_idesc_bf16(kOwnRows, kBD, false, true);       // 128 x 128, B MN-major
-      const uint32_t own_s = smem_u32(sOwn), own_g_s = smem_u32(sOwnG), stage_s = smem_u32(sStage);
+      const uint64_t own_desc = umma_smem_desc(smem_u32(sOwn), 16, 1024);
+      const uint64_t own_g_desc = umma_smem_desc(smem_u32(sOwnG), 16, 1024);
+      const uint64_t str_k_desc0 = umma_smem_desc(smem_u32(sStage), 16, 1024);             // K-major view, stage 0
+      const uint64_t str_mn_desc0 = umma_smem_desc(smem_u32(sStage), kStrHalfBytes, 1024);  // MN-major view, stage 0
+      constexpr uint32_t kStageUnits = kBwdStageBytes / 16, kStrGUnits = kStrTileBytes / 16;
       const int T = total_steps;
-      bool ok = mbar_wait(&ctl->own_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
+      const bool dkv = a.mode_dkv != 0;
+      bool ok = mbar_wait_warp(&ctl->own_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
 
       auto issue_xy = [&](int t) {
-        const int stage = t % kBwdStages, buf = t & 1;
-        const uint32_t str_s = stage_s + stage * kBwdStageBytes;
-        const uint32_t tx = tmem + 256 + buf * 128, ty = tx + 64;
-#pragma unroll
-        for (int k = 0; k < kBD / 16; ++k) {
-          const uint32_t offo = (k >> 2) * kOwnHalfBytes + (k & 3) * 32;
-          const uint32_t offs = (k >> 2) * kStrHalfBytes + (k & 3) * 32;
-          umma_ss(tx, umma_smem_desc(own_s + offo, 16, 1024), umma_smem_desc(str_s + offs, 16, 1024), idesc_xy,
-                  k > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < kBD / 16; ++k) {
-          const uint32_t offo = (k >> 2) * kOwnHalfBytes + (k & 3) * 32;
-          const uint32_t offs = (k >> 2) * kStrHalfBytes + (k & 3) * 32;
-          umma_ss(ty, umma_smem_desc(own_g_s + offo, 16, 1024),
-                  umma_smem_desc(str_s + kStrTileBytes + offs, 16, 1024), idesc_xy, k > 0 ? 1u : 0u);
-        }
-        umma_commit(&ctl->xy_full[buf]);
+        const uint32_t su = (t % kBwdStages) * kStageUnits;
+        const uint32_t tx = tmem + 256 + (t & 1) * 128;
+        issue_xy_group(tx, own_desc, str_k_desc0 + su, idesc_xy);
+        issue_xy_group(tx + 64, own_g_desc, str_k_desc0 + su + kStrGUnits, idesc_xy);
+        umma_commit_elect(&ctl->xy_full[t & 1]);
       };
       auto issue_acc = [&](int t) {
-        const int stage = t % kBwdStages, buf = t & 1;
-        const uint32_t str_s = stage_s + stage * kBwdStageBytes;
-        const uint32_t tx = tmem + 256 + buf * 128, ty = tx + 64;
-        // dS (overlaying Y) times the stream tile read MN-major: 16 stream rows per instruction.
-        // P/dS columns: rows 0..31 of the step sit in columns [0,16), rows 32..63 in [32,48).
-#pragma unroll
-        for (int k = 0; k < kStrRows / 16; ++k) {
-          const uint32_t acol = (k >> 1) * 32 + (k & 1) * 8;
-          umma_ts(tmem + 0, ty + acol, umma_smem_desc(str_s + k * 2048, kStrHalfBytes, 1024), idesc_acc,
-                  (t > 0 || k > 0) ? 1u : 0u);
-        }
-        if (a.mode_dkv) {
-#pragma unroll
-          for (int k = 0; k < kStrRows / 16; ++k) {
-            const uint32_t acol = (k >> 1) * 32 + (k & 1) * 8;
-            umma_ts(tmem + 128, tx + acol, umma_smem_desc(str_s + kStrTileBytes + k * 2048, kStrHalfBytes, 1024),
-                    idesc_acc, (t > 0 || k > 0) ? 1u : 0u);
-          }
-        }
-        umma_commit(&ctl->str_empty[stage]);
+        const int stage = t % kBwdStages;
+        const uint32_t su = stage * kStageUnits;
+        const uint32_t tx = tmem + 256 + (t & 1) * 128;
+        // dS overlays Y, P overlays X
+        issue_acc_group(tmem + 0, tx + 64, str_mn_desc0 + su, idesc_acc, t > 0 ? 1u : 0u);
+        if (dkv) issue_acc_group(tmem + 128, tx, str_mn_desc0 + su + kStrGUnits, idesc_acc, t > 0 ? 1u : 0u);
+        umma_commit_elect(&ctl->str_empty[stage]);
       };
 
       for (int t = 0; t < 2 && t < T && ok; ++t) {
-        ok = mbar_wait(&ctl->str_full[t % kBwdStages], 0, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+        ok = mbar_wait_warp(&ctl->str_full[t % kBwdStages], 0, abort_word, MB_ERR_TIMEOUT_KV_FULL);
         if (ok) {
           tc_fence_after();
           issue_xy(t);
         }
       }
       for (int t = 0; t < T && ok; ++t) {
-        ok = mbar_wait(&ctl->pd_full[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_P);
+        ok = mbar_wait_warp(&ctl->pd_full[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_P);
         if (!ok) break;
         tc_fence_after();
         issue_acc(t);
         if (t + 2 < T) {
           const int n = t + 2;
-          ok = mbar_wait(&ctl->str_full[n % kBwdStages], (n / kBwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+          ok = mbar_wait_warp(&ctl->str_full[n % kBwdStages], (n / kBwdStages) & 1, abort_word,
+                              MB_ERR_TIMEOUT_KV_FULL);
           if (!ok) break;
           tc_fence_after();
           issue_xy(n);
         }
       }
       if (ok) {
-        umma_commit(&ctl->acc_full);
+        umma_commit_elect(&ctl->acc_full);
       } else {
-        umma_commit(&ctl->drain);
+        umma_commit_elect(&ctl->drain);
         const long long t0 = clock64();
         while (!mbar_try_wait(&ctl->drain, 0) && clock64() - t0 < kWaitCycleLimit / 16) {
         }
+        __syncwarp();
       }
     }
   } else {
@@ -313,12 +358,15 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
     const int own_pos = a.own_off + own0 + row;
     bool ok = true;
 
-    float row_lse2 = 0.f, row_delta = 0.f;
-    if (!a.mode_dkv) {
+    const bool dkv_mode = a.mode_dkv != 0;
+    const uint64_t c2 = pack2(a.scale_log2, a.scale_log2);
+    uint64_t row_nl2 = 0, row_d2 = 0;
+    if (!dkv_mode) {
       const int r = min(own0 + row, a.own_stat_pad - 1);
       const long long soff = ((long long)b * a.Hq + h_own) * a.own_stat_pad + r;
-      row_lse2 = a.own_lse2[soff];
-      row_delta = a.own_delta[soff];
+      const float nl = a.own_lse2[soff], dl = a.own_delta[soff];
+      row_nl2 = pack2(nl, nl);
+      row_d2 = pack2(dl, dl);
     }
 
     int t = 0;
@@ -349,25 +397,27 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
             if (a.mode_dkv) lo = own_pos - (seg_off + c0);        // query c visible iff seg_off+c0+c >= own_pos
             else hi = own_pos - (seg_off + c0) + 1;               // key c visible iff seg_off+c0+c <= own_pos
           }
+          const bool need_mask = __any_sync(0xffffffffu, lo > 0 || hi < 32);  // only steps crossing the diagonal
           const float* stats = reinterpret_cast<const float*>(sStage + stage * kBwdStageBytes + 2 * kStrTileBytes);
+          const uint64_t* nl_col = reinterpret_cast<const uint64_t*>(stats + half * 32);            // -lse2 pairs
+          const uint64_t* d_col = reinterpret_cast<const uint64_t*>(stats + kStrRows + half * 32);  // delta pairs
           uint32_t pk[16], dk[16];
+          // Packed pairs: p = exp2(x*c + nlse2), ds = p * (y - delta); two elements per FMA-pipe instruction.
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            float l0, l1, d0, d1;
-            if (a.mode_dkv) {
-              const float2 lv = *reinterpret_cast<const float2*>(stats + half * 32 + e);
-              const float2 dv = *reinterpret_cast<const float2*>(stats + kStrRows + half * 32 + e);
-              l0 = lv.x; l1 = lv.y; d0 = dv.x; d1 = dv.y;
-            } else {
-              l0 = l1 = row_lse2;
-              d0 = d1 = row_delta;
+            const uint64_t nl2 = dkv_mode ? nl_col[e >> 1] : row_nl2;
+            const uint64_t d2 = dkv_mode ? d_col[e >> 1] : row_d2;
+            const uint64_t t2 = fma2(pack2(__uint_as_float(xr[e]), __uint_as_float(xr[e + 1])), c2, nl2);
+            float t0, t1;
+            unpack2(t2, t0, t1);
+            float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+            if (need_mask) {
+              if (e < lo || e >= hi) p0 = 0.f;
+              if (e + 1 < lo || e + 1 >= hi) p1 = 0.f;
             }
-            float p0 = fast_exp2(fmaf(__uint_as_float(xr[e]), a.scale_log2, -l0));
-            float p1 = fast_exp2(fmaf(__uint_as_float(xr[e + 1]), a.scale_log2, -l1));
-            if (e < lo || e >= hi) p0 = 0.f;
-            if (e + 1 < lo || e + 1 >= hi) p1 = 0.f;
-            const float s0 = p0 * (__uint_as_float(yr[e]) - d0);
-            const float s1 = p1 * (__uint_as_float(yr[e + 1]) - d1);
+            const uint64_t s2 = mul2(pack2(p0, p1), sub2(pack2(__uint_as_float(yr[e]), __uint_as_float(yr[e + 1])), d2));
+            float s0, s1;
+            unpack2(s2, s0, s1);
             pk[e >> 1] = pack_bf16x2(p0, p1);
             dk[e >> 1] = pack_bf16x2(s0, s1);
           }
@@ -444,7 +494,7 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
 }
 
 // ---------------------------------------------------------------------------
-// preprocess: delta = rowsum(dO * O), lse2 = lse * log2(e)  ->  [B, Hq, pad] fp32 each
+// preprocess: delta = rowsum(dO * O), lse2 = -lse * log2(e)  ->  [B, Hq, pad] fp32 each
 // ---------------------------------------------------------------------------
 struct PreArgs {
   const __nv_bfloat16* dout;
@@ -465,7 +515,7 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreArgs a) {
   const long long sidx = ((long long)b * a.Hq + h) * a.pad + row;
   if (row >= a.Sq) {
     if (lane == 0) {
-      a.lse2[sidx] = INFINITY;
+      a.lse2[sidx] = -INFINITY;
       a.delta[sidx] = 0.f;
     }
     return;
@@ -480,7 +530,7 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreArgs a) {
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) {
     const float l = a.lse[((long long)b * a.Hq + h) * a.Sq + row];
-    a.lse2[sidx] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+    a.lse2[sidx] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
     a.delta[sidx] = acc;
   }
 }

@@ -211,6 +211,12 @@ typedef struct mb_merge_args {
  * Rows whose block_lse is -inf are left unchanged; rows whose lse is -inf adopt the block. */
 MB_API int mb_merge_out_lse(const mb_merge_args* args, void* cuda_stream);
 
+/* Merge of two packed fp32 buffers of `rows` rows, each row = head_dim_plus_1 floats
+ * [out | lse]; out may alias lhs.  Replaces flash_reduce, utils/flash_attn_dsl.py:293-305 (the
+ * reduce op of the ring-over-Q schedule, mercury/backend/pytorch/codegen.py:116-190). */
+MB_API int mb_flash_reduce(const float* lhs, const float* rhs, float* out, int64_t rows, int32_t head_dim_plus_1,
+                           void* cuda_stream);
+
 /* ---- peer memory over NVLink (one process per GPU) ------------------------------------
  * Together these replace SendRecv.send_recv / commit / wait of
  * mercury/backend/pytorch/utils.py:9-39 (NCCL batch_isend_irecv): a send is a copy into the

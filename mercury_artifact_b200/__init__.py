@@ -2,4 +2,5 @@
 from . import _lib  # noqa: F401  (fails loudly when libmercury_b200.so is missing)
 from .attention import attn_bwd_dkv, attn_bwd_dq, attn_fwd_segments, bwd_preprocess  # noqa: F401
 from .integration import install_backend, load_generated, namespace  # noqa: F401
-from .ops import _flash_attn_backward, _flash_attn_forward, get_default_args, update_out_and_lse  # noqa: F401
+from .ops import (_flash_attn_backward, _flash_attn_forward, flash_reduce, get_default_args,  # noqa: F401
+                  update_out_and_lse)

@@ -81,6 +81,54 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeArgs a) {
   }
 }
 
+// Packed merge of two [rows, D+1] fp32 buffers, each row = [out (D values) | lse]:
+// the reference's flash_reduce (utils/flash_attn_dsl.py:293-305), used by the ring-over-Q
+// schedule whose reduce buffer rotates with the queries.  One warp per row; rows of D+1 floats
+// are not 16-byte aligned, so lanes read consecutive floats (coalesced 128-byte lines).
+__global__ void __launch_bounds__(256) flash_reduce_kernel(const float* __restrict__ lhs, const float* __restrict__ rhs,
+                                                           float* __restrict__ out, long long rows, int width) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int d = width - 1;
+  for (long long row = warp0; row < rows; row += nwarps) {
+    const float* l = lhs + row * width;
+    const float* r = rhs + row * width;
+    float* o = out + row * width;
+    const float ll = l[d], rl = r[d];
+    float w, new_l;
+    if (ll == -INFINITY) {
+      w = 1.f;
+      new_l = rl;
+    } else if (rl == -INFINITY) {
+      w = 0.f;
+      new_l = ll;
+    } else {
+      const float x = rl - ll;
+      w = 1.f / (1.f + expf(-x));                            // sigmoid(r_lse - l_lse)
+      new_l = ll + fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));  // l_lse - logsigmoid(l_lse - r_lse)
+    }
+    for (int c = lane; c < d; c += 32) {
+      const float lo = l[c];
+      o[c] = lo - w * (lo - r[c]);
+    }
+    if (lane == 0) o[d] = new_l;
+  }
+}
+
+int launch_flash_reduce(const float* lhs, const float* rhs, float* out, long long rows, int width,
+                        cudaStream_t stream) {
+  if (rows < 0 || width < 2) return MB_E_INVALID;
+  if (rows == 0) return MB_SUCCESS;
+  if (lhs == nullptr || rhs == nullptr || out == nullptr) return MB_E_INVALID;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long want = (rows + 7) / 8;
+  const long long cap = static_cast<long long>(sms) * 8;
+  flash_reduce_kernel<<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(lhs, rhs, out, rows, width);
+  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+}
+
 int launch_merge(const mb_merge_args* x, cudaStream_t stream) {
   if (x == nullptr || x->out == nullptr || x->lse == nullptr || x->block_out == nullptr || x->block_lse == nullptr)
     return MB_E_INVALID;

@@ -24,6 +24,7 @@ def namespace(extra: Dict[str, object] | None = None) -> Dict[str, object]:
         "_flash_attn_forward": ops._flash_attn_forward,
         "get_default_args": ops.get_default_args,
         "update_out_and_lse": ops.update_out_and_lse,
+        "flash_reduce": ops.flash_reduce,
     }
     if hasattr(ops, "_flash_attn_backward"):
         ns["_flash_attn_backward"] = ops._flash_attn_backward

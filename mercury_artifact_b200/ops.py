@@ -178,3 +178,20 @@ def update_out_and_lse(
         raise ValueError("update_out_and_lse: running state must be contiguous fp32")
     _merge_launch(out, lse, block_out, block_lse, first=False)
     return out, lse
+
+
+def flash_reduce(lhs: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
+    """Merge of two packed fp32 [..., D+1] = [out | lse] buffers, the reduce op of the ring-over-Q
+    schedule (utils/flash_attn_dsl.py:293-305).  Returns a new tensor, like the reference."""
+    if not (lhs.is_cuda and rhs.is_cuda):
+        raise ValueError("flash_reduce: CUDA tensors only (there is no CPU path)")
+    if lhs.shape != rhs.shape or lhs.dtype != torch.float32 or rhs.dtype != torch.float32:
+        raise ValueError("flash_reduce: both operands must be fp32 with the same [..., D+1] shape")
+    lhs, rhs = lhs.contiguous(), rhs.contiguous()
+    out = torch.empty_like(lhs)
+    width = lhs.shape[-1]
+    rows = lhs.numel() // width if width else 0
+    with torch.cuda.device(lhs.device):
+        _lib.check(_lib.lib.mb_flash_reduce(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr(), rows, width,
+                                            C.c_void_p(_stream_ptr())), "mb_flash_reduce")
+    return out

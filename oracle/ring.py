@@ -149,6 +149,39 @@ def simulate_ring_fwd(
 
 
 # ---------------------------------------------------------------------------
+# ring over Q with a rotating packed reduce buffer (codegen.py:116-190, flash_reduce)
+# ---------------------------------------------------------------------------
+def simulate_ring_over_q(q_shards, kv_shards, softmax_scale: float, mesh_shape: Sequence[int],
+                         block_fn: Callable = _block.block_attn_fwd):
+    """K/V stay put; the query shard and a packed fp32 [B,S/P,H,D+1] = [out | lse] buffer rotate
+    together.  Step 0 starts the buffer from the local block result, later steps merge the buffer
+    that arrived with the queries (flash_reduce), and one extra hop (get_src_dst_ranks) returns
+    each buffer to the rank that owns those queries.  Non-causal, as in the reference."""
+    p = len(q_shards)
+    ring_dims = list(range(len(mesh_shape)))
+    held_q = [q.clone() for q in q_shards]
+    buf: List[Optional[torch.Tensor]] = [None] * p
+    incoming: List[Optional[torch.Tensor]] = [None] * p
+    for idx, st in enumerate(ring_steps(mesh_shape)):
+        d = hop_dim(st, mesh_shape)
+        if d is not None:
+            src = [rank_of(shift_coord(coords_of(r, mesh_shape), d, -1, mesh_shape[d]), mesh_shape) for r in range(p)]
+        for r in range(p):
+            bo, bl = block_fn(held_q[r], kv_shards[r][0], kv_shards[r][1], softmax_scale, causal=False)
+            res = torch.cat([bo.to(torch.float32), bl.transpose(-2, -1).unsqueeze(-1)], dim=-1)
+            buf[r] = res.contiguous() if idx == 0 else _merge.flash_reduce(incoming[r], res)
+        if d is not None:
+            held_q = [held_q[s] for s in src]
+            incoming = [buf[s] for s in src]
+        else:
+            back = [writeback_src_dst(coords_of(r, mesh_shape), mesh_shape, ring_dims)[0] for r in range(p)]
+            buf = [buf[s] for s in back]
+    outs = [b[..., :-1].to(q_shards[r].dtype) for r, b in enumerate(buf)]
+    lses = [b[..., -1].transpose(1, 2).contiguous() for b in buf]
+    return outs, lses
+
+
+# ---------------------------------------------------------------------------
 # backward, all ranks in one process (codegen.py:99-190)
 # ---------------------------------------------------------------------------
 def simulate_ring_bwd(

@@ -65,6 +65,8 @@ def generate(ref_root: str, kind: str, world: int, B: int, S: int, H: int, D: in
             BATCH=B, HEADS=H, SEQ_LEN=S, HEAD_DIM=D, SEQ_LEN_IN=S // mesh[1], SEQ_LEN_OUT=mesh[1])
     elif kind == "bwd":
         src = attn_backward_template.format(BATCH=B, HEADS=H, SEQ_LEN=S, HEAD_DIM=D)
+    elif kind == "ring_over_q":
+        src = dsl.flash_attn_manage_reduction.format(BATCH=B, HEADS=H, SEQ_LEN=S, HEAD_DIM=D, RED_DIM=D + 1)
     else:
         raise ValueError(kind)
     prog = IRBuilder().visit(ast.parse(textwrap.dedent(src)).body[0])
@@ -73,7 +75,11 @@ def generate(ref_root: str, kind: str, world: int, B: int, S: int, H: int, D: in
     shape = tuple(mesh) if mesh else (world,)
     dm = DeviceMesh(list(range(world)), shape)
     init_distributed(prog, dm)
-    if world > 1:
+    if world > 1 and kind == "ring_over_q":
+        # K/V sharded and stationary; the queries and the packed reduce buffer rotate
+        parallelize(prog, loops[1], axes[3], dm, 0, len(shape))
+        shift(prog, axes[3], dm, 0, len(shape), 1)
+    elif world > 1:
         outer = loops[1] if kind == "bwd" else loops[0]
         parallelize(prog, outer, axes[2], dm, 0, len(shape))
         shift(prog, axes[2], dm, 0, len(shape), 1)
@@ -121,8 +127,10 @@ def _worker(rank, world, ref_root, code, fn_name, kind, dims, seed, port, ret):
         "update_out_and_lse": dsl.update_out_and_lse,
         "_flash_attn_forward": _flash_attn_forward,
         "_flash_attn_backward": _flash_attn_backward,
+        "flash_reduce": dsl.flash_reduce,
+        "update_out_and_lse_collective": dsl.update_out_and_lse_collective,
     }
-    if kind == "bwd":
+    if kind in ("bwd", "ring_over_q"):
         code = code.replace('torch.device(f"cuda:{local_rank}")', 'torch.device("cpu")')
     exec(code, ns)
     fn = ns[fn_name]
@@ -156,6 +164,8 @@ CASES = [
     ("double_ring_2x2", "double_ring", "flash_attn_pack_split_kv", 4, (2, 2), (1, 256, 2, 2, 32), 15),
     ("bwd_p2", "bwd", "flash_attn_backward", 2, None, (1, 256, 2, 2, 32), 16),
     ("bwd_p4", "bwd", "flash_attn_backward", 4, None, (1, 256, 2, 2, 32), 17),
+    ("ring_over_q_p2", "ring_over_q", "flash_attn_expose_reduce", 2, None, (1, 256, 2, 2, 32), 18),
+    ("ring_over_q_p4", "ring_over_q", "flash_attn_expose_reduce", 4, None, (1, 256, 2, 2, 32), 19),
 ]
 
 # Program text only (no vectors): the shapes the GPU tests run through the drop-in ops.
@@ -168,13 +178,18 @@ TEXT_ONLY = [
     ("gpu_double_ring_4x2", "double_ring", 8, (4, 2), (1, 4096, 2, 2, 128)),
     ("gpu_bwd_p2", "bwd", 2, None, (1, 1024, 4, 4, 128)),
     ("gpu_bwd_p4", "bwd", 4, None, (1, 2048, 4, 4, 128)),
+    ("gpu_ring_over_q_p2", "ring_over_q", 2, None, (1, 1024, 4, 4, 128)),
+    ("gpu_ring_over_q_p4", "ring_over_q", 4, None, (2, 1024, 4, 4, 128)),
 ]
 
 
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    only = set(sys.argv[2:])  # optional: regenerate just the named cases
     port = 29611
     for name, kind, fn_name, world, mesh, dims, seed in CASES:
+        if only and name not in only:
+            continue
         B, S, H, hkv, D = dims
         code = generate(ref_root, kind, world, B, S, H, D, hkv=hkv, mesh=mesh)
         (HERE / f"{name}.gen.txt").write_text(code)
@@ -191,6 +206,8 @@ def main():
         np.savez_compressed(HERE / f"{name}.npz", **arrays)
         print("wrote", name, {k: v.shape for k, v in arrays.items() if k != "meta"})
     for name, kind, world, mesh, dims in TEXT_ONLY:
+        if only and name not in only:
+            continue
         B, S, H, hkv, D = dims
         code = generate(ref_root, kind, world, B, S, H, D, hkv=hkv, mesh=mesh)
         (HERE / f"{name}.gen.txt").write_text(code)

@@ -65,3 +65,13 @@ def test_double_ring_program_2x2():
 
 def test_double_ring_program_4x2():
     _run_forward("gpu_double_ring_4x2", "flash_attn_pack_split_kv", 8, 1, 4096, 2, 2)
+
+
+def test_ring_over_q_program_two_ranks():
+    """Ring-over-Q schedule (K/V stationary, queries + packed reduce buffer rotate, write-back hop)
+    with the drop-in block op and the flash_reduce kernel."""
+    _run_forward("gpu_ring_over_q_p2", "flash_attn_expose_reduce", 2, 1, 1024, 4, 4)
+
+
+def test_ring_over_q_program_four_ranks():
+    _run_forward("gpu_ring_over_q_p4", "flash_attn_expose_reduce", 4, 2, 1024, 4, 4)

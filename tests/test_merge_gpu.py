@@ -58,3 +58,23 @@ def test_merge_handles_rows_without_keys():
     assert (out[:, :16] == 1).all() and (out[:, 48:] == 3).all()
     assert torch.allclose(out[:, 16:48], torch.full((B, 32, H, D), 2.0))
     assert torch.allclose(lse[:, 16:48], torch.full((B, 32, H), 0.6931472))
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 2, 129), (2, 333, 5, 65), (1, 2048, 32, 129)])
+def test_flash_reduce_matches_oracle(shape):
+    import mercury_artifact_b200 as mb
+    from oracle import merge
+
+    g = torch.Generator().manual_seed(8)
+    parts = [torch.randn(*shape, generator=g) for _ in range(3)]
+    for p in parts:
+        p[..., -1] *= 4
+    acc = parts[0].cuda()
+    ref = parts[0]
+    for p in parts[1:]:
+        acc = mb.flash_reduce(acc, p.cuda())
+        ref = merge.flash_reduce(ref, p)
+    assert acc.shape == ref.shape and acc.dtype == torch.float32
+    assert (acc.cpu() - ref).abs().max().item() <= 1e-5
+    with pytest.raises(ValueError):
+        mb.flash_reduce(parts[0], parts[1])

@@ -131,3 +131,18 @@ def test_config1_ring_fp32_matches_full_attention():
     fo, fl = block.full_attention(q, k, v, D ** -0.5)
     assert (torch.cat(o, 1) - fo).abs().max() < 1e-5
     assert (torch.cat(l, 2) - fl).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("name", ["ring_over_q_p2", "ring_over_q_p4"])
+def test_ring_over_q_schedule_matches_reference_output(name):
+    """K/V stationary, queries and the packed [out | lse] reduce buffer rotate (flash_reduce),
+    with the write-back hop: oracle vs the reference's own generated program."""
+    g = load_golden(name)
+    t = g["t"]
+    qs, kvs = shard_inputs(t["q"], t["k"], t["v"], g["world"])
+    outs, lses = ring.simulate_ring_over_q(qs, kvs, g["D"] ** -0.5, g["mesh"])
+    fo, fl = block.full_attention(t["q"], t["k"], t["v"], g["D"] ** -0.5)
+    for r in range(g["world"]):
+        assert torch.allclose(outs[r], t[f"o_rank{r}"], atol=2e-6)
+        assert torch.allclose(lses[r], t[f"lse_rank{r}"], atol=2e-6)
+        assert torch.allclose(fo.chunk(g["world"], 1)[r], t[f"o_rank{r}"], atol=1e-5)

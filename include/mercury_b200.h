@@ -217,6 +217,15 @@ MB_API int mb_merge_out_lse(const mb_merge_args* args, void* cuda_stream);
 MB_API int mb_flash_reduce(const float* lhs, const float* rhs, float* out, int64_t rows, int32_t head_dim_plus_1,
                            void* cuda_stream);
 
+/* One-shot merge of n (<= 16) packed fp32 buffers [rows, head_dim_plus_1] into out:
+ * lse* = log sum_r exp(lse_r), out* = sum_r exp(lse_r - lse*) out_r.  srcs is a HOST array of n
+ * device pointers; they may be peer mappings (the kernel then reads over NVLink).  out must not
+ * alias a source another rank is still reading.  Replaces update_out_and_lse_collective,
+ * utils/flash_attn_dsl.py:307-324 (the tree / all-reduce merge emitted at
+ * mercury/backend/pytorch/codegen.py:427-440). */
+MB_API int mb_tree_merge(const float* const* srcs, int32_t n, float* out, int64_t rows, int32_t head_dim_plus_1,
+                         void* cuda_stream);
+
 /* ---- peer memory over NVLink (one process per GPU) ------------------------------------
  * Together these replace SendRecv.send_recv / commit / wait of
  * mercury/backend/pytorch/utils.py:9-39 (NCCL batch_isend_irecv): a send is a copy into the

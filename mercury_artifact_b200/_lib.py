@@ -230,6 +230,7 @@ _SIGNATURES = {
     "mb_attn_bwd": [C.POINTER(AttnBwdArgs), C.c_void_p],
     "mb_attn_bwd_block_noalloc": [C.POINTER(AttnBwdBlockArgs), C.c_void_p],
     "mb_merge_out_lse": [C.POINTER(MergeArgs), C.c_void_p],
+    "mb_tree_merge": [C.POINTER(C.c_void_p), C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p],
     "mb_flash_reduce": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p],
     "mb_mem_alloc": [C.POINTER(C.c_void_p), C.c_uint64],
     "mb_mem_free": [C.c_void_p],

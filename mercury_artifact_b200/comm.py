@@ -73,13 +73,6 @@ class DeviceBuffer:
             self.ptr = 0
 
 
-class _RawDeviceMemory:
-    """Exposes a raw device address range to torch through the CUDA array interface."""
-
-    def __init__(self, ptr: int, nbytes: int):
-        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
-
-
 class SymmetricBuffer:
     """The same-sized allocation on every rank, with every peer's copy mapped locally."""
 
@@ -108,16 +101,6 @@ class SymmetricBuffer:
 
     def ptr(self, rank: int, offset: int = 0) -> int:
         return self.peer_ptr[rank] + offset
-
-    def bytes_of(self, rank: int) -> torch.Tensor:
-        """uint8 view of `rank`'s copy of the buffer (a peer mapping unless rank is this rank)."""
-        if rank == self.ctx.rank:
-            return self.local.bytes()
-        cache = self.__dict__.setdefault("_peer_views", {})
-        if rank not in cache:
-            holder = _RawDeviceMemory(self.peer_ptr[rank], self.nbytes)
-            cache[rank] = (holder, torch.as_tensor(holder, device=self.ctx.device))
-        return cache[rank][1]
 
 
 class PeerContext:

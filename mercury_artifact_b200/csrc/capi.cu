@@ -64,6 +64,11 @@ int mb_flash_reduce(const float* lhs, const float* rhs, float* out, int64_t rows
   return mb::launch_flash_reduce(lhs, rhs, out, rows, head_dim_plus_1, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int mb_tree_merge(const float* const* srcs, int32_t n, float* out, int64_t rows, int32_t head_dim_plus_1,
+                  void* cuda_stream) {
+  return mb::launch_tree_merge(srcs, n, out, rows, head_dim_plus_1, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int mb_merge_out_lse(const mb_merge_args* args, void* cuda_stream) {
   return mb::launch_merge(args, static_cast<cudaStream_t>(cuda_stream));
 }

@@ -18,6 +18,7 @@ int* default_status_word();
 
 int launch_attn_fwd(const mb_attn_fwd_args* args, cudaStream_t stream);
 int launch_merge(const mb_merge_args* args, cudaStream_t stream);
+int launch_tree_merge(const float* const* srcs, int n, float* out, long long rows, int width, cudaStream_t stream);
 int launch_flash_reduce(const float* lhs, const float* rhs, float* out, long long rows, int width, cudaStream_t stream);
 int launch_bwd_preprocess(const mb_bwd_preprocess_args* args, cudaStream_t stream);
 int launch_attn_bwd(const mb_attn_bwd_args* args, cudaStream_t stream);

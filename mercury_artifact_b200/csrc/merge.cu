@@ -129,6 +129,72 @@ int launch_flash_reduce(const float* lhs, const float* rhs, float* out, long lon
   return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
 }
 
+// One-shot merge of n packed [rows, D+1] fp32 buffers (row = [out | lse]) into `out`:
+//   lse* = log sum_r exp(lse_r),   out* = sum_r exp(lse_r - lse*) out_r
+// which is what the reference's tree merge computes with three collectives
+// (update_out_and_lse_collective, utils/flash_attn_dsl.py:307-324: all_reduce(MAX) of the LSE,
+// then all_reduce(SUM) of the rescaled outputs and of the weights).  The source pointers may
+// be other ranks' buffers mapped into this process: the loads then cross NVLink inside the
+// kernel, each rank reading every peer once.  One warp per row, n <= 16.
+struct TreeArgs {
+  const float* src[16];
+  float* out;
+  long long rows;
+  int n, width;
+};
+
+__global__ void __launch_bounds__(256) tree_merge_kernel(const TreeArgs a) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int d = a.width - 1;
+  for (long long row = warp0; row < a.rows; row += nwarps) {
+    const long long base = row * a.width;
+    float m = -INFINITY;
+    float lse_r[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      lse_r[r] = r < a.n ? a.src[r][base + d] : -INFINITY;
+      m = fmaxf(m, lse_r[r]);
+    }
+    float denom = 0.f;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      lse_r[r] = (r < a.n && m != -INFINITY) ? expf(lse_r[r] - m) : 0.f;  // now the weight of rank r
+      denom += lse_r[r];
+    }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    for (int c = lane; c < d; c += 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int r = 0; r < 16; ++r)
+        if (r < a.n) acc += lse_r[r] * a.src[r][base + c];
+      a.out[base + c] = acc * inv;
+    }
+    if (lane == 0) a.out[base + d] = denom > 0.f ? m + logf(denom) : -INFINITY;
+  }
+}
+
+int launch_tree_merge(const float* const* srcs, int n, float* out, long long rows, int width, cudaStream_t stream) {
+  if (n < 1 || n > 16 || rows < 0 || width < 2) return MB_E_INVALID;
+  if (rows == 0) return MB_SUCCESS;
+  if (srcs == nullptr || out == nullptr) return MB_E_INVALID;
+  TreeArgs a;
+  for (int r = 0; r < 16; ++r) a.src[r] = r < n ? srcs[r] : nullptr;
+  for (int r = 0; r < n; ++r)
+    if (a.src[r] == nullptr) return MB_E_INVALID;
+  a.out = out;
+  a.rows = rows;
+  a.n = n;
+  a.width = width;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long want = (rows + 7) / 8;
+  const long long cap = static_cast<long long>(sms) * 8;
+  tree_merge_kernel<<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+}
+
 int launch_merge(const mb_merge_args* x, cudaStream_t stream) {
   if (x == nullptr || x->out == nullptr || x->lse == nullptr || x->block_out == nullptr || x->block_lse == nullptr)
     return MB_E_INVALID;

@@ -18,6 +18,12 @@ from typing import Dict
 from . import mesh, ops
 
 
+def _collective(tensor, op, group, dst=None):
+    from .collective import update_out_and_lse_collective
+
+    return update_out_and_lse_collective(tensor, op, group, dst)
+
+
 def namespace(extra: Dict[str, object] | None = None) -> Dict[str, object]:
     """Globals for exec(generated_code, ns): every free name the DSL bodies use."""
     ns: Dict[str, object] = {
@@ -25,6 +31,7 @@ def namespace(extra: Dict[str, object] | None = None) -> Dict[str, object]:
         "get_default_args": ops.get_default_args,
         "update_out_and_lse": ops.update_out_and_lse,
         "flash_reduce": ops.flash_reduce,
+        "update_out_and_lse_collective": _collective,
     }
     if hasattr(ops, "_flash_attn_backward"):
         ns["_flash_attn_backward"] = ops._flash_attn_backward
@@ -33,7 +40,8 @@ def namespace(extra: Dict[str, object] | None = None) -> Dict[str, object]:
     return ns
 
 
-_RUNTIME_NAMES = ("one_dim_to_n_dim", "n_dim_to_one_dim", "shift_tuple_element", "get_src_dst_ranks")
+_RUNTIME_NAMES = ("one_dim_to_n_dim", "n_dim_to_one_dim", "shift_tuple_element", "get_src_dst_ranks",
+                  "get_device_group")
 
 
 def install_backend(send_recv_cls=None, force_stub: bool = False) -> types.ModuleType:

@@ -82,3 +82,48 @@ def kv_origin_schedule(rank: int, mesh_shape: Sequence[int]) -> List[int]:
                 break
             idx[d] = 0
     return out
+
+
+_group_cache = {}
+
+
+def group_ranks(indices: Tuple[int, ...], mesh_shape: Tuple[int, ...], dims: Sequence[int]) -> Tuple[int, ...]:
+    """Ranks that share every mesh coordinate with `indices` except along `dims` (sorted)."""
+    for d in dims:
+        if d < 0 or d >= len(mesh_shape):
+            raise ValueError(f"Invalid dimension index: {d}, mesh shape: {mesh_shape}")
+    ranks = []
+    total = 1
+    for n in mesh_shape:
+        total *= n
+    for r in range(total):
+        c = one_dim_to_n_dim(r, tuple(mesh_shape))
+        if all(c[i] == indices[i] for i in range(len(mesh_shape)) if i not in dims):
+            ranks.append(r)
+    return tuple(sorted(ranks))
+
+
+def get_device_group(indices: Tuple[int, ...], mesh_shape: Tuple[int, ...], dims: Tuple[int, ...], debug: bool = False):
+    """Communication group of the ranks that differ from `indices` only along `dims`
+    (mercury/backend/pytorch/utils.py:114-169).  Every rank of the job must call this in the same
+    order, because the groups of ALL ranks are created (torch.distributed.new_group is collective);
+    debug=True returns the tuple of ranks instead of a process group."""
+    key = (tuple(indices), tuple(mesh_shape), tuple(dims), bool(debug))
+    if key in _group_cache:
+        return _group_cache[key]
+    import torch.distributed as dist
+
+    total = 1
+    for n in mesh_shape:
+        total *= n
+    made = {}
+    mine = None
+    for r in range(total):
+        c = one_dim_to_n_dim(r, tuple(mesh_shape))
+        ranks = group_ranks(c, tuple(mesh_shape), tuple(dims))
+        if ranks not in made:
+            made[ranks] = ranks if debug else dist.new_group(ranks=list(ranks))
+        if c == tuple(indices):
+            mine = made[ranks]
+    _group_cache[key] = mine
+    return mine

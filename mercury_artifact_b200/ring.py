@@ -69,8 +69,9 @@ class _ShardExchange:
         off = (self.epoch % 2) * self.slot_bytes
         return self.sym.local.bytes()[off:off + self.slot_bytes]
 
-    def begin(self, main: torch.cuda.Stream) -> torch.Tensor:
-        """Start a new epoch; returns this rank's byte slot to fill on the transfer stream."""
+    def begin(self, main: torch.cuda.Stream, peers: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """Start a new epoch; returns this rank's byte slot to fill on the transfer stream.
+        peers restricts the exchange to a sub-group of ranks (default: every rank)."""
         ctx, comm = self.ctx, self.ctx.comm_stream
         self.epoch += 1
         self._next_stage = 0
@@ -78,17 +79,17 @@ class _ShardExchange:
         e = self.epoch
         comm.wait_stream(main)
         if e > 2:  # the slot was last used at epoch e-2: every peer has released it by now or soon
-            for p in range(self.world):
+            for p in (peers if peers is not None else range(self.world)):
                 if p != self.rank:
                     ctx.wait_flag(self._done_ptr(self.rank, p), e - 2, comm)
         return self.local_slot()
 
-    def publish(self) -> torch.cuda.Event:
+    def publish(self, peers: Optional[Sequence[int]] = None) -> torch.cuda.Event:
         """Announce the filled slot to every peer; the event fires once the local copy is in place."""
         ctx, comm = self.ctx, self.ctx.comm_stream
         ev = torch.cuda.Event()
         ev.record(comm)
-        for p in range(self.world):
+        for p in (peers if peers is not None else range(self.world)):
             if p != self.rank:
                 ctx.signal(self._ready_ptr(p, self.rank), self.epoch, comm)
         return ev

@@ -64,3 +64,14 @@ def merge_exact(parts):
     w = torch.nan_to_num(w, nan=0.0)
     out = sum(p[0].float() * w[i].transpose(-2, -1).unsqueeze(-1) for i, p in enumerate(parts))
     return out, total
+
+
+def tree_merge(packed_parts):
+    """What update_out_and_lse_collective leaves on every rank (utils/flash_attn_dsl.py:307-324):
+    with m = max_r lse_r and d_r = exp(lse_r - m):  out = sum_r d_r out_r / sum_r d_r,
+    lse = m + log sum_r d_r.  packed_parts: list of [..., D+1] fp32 tensors, one per rank."""
+    lses = torch.stack([p[..., -1:] for p in packed_parts])
+    m = lses.max(dim=0).values
+    d = torch.exp(lses - m)
+    out = sum(p[..., :-1] * d[i] for i, p in enumerate(packed_parts)) / d.sum(dim=0)
+    return torch.cat([out, m + torch.log(d.sum(dim=0))], dim=-1)

@@ -65,7 +65,7 @@ def generate(ref_root: str, kind: str, world: int, B: int, S: int, H: int, D: in
             BATCH=B, HEADS=H, SEQ_LEN=S, HEAD_DIM=D, SEQ_LEN_IN=S // mesh[1], SEQ_LEN_OUT=mesh[1])
     elif kind == "bwd":
         src = attn_backward_template.format(BATCH=B, HEADS=H, SEQ_LEN=S, HEAD_DIM=D)
-    elif kind == "ring_over_q":
+    elif kind in ("ring_over_q", "tree"):
         src = dsl.flash_attn_manage_reduction.format(BATCH=B, HEADS=H, SEQ_LEN=S, HEAD_DIM=D, RED_DIM=D + 1)
     else:
         raise ValueError(kind)
@@ -75,7 +75,10 @@ def generate(ref_root: str, kind: str, world: int, B: int, S: int, H: int, D: in
     shape = tuple(mesh) if mesh else (world,)
     dm = DeviceMesh(list(range(world)), shape)
     init_distributed(prog, dm)
-    if world > 1 and kind == "ring_over_q":
+    if world > 1 and kind == "tree":
+        # K/V sharded, queries replicated: partial results merged by the all-reduce collective
+        parallelize(prog, loops[1], axes[3], dm, 0, len(shape))
+    elif world > 1 and kind == "ring_over_q":
         # K/V sharded and stationary; the queries and the packed reduce buffer rotate
         parallelize(prog, loops[1], axes[3], dm, 0, len(shape))
         shift(prog, axes[3], dm, 0, len(shape), 1)
@@ -130,12 +133,12 @@ def _worker(rank, world, ref_root, code, fn_name, kind, dims, seed, port, ret):
         "flash_reduce": dsl.flash_reduce,
         "update_out_and_lse_collective": dsl.update_out_and_lse_collective,
     }
-    if kind in ("bwd", "ring_over_q"):
+    if kind in ("bwd", "ring_over_q", "tree"):
         code = code.replace('torch.device(f"cuda:{local_rank}")', 'torch.device("cpu")')
     exec(code, ns)
     fn = ns[fn_name]
     q, k, v, do = make_inputs(seed, B, S, H, hkv, D)
-    lq = q.chunk(world, 1)[rank].contiguous()
+    lq = q.contiguous() if kind == "tree" else q.chunk(world, 1)[rank].contiguous()
     lkv = torch.stack([k.chunk(world, 1)[rank], v.chunk(world, 1)[rank]]).contiguous()
     if kind == "bwd":
         fo, fl = ob.full_attention(q, k, v, scale)
@@ -148,7 +151,7 @@ def _worker(rank, world, ref_root, code, fn_name, kind, dims, seed, port, ret):
         ret[rank] = dict(dq=dq.numpy(), dkv=dkv.numpy())
     else:
         o = torch.zeros_like(lq)
-        lse = torch.zeros(B, H, S // world)
+        lse = torch.zeros(B, H, lq.shape[1])
         fn(lq, lkv, o, lse, scale)
         ret[rank] = dict(o=o.numpy(), lse=lse.numpy())
     dist.barrier()
@@ -166,6 +169,8 @@ CASES = [
     ("bwd_p4", "bwd", "flash_attn_backward", 4, None, (1, 256, 2, 2, 32), 17),
     ("ring_over_q_p2", "ring_over_q", "flash_attn_expose_reduce", 2, None, (1, 256, 2, 2, 32), 18),
     ("ring_over_q_p4", "ring_over_q", "flash_attn_expose_reduce", 4, None, (1, 256, 2, 2, 32), 19),
+    ("tree_p2", "tree", "flash_attn_expose_reduce", 2, None, (1, 256, 2, 2, 32), 20),
+    ("tree_p4", "tree", "flash_attn_expose_reduce", 4, None, (1, 256, 2, 2, 32), 21),
 ]
 
 # Program text only (no vectors): the shapes the GPU tests run through the drop-in ops.
@@ -180,6 +185,7 @@ TEXT_ONLY = [
     ("gpu_bwd_p4", "bwd", 4, None, (1, 2048, 4, 4, 128)),
     ("gpu_ring_over_q_p2", "ring_over_q", 2, None, (1, 1024, 4, 4, 128)),
     ("gpu_ring_over_q_p4", "ring_over_q", 4, None, (2, 1024, 4, 4, 128)),
+    ("gpu_tree_p2", "tree", 2, None, (1, 1024, 4, 4, 128)),
 ]
 
 

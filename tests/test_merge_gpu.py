@@ -78,3 +78,30 @@ def test_flash_reduce_matches_oracle(shape):
     assert (acc.cpu() - ref).abs().max().item() <= 1e-5
     with pytest.raises(ValueError):
         mb.flash_reduce(parts[0], parts[1])
+
+
+@pytest.mark.parametrize("n,shape", [(2, (1, 128, 2, 129)), (8, (2, 100, 3, 65)), (16, (1, 64, 1, 129))])
+def test_tree_merge_kernel_matches_oracle(n, shape):
+    """mb_tree_merge on one device (all sources local) against the oracle's restatement of
+    update_out_and_lse_collective; one source has rows without keys (lse = -inf)."""
+    import ctypes as C
+
+    from mercury_artifact_b200 import _lib
+    from oracle import merge
+
+    g = torch.Generator().manual_seed(9)
+    parts = [torch.randn(*shape, generator=g) for _ in range(n)]
+    for p in parts:
+        p[..., -1] *= 3
+    parts[0][:, :7, :, -1] = float("-inf")
+    dev = [p.cuda() for p in parts]
+    out = torch.empty_like(dev[0])
+    srcs = (C.c_void_p * n)(*[d.data_ptr() for d in dev])
+    width = shape[-1]
+    rc = _lib.lib.mb_tree_merge(srcs, n, out.data_ptr(), out.numel() // width, width,
+                                C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    ref = merge.tree_merge(parts)
+    assert not torch.isnan(out).any()
+    assert (out.cpu() - ref).abs().max().item() <= 1e-5
+    assert _lib.lib.mb_tree_merge(srcs, 17, out.data_ptr(), 1, width, None) == -1

@@ -146,3 +146,24 @@ def test_ring_over_q_schedule_matches_reference_output(name):
         assert torch.allclose(outs[r], t[f"o_rank{r}"], atol=2e-6)
         assert torch.allclose(lses[r], t[f"lse_rank{r}"], atol=2e-6)
         assert torch.allclose(fo.chunk(g["world"], 1)[r], t[f"o_rank{r}"], atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["tree_p2", "tree_p4"])
+def test_tree_merge_matches_reference_output(name):
+    """K/V sharded, queries replicated, partial results merged by the all-reduce collective:
+    the oracle's one-pass merge equals what the reference's three collectives leave on every rank."""
+    g = load_golden(name)
+    t = g["t"]
+    w = g["world"]
+    scale = g["D"] ** -0.5
+    parts = []
+    for r in range(w):
+        k, v = t["k"].chunk(w, 1)[r], t["v"].chunk(w, 1)[r]
+        bo, bl = block.block_attn_fwd(t["q"], k, v, scale)
+        parts.append(torch.cat([bo.float(), bl.transpose(-2, -1).unsqueeze(-1)], dim=-1))
+    res = merge.tree_merge(parts)
+    fo, fl = block.full_attention(t["q"], t["k"], t["v"], scale)
+    for r in range(w):
+        assert torch.allclose(res[..., :-1], t[f"o_rank{r}"], atol=2e-6)
+        assert torch.allclose(res[..., -1].transpose(1, 2), t[f"lse_rank{r}"], atol=2e-6)
+        assert torch.allclose(fo, t[f"o_rank{r}"], atol=1e-5)

@@ -196,3 +196,51 @@ def test_eight_gpus(mesh_shape, causal, with_bwd):
                 assert (res[2] - gq.chunk(world, 1)[r]).abs().max().item() <= 2e-2
                 assert (res[3][0] - gk.chunk(world, 1)[r]).abs().max().item() <= 2e-2
                 assert (res[3][1] - gv.chunk(world, 1)[r]).abs().max().item() <= 2e-2
+
+
+def _tree_worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200.comm import init_p2p
+    from tests.helpers import golden_text, seeded_qkv
+
+    ctx = init_p2p(device=torch.device("cuda", rank))
+    mb.install_backend(force_stub=True)
+    B, S, H = 1, 1024, 4
+    q, k, v, _ = seeded_qkv(1234, B, S, H, H, 128)
+    lkv = torch.stack([k.chunk(world, 1)[rank], v.chunk(world, 1)[rank]]).contiguous().cuda()
+    fn = mb.load_generated(golden_text("gpu_tree_p2"))["flash_attn_expose_reduce"]
+    outs = []
+    for _ in range(3):
+        o = torch.zeros(B, S, H, 128, dtype=torch.bfloat16, device="cuda")
+        lse = torch.zeros(B, H, S, device="cuda")
+        fn(q.cuda(), lkv, o, lse, 128 ** -0.5)
+        outs.append((o.float().cpu(), lse.cpu()))
+    ctx.check()
+    ret[rank] = outs
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_generated_tree_program_two_gpus():
+    """The tree schedule emitted by the reference (K/V sharded, queries replicated, merge by
+    update_out_and_lse_collective) with the one-shot peer-memory merge on two GPUs."""
+    import torch.multiprocessing as mp
+    from oracle import block
+    from tests.helpers import seeded_qkv
+
+    world, B, S, H = 2, 1, 1024, 4
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_tree_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    q, k, v, _ = seeded_qkv(1234, B, S, H, H, 128)
+    fo, fl = block.full_attention(q, k, v, 128 ** -0.5)
+    for r in range(world):
+        for o, lse in ret[r]:
+            assert (o - fo.float()).abs().max().item() <= 2e-2
+            assert (lse - fl).abs().max().item() <= 1e-3

@@ -249,12 +249,12 @@ def run_ours(args):
         op.forward(q, kv, o, lse, scale)
 
     def step_e2e():
-        q.copy_(q_host, non_blocking=True)
-        kv.copy_(kv_host, non_blocking=True)
+        # public host-buffer entry: pinned host q/kv in, o/lse back in host memory when it returns
+        op.forward_host(q_host, kv_host, o_host, lse_host, scale)
+
+    def step_fwd_bwd():
         op.forward(q, kv, o, lse, scale)
-        o_host.copy_(o, non_blocking=True)
-        lse_host.copy_(lse, non_blocking=True)
-        stream.synchronize()
+        op.backward(dout, q, kv, o, lse, dq, dkv, scale)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -264,6 +264,11 @@ def run_ours(args):
     clocks = sampler.stop(t0, t1) if rank == 0 else None
     status = _lib.status_fetch(stream.cuda_stream)
     ms_e2e, _, _ = timed(step_e2e, max(3, args.steps // 2), 3)
+    status |= _lib.status_fetch(stream.cuda_stream)
+    # forward + backward (the metric's second figure): bwd counted as 2.5x the forward FLOPs
+    dout = (torch.randn(B, L, H, D, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    dq, dkv = torch.empty_like(q), torch.empty_like(kv)
+    ms_fb, _, _ = timed(step_fwd_bwd, max(3, args.steps // 2), 3)
     status |= _lib.status_fetch(stream.cuda_stream)
 
     # kernel-only duration for the roofline: the attention launch of the slowest rank, timed alone
@@ -298,6 +303,8 @@ def run_ours(args):
             "e2e": {"value": e2e, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": (q_host.numel() + kv_host.numel()) * 2 * world,
                     "d2h_bytes_per_step": (o_host.numel() * 2 + lse_host.numel() * 4) * world},
+            "fwd_bwd": {"value": 3.5 * fl_total / (ms_fb * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_fb,
+                        "note": "forward + backward per step, FLOPs = 3.5 x forward (backward counted as 2.5 x)"},
             "gpu_launches": args.steps * op.launches_per_forward * world,
             "roofline": {"bound": "tensor", "achieved": kernel_tf, "peak": peak, "unit": "TFLOP/s",
                          "frac": kernel_tf / peak, "traffic": None,

@@ -408,6 +408,71 @@ class RingAttention:
                      hq=self.hq)
         return dq, dkv
 
+    # ------------------------------------------------------------------ host-buffer entry
+    def forward_host(self, q_host: torch.Tensor, kv_host: torch.Tensor, o_host: torch.Tensor, lse_host: torch.Tensor,
+                     softmax_scale: Optional[float] = None, chunks: int = 8) -> None:
+        """Forward with pinned HOST tensors in and out (same shapes as forward()).
+
+        Single rank, batch 1: the sequence is cut into up to 8 chunks; chunk i is copied in while
+        chunk i-1 is being computed (its queries against K/V chunks 0..i as segments of one launch)
+        and chunk i-2 is copied out, so the PCIe transfers in both directions overlap the kernels.
+        Otherwise: copy in, forward(), copy out.  Returns after the results are in host memory.
+        """
+        dev = torch.device("cuda", torch.cuda.current_device()) if self.ctx is None else self.ctx.device
+        if softmax_scale is None:
+            softmax_scale = self.head_dim ** -0.5
+        L = self.seq_local
+        if not hasattr(self, "_host_bufs"):
+            self._host_bufs = (torch.empty(self.q_shape, dtype=torch.bfloat16, device=dev),
+                               torch.empty(self.kv_shape, dtype=torch.bfloat16, device=dev),
+                               torch.empty(self.q_shape, dtype=torch.bfloat16, device=dev),
+                               torch.empty((self.batch, self.hq, L), dtype=torch.float32, device=dev),
+                               torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
+        q, kv, o, lse, s_in, s_out = self._host_bufs
+        main = torch.cuda.current_stream()
+        n = min(chunks, 8)
+        pipelined = self.world == 1 and self.batch == 1 and L % n == 0 and (L // n) % 128 == 0
+        if not pipelined:
+            q.copy_(q_host, non_blocking=True)
+            kv.copy_(kv_host, non_blocking=True)
+            self.forward(q, kv, o, lse, softmax_scale)
+            o_host.copy_(o, non_blocking=True)
+            lse_host.copy_(lse, non_blocking=True)
+            main.synchronize()
+            return
+        c = L // n
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        arrived = []
+        for i in range(n):
+            rows = slice(i * c, (i + 1) * c)
+            with torch.cuda.stream(s_in):
+                # contiguous pieces only: strided host<->device copies take a slow staged path
+                q[:, rows].copy_(q_host[:, rows], non_blocking=True)
+                kv[0][:, rows].copy_(kv_host[0][:, rows], non_blocking=True)
+                kv[1][:, rows].copy_(kv_host[1][:, rows], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+            arrived.append(ev)
+        for i in range(n):
+            rows = slice(i * c, (i + 1) * c)
+            main.wait_event(arrived[i])
+            if self.causal:
+                segs = [(kv[0][:, j * c:(j + 1) * c], kv[1][:, j * c:(j + 1) * c], j * c) for j in range(i + 1)]
+            else:
+                main.wait_event(arrived[-1])
+                segs = [(kv[0], kv[1], 0)]
+            attn_fwd_segments(q[:, rows], segs, softmax_scale, causal=self.causal, q_off=i * c, out=o[:, rows],
+                              lse=lse[:, :, rows])
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                o_host[:, rows].copy_(o[:, rows], non_blocking=True)
+                if i == n - 1:
+                    lse_host.copy_(lse, non_blocking=True)
+        s_out.synchronize()
+
     def check(self) -> None:
         """Synchronise and raise if a device-side wait timed out."""
         if self.ctx is not None:

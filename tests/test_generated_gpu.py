@@ -75,3 +75,23 @@ def test_ring_over_q_program_two_ranks():
 
 def test_ring_over_q_program_four_ranks():
     _run_forward("gpu_ring_over_q_p4", "flash_attn_expose_reduce", 4, 2, 1024, 4, 4)
+
+
+def test_fused_rewrite_of_the_unsharded_program():
+    """emitter.fuse_generated: same function name and signature, one fused call instead of the loop."""
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200 import emitter
+    from oracle import block
+
+    ns = mb.load_generated(emitter.fuse_generated(golden_text("gpu_ring_p1")))
+    q, k, v, _ = seeded_qkv(4321, 1, 512, 4, 4, 128)
+    kv = torch.stack([k, v]).cuda()
+    for causal in (False, True):
+        o = torch.zeros(1, 512, 4, 128, dtype=torch.bfloat16, device="cuda")
+        lse = torch.zeros(1, 4, 512, device="cuda")
+        ns["flash_attn_pack_kv"](q.cuda(), kv, o, lse, 128 ** -0.5, causal=causal)
+        fo, fl = block.full_attention(q, k, v, 128 ** -0.5, causal=causal)
+        assert (o.float().cpu() - fo.float()).abs().max().item() <= O_TOL
+        assert (lse.cpu() - fl).abs().max().item() <= LSE_TOL
+    with pytest.raises(NotImplementedError):
+        ns["flash_attn_pack_kv"](q.cuda(), kv, o, lse, 1.0, dropout_p=0.1)

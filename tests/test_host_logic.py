@@ -139,3 +139,22 @@ def test_generated_programs_run_on_virtual_ranks_with_oracle_ops():
         for r in range(g["world"]):
             assert torch.allclose(res[r][0], g["t"][f"o_rank{r}"], atol=2e-6)
             assert torch.allclose(res[r][1], g["t"][f"lse_rank{r}"], atol=2e-6)
+
+
+def test_emitter_recognises_kv_rings_and_leaves_other_programs_alone():
+    from mercury_artifact_b200 import emitter
+    from tests.helpers import golden_text
+
+    d = emitter.recognise(golden_text("gpu_double_ring_4x2"))
+    assert d["mesh"] == (4, 2) and d["name"] == "flash_attn_pack_split_kv" and not d["backward"]
+    assert (d["batch"], d["seq_local"], d["hq"], d["hkv"], d["head_dim"]) == (1, 512, 2, 2, 128)
+    d = emitter.recognise(golden_text("gpu_gqa_p2"))
+    assert (d["hq"], d["hkv"], d["mesh"]) == (8, 2, (2,))
+    assert emitter.recognise(golden_text("gpu_bwd_p4"))["backward"] is True
+    for name in ("gpu_ring_over_q_p2", "gpu_tree_p2"):   # other schedules: untouched
+        text = golden_text(name)
+        assert emitter.recognise(text) is None and emitter.fuse_generated(text) == text
+    fused = emitter.fuse_generated(golden_text("gpu_ring_p4"))
+    assert "def flash_attn_pack_kv(q, kv, o, lse, softmax_scale, dropout_p=0, causal=False" in fused
+    assert "for S_kv_ring_idx" not in fused and "RingAttention((4,), 1, 512, 4, 4, 128" in fused
+    compile(fused, "<fused>", "exec")

@@ -112,7 +112,7 @@ def test_ring_backward_two_gpus(causal):
             assert (dkv[1] - gv.chunk(world, 1)[r]).abs().max().item() <= 2e-2
 
 
-def _generated_worker(rank, world, port, ret):
+def _generated_worker(rank, world, port, ret, fused=False):
     """The reference-emitted per-step programs with the real peer transport (SendRecv over NVLink)."""
     import torch.distributed as dist
 
@@ -131,8 +131,14 @@ def _generated_worker(rank, world, port, ret):
     qs, kvs = shard_inputs(q, k, v, world)
     lq, lkv = qs[rank].cuda(), kvs[rank].cuda()
     scale = 128 ** -0.5
-    fwd = mb.load_generated(golden_text("gpu_ring_p2"))["flash_attn_pack_kv"]
-    bwd = mb.load_generated(golden_text("gpu_bwd_p2"))["flash_attn_backward"]
+    if fused:
+        from mercury_artifact_b200 import emitter
+
+        fwd = mb.load_generated(emitter.fuse_generated(golden_text("gpu_ring_p2")))["flash_attn_pack_kv"]
+        bwd = mb.load_generated(emitter.fuse_generated(golden_text("gpu_bwd_p2")))["flash_attn_backward"]
+    else:
+        fwd = mb.load_generated(golden_text("gpu_ring_p2"))["flash_attn_pack_kv"]
+        bwd = mb.load_generated(golden_text("gpu_bwd_p2"))["flash_attn_backward"]
     outs = []
     for _ in range(2):
         o = torch.zeros_like(lq)
@@ -147,7 +153,9 @@ def _generated_worker(rank, world, port, ret):
     dist.destroy_process_group()
 
 
-def test_generated_programs_with_peer_transport_two_gpus():
+@pytest.mark.parametrize("fused", [False, True])
+def test_generated_programs_with_peer_transport_two_gpus(fused):
+    """fused=True: the same emitted programs after emitter.fuse_generated (one launch per rank)."""
     import torch.multiprocessing as mp
     from oracle import block
     from tests.helpers import seeded_qkv
@@ -155,7 +163,7 @@ def test_generated_programs_with_peer_transport_two_gpus():
     world, B, S, H = 2, 1, 1024, 4
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_generated_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    mp.spawn(_generated_worker, args=(world, _free_port(), ret, fused), nprocs=world, join=True)
     q, k, v, do = seeded_qkv(1234, B, S, H, H, 128)
     scale = 128 ** -0.5
     fo, fl = block.full_attention(q, k, v, scale)

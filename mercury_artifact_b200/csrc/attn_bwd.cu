@@ -185,6 +185,61 @@ __device__ __forceinline__ void issue_acc_group(uint32_t d_tmem, uint32_t a_tmem
       : "memory");
 }
 
+#ifndef MB_BWD_PACKED
+#define MB_BWD_PACKED 1
+#endif
+
+// p = exp2(x*c + nlse2), ds = p * (y - delta) for the 32 columns a thread owns; bf16 pairs out.
+// kDkv: the statistics vary per column (read from the stage's shared-memory copy); otherwise they
+// are the thread's row constants.  kMask: columns outside [lo, hi) are invisible (causal diagonal).
+template <bool kDkv, bool kMask>
+__device__ __forceinline__ void ew_compute(const uint32_t (&xr)[32], const uint32_t (&yr)[32], uint32_t (&pk)[16],
+                                           uint32_t (&dk)[16], float c, const float* nl_col, const float* d_col,
+                                           float row_nl, float row_d, int lo, int hi) {
+#if MB_BWD_PACKED
+  const uint64_t c2 = pack2(c, c);
+  const uint64_t row_nl2 = pack2(row_nl, row_nl), row_d2 = pack2(row_d, row_d);
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    const uint64_t nl2 = kDkv ? *reinterpret_cast<const uint64_t*>(nl_col + e) : row_nl2;
+    const uint64_t d2 = kDkv ? *reinterpret_cast<const uint64_t*>(d_col + e) : row_d2;
+    const uint64_t t2 = fma2(pack2(__uint_as_float(xr[e]), __uint_as_float(xr[e + 1])), c2, nl2);
+    float t0, t1;
+    unpack2(t2, t0, t1);
+    float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+    if (kMask) {
+      if (e < lo || e >= hi) p0 = 0.f;
+      if (e + 1 < lo || e + 1 >= hi) p1 = 0.f;
+    }
+    const uint64_t s2 = mul2(pack2(p0, p1), sub2(pack2(__uint_as_float(yr[e]), __uint_as_float(yr[e + 1])), d2));
+    float s0, s1;
+    unpack2(s2, s0, s1);
+    pk[e >> 1] = pack_bf16x2(p0, p1);
+    dk[e >> 1] = pack_bf16x2(s0, s1);
+  }
+#else
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    float nl0 = row_nl, nl1 = row_nl, d0 = row_d, d1 = row_d;
+    if (kDkv) {
+      const float2 nv = *reinterpret_cast<const float2*>(nl_col + e);
+      const float2 dv = *reinterpret_cast<const float2*>(d_col + e);
+      nl0 = nv.x; nl1 = nv.y; d0 = dv.x; d1 = dv.y;
+    }
+    float p0 = fast_exp2(fmaf(__uint_as_float(xr[e]), c, nl0));
+    float p1 = fast_exp2(fmaf(__uint_as_float(xr[e + 1]), c, nl1));
+    if (kMask) {
+      if (e < lo || e >= hi) p0 = 0.f;
+      if (e + 1 < lo || e + 1 >= hi) p1 = 0.f;
+    }
+    const float s0 = p0 * (__uint_as_float(yr[e]) - d0);
+    const float s1 = p1 * (__uint_as_float(yr[e + 1]) - d1);
+    pk[e >> 1] = pack_bf16x2(p0, p1);
+    dk[e >> 1] = pack_bf16x2(s0, s1);
+  }
+#endif
+}
+
 template <int kDummy>
 __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps maps, const BwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -359,14 +414,12 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
     bool ok = true;
 
     const bool dkv_mode = a.mode_dkv != 0;
-    const uint64_t c2 = pack2(a.scale_log2, a.scale_log2);
-    uint64_t row_nl2 = 0, row_d2 = 0;
+    float row_nl = 0.f, row_d = 0.f;
     if (!dkv_mode) {
       const int r = min(own0 + row, a.own_stat_pad - 1);
       const long long soff = ((long long)b * a.Hq + h_own) * a.own_stat_pad + r;
-      const float nl = a.own_lse2[soff], dl = a.own_delta[soff];
-      row_nl2 = pack2(nl, nl);
-      row_d2 = pack2(dl, dl);
+      row_nl = a.own_lse2[soff];
+      row_d = a.own_delta[soff];
     }
 
     int t = 0;
@@ -399,27 +452,15 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
           }
           const bool need_mask = __any_sync(0xffffffffu, lo > 0 || hi < 32);  // only steps crossing the diagonal
           const float* stats = reinterpret_cast<const float*>(sStage + stage * kBwdStageBytes + 2 * kStrTileBytes);
-          const uint64_t* nl_col = reinterpret_cast<const uint64_t*>(stats + half * 32);            // -lse2 pairs
-          const uint64_t* d_col = reinterpret_cast<const uint64_t*>(stats + kStrRows + half * 32);  // delta pairs
+          const float* nl_col = stats + half * 32;            // -lse2 of my 32 columns (dKV mode)
+          const float* d_col = stats + kStrRows + half * 32;  // delta of my 32 columns
           uint32_t pk[16], dk[16];
-          // Packed pairs: p = exp2(x*c + nlse2), ds = p * (y - delta); two elements per FMA-pipe instruction.
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const uint64_t nl2 = dkv_mode ? nl_col[e >> 1] : row_nl2;
-            const uint64_t d2 = dkv_mode ? d_col[e >> 1] : row_d2;
-            const uint64_t t2 = fma2(pack2(__uint_as_float(xr[e]), __uint_as_float(xr[e + 1])), c2, nl2);
-            float t0, t1;
-            unpack2(t2, t0, t1);
-            float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-            if (need_mask) {
-              if (e < lo || e >= hi) p0 = 0.f;
-              if (e + 1 < lo || e + 1 >= hi) p1 = 0.f;
-            }
-            const uint64_t s2 = mul2(pack2(p0, p1), sub2(pack2(__uint_as_float(yr[e]), __uint_as_float(yr[e + 1])), d2));
-            float s0, s1;
-            unpack2(s2, s0, s1);
-            pk[e >> 1] = pack_bf16x2(p0, p1);
-            dk[e >> 1] = pack_bf16x2(s0, s1);
+          if (dkv_mode) {
+            if (need_mask) ew_compute<true, true>(xr, yr, pk, dk, a.scale_log2, nl_col, d_col, 0.f, 0.f, lo, hi);
+            else ew_compute<true, false>(xr, yr, pk, dk, a.scale_log2, nl_col, d_col, 0.f, 0.f, lo, hi);
+          } else {
+            if (need_mask) ew_compute<false, true>(xr, yr, pk, dk, a.scale_log2, nl_col, d_col, row_nl, row_d, lo, hi);
+            else ew_compute<false, false>(xr, yr, pk, dk, a.scale_log2, nl_col, d_col, row_nl, row_d, lo, hi);
           }
           tmem_st16(tx + half * 32, pk);
           tmem_st16(ty + half * 32, dk);

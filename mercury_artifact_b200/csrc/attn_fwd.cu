@@ -13,169 +13,46 @@
 // Roles inside the CTA (384 threads, three warpgroups):
 //   warps 0-3  softmax + epilogue for query tile 0 (one thread per row)
 //   warps 4-7  softmax + epilogue for query tile 1
-//   warp  8    tcgen05.mma issuer for query tile 0 (lane 0) and tensor-memory owner
+//   warp  8    tcgen05.mma issuer for query tile 0 and tensor-memory owner
 //   warp  9    TMA loader (lane 0)
-//   warp 10    tcgen05.mma issuer for query tile 1 (lane 0); one issuing thread for both tiles
+//   warp 10    tcgen05.mma issuer for query tile 1; one issuing thread for both tiles
 //              cannot feed the tensor pipe (measured ~95 cycles per MMA instruction issued)
 //   warp 11    idle; the auxiliary warpgroup's registers go to the softmax warps (setmaxnreg)
-// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  The
-// bf16 probabilities overwrite the first 64 columns of their score tile and are
-// consumed from tensor memory as the A operand of the P.V product.
-#include "mb_common.cuh"
-#include "mb_host.h"
+//
+// Tensor memory (512 columns): S | P0 | P1 | O0 | O1 = 128 + 64 + 64 + 128 + 128.  There is ONE
+// fp32 score region, used by the two query tiles in turn: a softmax thread copies its whole score
+// row into registers as soon as the tile is complete and hands the region on, so the next Q.K^T
+// product (of the other query tile) starts while this tile is still in its exponentials.  The bf16
+// probabilities have a region of their own per query tile, so that the next score tile of a query
+// tile does not have to wait for its P.V product either.  The per-tile dependency chain is then the
+// softmax alone; with the two warpgroups taking turns in the exp2 phase the 16-lane MUFU never
+// idles, and both products of one tile run under the other tile's exponentials.
+//
+// K/V tiles are loaded, and consumed by both issuing warps, in the order K0 K1 V0 K2 V1 K3 V2 ...:
+// the score product of iteration g+1 is issued before the P.V product of iteration g.
+#include "attn_fwd_common.cuh"
 
 namespace mb {
 
-constexpr int kBM = 128;            // query rows per tile
-constexpr int kBN = 128;            // keys per tile
-constexpr int kD = 128;             // head dimension
-constexpr int kTileBytes = kBN * kD * 2;  // 32 KiB, stored as two 64-column halves
-constexpr int kHalfBytes = kTileBytes / 2;
-constexpr int kFwdStages = 4;
-constexpr int kFwdThreads = 384;  // 8 softmax warps + one auxiliary warpgroup (MMA, loader, 2 idle)
-constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: tolerate p up to 2^8
-#ifndef MB_POLY_EVERY
-#define MB_POLY_EVERY 0
-#endif
-constexpr int kPolyEvery = MB_POLY_EVERY;
-#ifndef MB_TAKE_TURNS
-#define MB_TAKE_TURNS 1
-#endif
-constexpr bool kTakeTurns = MB_TAKE_TURNS != 0;  // every n-th pair of exponentials goes to the FMA pipe (0: none)
-
-// Optional timeline capture for kernel tuning (compiled in only with -DMB_TRACE): CTA (0,0,0)
-// records clock64() at fixed points of the first kTraceIters K/V iterations.
-#ifdef MB_TRACE
-constexpr int kTraceIters = 24;
-__device__ long long g_fwd_trace[3][kTraceIters][12];
-#define MB_TRACE_AT(role, it, ev)                                                              \
-  do {                                                                                         \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < kTraceIters)           \
-      g_fwd_trace[role][it][ev] = clock64();                                                   \
-  } while (0)
-#else
-#define MB_TRACE_AT(role, it, ev) \
-  do {                            \
-  } while (0)
-#endif
-
-struct FwdMaps {
-  CUtensorMap q;
-  CUtensorMap k[MB_MAX_SEGMENTS];
-  CUtensorMap v[MB_MAX_SEGMENTS];
+// Position in the CTA's list of K/V tiles: every tile of every segment that at least one of the two
+// query tiles takes part in, in segment order.
+struct TileIter {
+  int s, jt;
 };
-
-struct FwdArgs {
-  __nv_bfloat16* o;
-  long long o_sb, o_ss, o_sh;  // element strides
-  float* lse;                  // [B, Hq, Sq], row-contiguous
-  long long lse_sb, lse_sh;    // element strides of lse
-  int B, Sq, Hq, group;
-  int nseg;
-  int seg_sk[MB_MAX_SEGMENTS];
-  int seg_koff[MB_MAX_SEGMENTS];
-  const int* seg_flag[MB_MAX_SEGMENTS];  // arrival flag of a staged shard (nullptr: already in place)
-  int seg_flag_value[MB_MAX_SEGMENTS];
-  int q_off;
-  int causal;
-  float scale;       // softmax scale
-  float scale_log2;  // softmax scale * log2(e)
-  int* status;
-};
-
-struct FwdSmem {
-  uint64_t q_full;
-  uint64_t kv_full[kFwdStages];
-  uint64_t kv_empty[kFwdStages];
-  uint64_t s_full[2];
-  uint64_t p_full[2][2];  // [query tile][half of the keys of a K/V tile]
-  uint64_t o_full[2];
-  uint64_t turn[2];  // exp2-phase token passed between the two softmax warpgroups
-  uint64_t drain;
-  uint32_t tmem_base;
-  int abort_word;
-  int n_tiles[2][MB_MAX_SEGMENTS];  // K/V tiles of each segment that query tile i takes part in
-};
-
-constexpr int kFwdSmemBytes = 2 * kTileBytes + kFwdStages * kTileBytes + 1024 /*alignment slack*/ + 1024 /*FwdSmem*/;
-static_assert(sizeof(FwdSmem) <= 1024, "control block too large");
-
-// Number of K/V tiles of a segment that a query tile starting at row q0 can see.
-__device__ __forceinline__ int visible_tiles(int q0, int Sq, int q_off, int causal, int sk, int koff) {
-  if (q0 >= Sq || sk <= 0) return 0;
-  int nt = (sk + kBN - 1) / kBN;
-  if (causal) {
-    int last_row = min(q0 + kBM - 1, Sq - 1);
-    long long max_k = (long long)q_off + last_row - koff;  // largest visible local key index
-    if (max_k < 0) return 0;
-    long long lim = max_k / kBN + 1;
-    if (lim < nt) nt = (int)lim;
+__device__ __forceinline__ int seg_tiles(const FwdSmem* ctl, int s) {
+  return max(ctl->n_tiles[0][s], ctl->n_tiles[1][s]);
+}
+__device__ __forceinline__ TileIter iter_first(const FwdSmem* ctl, int nseg) {
+  TileIter it{0, 0};
+  while (it.s < nseg && seg_tiles(ctl, it.s) == 0) ++it.s;
+  return it;
+}
+__device__ __forceinline__ void iter_next(const FwdSmem* ctl, int nseg, TileIter& it) {
+  if (++it.jt >= seg_tiles(ctl, it.s)) {
+    it.jt = 0;
+    ++it.s;
+    while (it.s < nseg && seg_tiles(ctl, it.s) == 0) ++it.s;
   }
-  return nt;
-}
-
-// Called by a converged warp; one elected lane issues.  Keeping the warp converged lets the
-// descriptor arithmetic run on the uniform datapath (tcgen05.mma takes its descriptors from uniform
-// registers), and one asm block per group of MMAs keeps the instruction count low: the
-// shared-memory descriptors of the k-steps differ from the first one only in the start-address
-// field (bits 0-13, in 16-byte units), so each is one 64-bit add away.
-
-// S = Q K^T for one 128x128 tile: 8 MMAs (K = 16 each) over the two 64-column halves of Q and K.
-// Offsets in 16-byte units: k-step k -> (k >> 2) * (kHalfBytes / 16) + (k & 3) * 2.
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint64_t q_desc, uint64_t k_desc, uint32_t idesc) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred pe, pt, pf;\n\t"
-      ".reg .b64 qa, kb;\n\t"
-      "elect.sync _|pe, 0xffffffff;\n\t"
-      "setp.eq.u32 pt, 0, 0;\n\t"
-      "setp.ne.u32 pf, 0, 0;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
-      "add.s64 qa, %1, 2;\n\t add.s64 kb, %2, 2;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
-      "add.s64 qa, %1, 4;\n\t add.s64 kb, %2, 4;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
-      "add.s64 qa, %1, 6;\n\t add.s64 kb, %2, 6;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
-      "add.s64 qa, %1, 1024;\n\t add.s64 kb, %2, 1024;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
-      "add.s64 qa, %1, 1026;\n\t add.s64 kb, %2, 1026;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
-      "add.s64 qa, %1, 1028;\n\t add.s64 kb, %2, 1028;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
-      "add.s64 qa, %1, 1030;\n\t add.s64 kb, %2, 1030;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
-      "}"
-      :
-      : "r"(d_tmem), "l"(q_desc), "l"(k_desc), "r"(idesc)
-      : "memory");
-}
-static_assert(kHalfBytes / 16 == 1024, "issue_qk hard-codes the half-tile pitch");
-
-// O (+)= P V for 64 keys (half of a K/V tile): 4 MMAs of 16 keys.  P comes from tensor memory
-// (8 columns per 16 keys); V is read MN-major, 16 keys = 2048 bytes = 128 descriptor units apart.
-// p_tmem and v_desc already point at the half to process.
-__device__ __forceinline__ void issue_pv_half(uint32_t d_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t idesc,
-                                              uint32_t accumulate_first) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred pe, pt, p0;\n\t"
-      ".reg .b64 vb;\n\t"
-      ".reg .b32 pa;\n\t"
-      "elect.sync _|pe, 0xffffffff;\n\t"
-      "setp.eq.u32 pt, 0, 0;\n\t"
-      "setp.ne.u32 p0, %4, 0;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
-      "add.s64 vb, %2, 128;\n\t add.u32 pa, %1, 8;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
-      "add.s64 vb, %2, 256;\n\t add.u32 pa, %1, 16;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
-      "add.s64 vb, %2, 384;\n\t add.u32 pa, %1, 24;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
-      "}"
-      :
-      : "r"(d_tmem), "r"(p_tmem), "l"(v_desc), "r"(idesc), "r"(accumulate_first)
-      : "memory");
 }
 
 // 160 registers/thread at launch (not the 168 that 384 threads would allow): the few warps' worth
@@ -213,6 +90,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
       mbar_init(&ctl->o_full[i], 1);
       mbar_init(&ctl->turn[i], 128);
     }
+    mbar_init(&ctl->s_free, 4);
     mbar_init(&ctl->drain, 2);
     ctl->abort_word = 0;
     for (int i = 0; i < 2; ++i)
@@ -230,7 +108,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
   __syncthreads();
   tc_fence_after();
 
-  const uint32_t tmem = ctl->tmem_base;  // columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512)
+  const uint32_t tmem = ctl->tmem_base;  // columns: S [0,128) P0 [128,192) P1 [192,256) O0 [256,384) O1 [384,512)
 
   bool any_work = false;
   for (int s = 0; s < a.nseg; ++s) any_work |= (ctl->n_tiles[0][s] | ctl->n_tiles[1][s]) != 0;
@@ -254,30 +132,39 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
       }
       int n = 0;
       bool ok = true;
-      for (int s = 0; s < a.nseg && ok; ++s) {
-        const int nmax = max(ctl->n_tiles[0][s], ctl->n_tiles[1][s]);
-        if (nmax > 0 && a.seg_flag[s] != nullptr) {
+      // One K or V tile into the next stage of the ring.
+      auto load_tile = [&](int which, const TileIter& it) {
+        if (which == 0 && it.jt == 0 && a.seg_flag[it.s] != nullptr) {
           // The shard is being staged by another stream: wait (bounded) for its arrival flag,
           // then order the TMA reads (async proxy) after the flag read.
-          ok = flag_wait_ge(a.seg_flag[s], a.seg_flag_value[s], abort_word, MB_ERR_TIMEOUT_SEGMENT);
+          ok = flag_wait_ge(a.seg_flag[it.s], a.seg_flag_value[it.s], abort_word, MB_ERR_TIMEOUT_SEGMENT);
           asm volatile("fence.proxy.async;" ::: "memory");
+          if (!ok) return;
         }
-        for (int jt = 0; jt < nmax && ok; ++jt) {
-          for (int which = 0; which < 2; ++which) {
-            const int stage = n % kFwdStages;
-            const int round = n / kFwdStages;
-            if (round > 0 && !mbar_wait(&ctl->kv_empty[stage], (round - 1) & 1, abort_word, MB_ERR_TIMEOUT_KV_EMPTY)) {
-              ok = false;
-              break;
-            }
-            const CUtensorMap* map = which ? &maps.v[s] : &maps.k[s];
-            uint8_t* dst = sKV + stage * kTileBytes;
-            mbar_expect_tx(&ctl->kv_full[stage], kTileBytes);
-            tma_load_4d(dst, map, &ctl->kv_full[stage], 0, hkv, jt * kBN, b);
-            tma_load_4d(dst + kHalfBytes, map, &ctl->kv_full[stage], 64, hkv, jt * kBN, b);
-            ++n;
-          }
+        const int stage = n % kFwdStages;
+        const int round = n / kFwdStages;
+        if (round > 0 && !mbar_wait(&ctl->kv_empty[stage], (round - 1) & 1, abort_word, MB_ERR_TIMEOUT_KV_EMPTY)) {
+          ok = false;
+          return;
         }
+        const CUtensorMap* map = which ? &maps.v[it.s] : &maps.k[it.s];
+        uint8_t* dst = sKV + stage * kTileBytes;
+        mbar_expect_tx(&ctl->kv_full[stage], kTileBytes);
+        tma_load_4d(dst, map, &ctl->kv_full[stage], 0, hkv, it.jt * kBN, b);
+        tma_load_4d(dst + kHalfBytes, map, &ctl->kv_full[stage], 64, hkv, it.jt * kBN, b);
+        ++n;
+      };
+      TileIter nxt = iter_first(ctl, a.nseg);
+      TileIter cur = nxt;
+      if (nxt.s < a.nseg) {
+        load_tile(0, nxt);
+        iter_next(ctl, a.nseg, nxt);
+      }
+      while (ok && cur.s < a.nseg) {
+        if (nxt.s < a.nseg) load_tile(0, nxt);
+        if (ok) load_tile(1, cur);
+        cur = nxt;
+        if (nxt.s < a.nseg) iter_next(ctl, a.nseg, nxt);
       }
       if (!ok) {
         // Give copies already in flight a bounded chance to land before the CTA exits.
@@ -292,7 +179,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     }
   } else if (warp == 8 || warp == 10) {
     // ------------------------------------------- MMA issuers: warp 8 -> query tile 0, warp 10 -> tile 1
-    // Each walks every K/V stage in load order (K0 V0 K1 V1 ...): it waits for the stage, uses it if
+    // Each walks every K/V stage in load order (K0 K1 V0 K2 V1 ...): it waits for the stage, uses it if
     // its query tile takes part in that K/V tile, and arrives on the stage's "empty" barrier either
     // way, so the barrier always sees one arrival per issuing warp.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
@@ -300,68 +187,83 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
       const int i = (warp - 8) >> 1;
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kBM, kBN, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kBM, kD, false, true);
-      const uint32_t tSi = tmem + i * 128, tOi = tmem + 256 + i * 128;
+      const uint32_t tS = tmem, tPi = tmem + 128 + i * 64, tOi = tmem + 256 + i * 128;
       const uint64_t q_desc = umma_smem_desc(smem_u32(sQ) + i * kTileBytes, 16, 1024);
       const uint64_t k_desc0 = umma_smem_desc(smem_u32(sKV), 16, 1024);          // K-major view of stage 0
       const uint64_t v_desc0 = umma_smem_desc(smem_u32(sKV), kHalfBytes, 1024);  // MN-major view of stage 0
       constexpr uint32_t kStageUnits = kTileBytes / 16;
       uint64_t* p_full0 = &ctl->p_full[i][0];
       uint64_t* p_full1 = &ctl->p_full[i][1];
-      int cnt = 0;   // tiles this query tile has taken part in
+      int cnt = 0;   // P.V products of this query tile issued so far
       int n = 0;     // next stage index in load order
+      int seq = 0;   // uses of the score region so far, by either query tile
       bool ok = mbar_wait_warp(&ctl->q_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
       bool first = true;
-      for (int s = 0; s < a.nseg && ok; ++s) {
-        const int mine = ctl->n_tiles[i][s];
-        const int nmax = max(ctl->n_tiles[0][s], ctl->n_tiles[1][s]);
-        for (int jt = 0; jt < nmax; ++jt) {
-          const bool part = jt < mine;
-          // ---- K tile of this iteration
-          {
-            const int stage = n % kFwdStages;
-            ok = mbar_wait_warp(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
-            if (!ok) break;
-            if (part) {
-              tc_fence_after();
-              issue_qk(tSi, q_desc, k_desc0 + stage * kStageUnits, idesc_qk);
-              umma_commit_elect(&ctl->s_full[i]);
-              umma_commit_elect(&ctl->kv_empty[stage]);
-              MB_TRACE_AT(2, cnt, i * 6 + 5);
-            } else {
-              mbar_arrive_elect(&ctl->kv_empty[stage]);
-            }
-            ++n;
+
+      // K stage: S = Q K^T into the shared score region, once its previous user has copied its scores out.
+      auto do_k = [&](const TileIter& it) {
+        const int stage = n % kFwdStages;
+        ok = mbar_wait_warp(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+        if (!ok) return;
+        const int part0 = it.jt < ctl->n_tiles[0][it.s], part1 = it.jt < ctl->n_tiles[1][it.s];
+        if (i ? part1 : part0) {
+          const int my_use = seq + (i ? part0 : 0);
+          if (my_use > 0) {
+            ok = mbar_wait_warp(&ctl->s_free, (my_use - 1) & 1, abort_word, MB_ERR_TIMEOUT_S);
+            if (!ok) return;
           }
-          // ---- V tile of this iteration
-          {
-            const int stage = n % kFwdStages;
-            ok = mbar_wait_warp(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
-            if (!ok) break;
-            if (part) {
-              const uint64_t v_desc = v_desc0 + stage * kStageUnits;
-              MB_TRACE_AT(2, cnt, i * 6 + 0);
-              ok = mbar_wait_warp(p_full0, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
-              if (!ok) break;
-              MB_TRACE_AT(2, cnt, i * 6 + 1);
-              tc_fence_after();
-              issue_pv_half(tOi, tSi, v_desc, idesc_pv, first ? 0u : 1u);
-              MB_TRACE_AT(2, cnt, i * 6 + 2);
-              ok = mbar_wait_warp(p_full1, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
-              if (!ok) break;
-              MB_TRACE_AT(2, cnt, i * 6 + 3);
-              tc_fence_after();
-              issue_pv_half(tOi, tSi + 32, v_desc + 4 * 128, idesc_pv, 1u);
-              umma_commit_elect(&ctl->o_full[i]);
-              umma_commit_elect(&ctl->kv_empty[stage]);
-              MB_TRACE_AT(2, cnt, i * 6 + 4);
-              first = false;
-              ++cnt;
-            } else {
-              mbar_arrive_elect(&ctl->kv_empty[stage]);
-            }
-            ++n;
-          }
+          tc_fence_after();
+          issue_qk(tS, q_desc, k_desc0 + stage * kStageUnits, idesc_qk);
+          umma_commit_elect(&ctl->s_full[i]);
+          umma_commit_elect(&ctl->kv_empty[stage]);
+          MB_TRACE_AT(2, cnt, i * 6 + 5);
+        } else {
+          mbar_arrive_elect(&ctl->kv_empty[stage]);
         }
+        seq += part0 + part1;
+        ++n;
+      };
+      // V stage: O (+)= P V, in two halves as the probabilities arrive.
+      auto do_v = [&](const TileIter& it) {
+        const int stage = n % kFwdStages;
+        ok = mbar_wait_warp(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+        if (!ok) return;
+        if (it.jt < ctl->n_tiles[i][it.s]) {
+          const uint64_t v_desc = v_desc0 + stage * kStageUnits;
+          MB_TRACE_AT(2, cnt, i * 6 + 0);
+          ok = mbar_wait_warp(p_full0, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+          if (!ok) return;
+          MB_TRACE_AT(2, cnt, i * 6 + 1);
+          tc_fence_after();
+          issue_pv_half(tOi, tPi, v_desc, idesc_pv, first ? 0u : 1u);
+          MB_TRACE_AT(2, cnt, i * 6 + 2);
+          ok = mbar_wait_warp(p_full1, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+          if (!ok) return;
+          MB_TRACE_AT(2, cnt, i * 6 + 3);
+          tc_fence_after();
+          issue_pv_half(tOi, tPi + 32, v_desc + 4 * 128, idesc_pv, 1u);
+          umma_commit_elect(&ctl->o_full[i]);
+          umma_commit_elect(&ctl->kv_empty[stage]);
+          MB_TRACE_AT(2, cnt, i * 6 + 4);
+          first = false;
+          ++cnt;
+        } else {
+          mbar_arrive_elect(&ctl->kv_empty[stage]);
+        }
+        ++n;
+      };
+
+      TileIter nxt = iter_first(ctl, a.nseg);
+      TileIter cur = nxt;
+      if (ok && nxt.s < a.nseg) {
+        do_k(nxt);
+        iter_next(ctl, a.nseg, nxt);
+      }
+      while (ok && cur.s < a.nseg) {
+        if (nxt.s < a.nseg) do_k(nxt);
+        if (ok) do_v(cur);
+        cur = nxt;
+        if (nxt.s < a.nseg) iter_next(ctl, a.nseg, nxt);
       }
       if (!ok) {
         // Let tensor-core work already issued finish (bounded) before tensor memory is released.
@@ -380,7 +282,8 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     const int i = warp >> 2;                    // query tile
     const int row = ((warp & 3) << 5) | lane;   // row inside the tile == tensor-memory lane
     const uint32_t lane_field = static_cast<uint32_t>((warp & 3) << 5) << 16;
-    const uint32_t tSi = tmem + i * 128 + lane_field;
+    const uint32_t tS = tmem + lane_field;
+    const uint32_t tPi = tmem + 128 + i * 64 + lane_field;
     const uint32_t tOi = tmem + 256 + i * 128 + lane_field;
     const int qrow = q0 + i * kBM + row;        // row inside this rank's Q
     const int qpos = a.q_off + qrow;            // global position used by the causal rule
@@ -403,11 +306,14 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
         if (row == 0) MB_TRACE_AT(i, cnt, 1);
         tc_fence_after();
         uint32_t sr[4][32];
-        tmem_ld32(tSi + 0, sr[0]);
-        tmem_ld32(tSi + 32, sr[1]);
-        tmem_ld32(tSi + 64, sr[2]);
-        tmem_ld32(tSi + 96, sr[3]);
+        tmem_ld32(tS + 0, sr[0]);
+        tmem_ld32(tS + 32, sr[1]);
+        tmem_ld32(tS + 64, sr[2]);
+        tmem_ld32(tS + 96, sr[3]);
         tmem_wait_ld();
+        // The scores are in registers: hand the score region to its next user.
+        tc_fence_before();
+        mbar_arrive_elect(&ctl->s_free);
         if (row == 0) MB_TRACE_AT(i, cnt, 2);
 
         // masking: only tiles that cross the segment end or the causal diagonal
@@ -438,13 +344,14 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
         if (cnt == 0) {
           m_ref = m_tile;
         } else {
+          // The previous P.V product of this query tile must be complete before its probabilities
+          // are overwritten, and before O is rescaled.
+          ok = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O);
+          if (!ok) break;
+          tc_fence_after();
           const float m_new = fmaxf(m_ref, m_tile);
           const bool need = (m_new - m_ref) * a.scale_log2 > kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
-            // O of the previous step must be complete before it is rescaled.
-            ok = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O);
-            if (!ok) break;
-            tc_fence_after();
             const float f = need ? fast_exp2((m_ref - m_new) * a.scale_log2) : 1.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -508,7 +415,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
             mbar_arrive(&ctl->turn[i ^ 1]);  // my exponentials are issued: the other warpgroup's turn
             ++shared_cnt;
           }
-          tmem_st32(tSi + half * 32, pk);
+          tmem_st32(tPi + half * 32, pk);
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(&ctl->p_full[i][half]);

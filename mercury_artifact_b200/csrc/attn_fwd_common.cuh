@@ -1,0 +1,163 @@
+// Pieces shared by the forward attention kernels: tile geometry, kernel arguments, the causal
+// tile count, and the MMA group issue helpers.
+#pragma once
+
+#include "mb_common.cuh"
+#include "mb_host.h"
+
+namespace mb {
+
+constexpr int kBM = 128;            // query rows per tile
+constexpr int kBN = 128;            // keys per tile
+constexpr int kD = 128;             // head dimension
+constexpr int kTileBytes = kBN * kD * 2;  // 32 KiB, stored as two 64-column halves
+constexpr int kHalfBytes = kTileBytes / 2;
+constexpr int kFwdStages = 4;
+constexpr int kFwdThreads = 384;  // 8 softmax warps + one auxiliary warpgroup (MMA, loader, 2 idle)
+constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: tolerate p up to 2^8
+#ifndef MB_POLY_EVERY
+#define MB_POLY_EVERY 0
+#endif
+constexpr int kPolyEvery = MB_POLY_EVERY;  // every n-th pair of exponentials goes to the FMA pipe (0: none)
+#ifndef MB_TAKE_TURNS
+#define MB_TAKE_TURNS 1
+#endif
+constexpr bool kTakeTurns = MB_TAKE_TURNS != 0;  // the softmax warpgroups alternate in the exp2 phase
+
+// Optional timeline capture for kernel tuning (compiled in only with -DMB_TRACE): CTA (0,0,0)
+// records clock64() at fixed points of the first kTraceIters K/V iterations.
+#ifdef MB_TRACE
+constexpr int kTraceIters = 24;
+static __device__ long long g_fwd_trace[3][kTraceIters][12];
+#define MB_TRACE_AT(role, it, ev)                                                              \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < kTraceIters)           \
+      g_fwd_trace[role][it][ev] = clock64();                                                   \
+  } while (0)
+#else
+#define MB_TRACE_AT(role, it, ev) \
+  do {                            \
+  } while (0)
+#endif
+
+struct FwdMaps {
+  CUtensorMap q;
+  CUtensorMap k[MB_MAX_SEGMENTS];
+  CUtensorMap v[MB_MAX_SEGMENTS];
+};
+
+struct FwdArgs {
+  __nv_bfloat16* o;
+  long long o_sb, o_ss, o_sh;  // element strides
+  float* lse;                  // [B, Hq, Sq], row-contiguous
+  long long lse_sb, lse_sh;    // element strides of lse
+  int B, Sq, Hq, group;
+  int nseg;
+  int seg_sk[MB_MAX_SEGMENTS];
+  int seg_koff[MB_MAX_SEGMENTS];
+  const int* seg_flag[MB_MAX_SEGMENTS];  // arrival flag of a staged shard (nullptr: already in place)
+  int seg_flag_value[MB_MAX_SEGMENTS];
+  int q_off;
+  int causal;
+  float scale;       // softmax scale
+  float scale_log2;  // softmax scale * log2(e)
+  int* status;
+};
+
+struct FwdSmem {
+  uint64_t q_full;
+  uint64_t kv_full[kFwdStages];
+  uint64_t kv_empty[kFwdStages];
+  uint64_t s_full[2];
+  uint64_t s_free;        // the one score region is handed from user to user (4 warp arrivals per use)
+  uint64_t p_full[2][2];  // [query tile][half of the keys of a K/V tile]
+  uint64_t o_full[2];
+  uint64_t turn[2];  // exp2-phase token passed between the two softmax warpgroups
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_word;
+  int n_tiles[2][MB_MAX_SEGMENTS];  // K/V tiles of each segment that query tile i takes part in
+};
+
+constexpr int kFwdSmemBytes = 2 * kTileBytes + kFwdStages * kTileBytes + 1024 /*alignment slack*/ + 1024 /*FwdSmem*/;
+static_assert(sizeof(FwdSmem) <= 1024, "control block too large");
+
+// Number of K/V tiles of a segment that a query tile starting at row q0 can see.
+__device__ __forceinline__ int visible_tiles(int q0, int Sq, int q_off, int causal, int sk, int koff) {
+  if (q0 >= Sq || sk <= 0) return 0;
+  int nt = (sk + kBN - 1) / kBN;
+  if (causal) {
+    int last_row = min(q0 + kBM - 1, Sq - 1);
+    long long max_k = (long long)q_off + last_row - koff;  // largest visible local key index
+    if (max_k < 0) return 0;
+    long long lim = max_k / kBN + 1;
+    if (lim < nt) nt = (int)lim;
+  }
+  return nt;
+}
+
+// Called by a converged warp; one elected lane issues.  Keeping the warp converged lets the
+// descriptor arithmetic run on the uniform datapath (tcgen05.mma takes its descriptors from uniform
+// registers), and one asm block per group of MMAs keeps the instruction count low: the
+// shared-memory descriptors of the k-steps differ from the first one only in the start-address
+// field (bits 0-13, in 16-byte units), so each is one 64-bit add away.
+
+// S = Q K^T for one 128x128 tile: 8 MMAs (K = 16 each) over the two 64-column halves of Q and K.
+// Offsets in 16-byte units: k-step k -> (k >> 2) * (kHalfBytes / 16) + (k & 3) * 2.
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint64_t q_desc, uint64_t k_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe, pt, pf;\n\t"
+      ".reg .b64 qa, kb;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.eq.u32 pt, 0, 0;\n\t"
+      "setp.ne.u32 pf, 0, 0;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+      "add.s64 qa, %1, 2;\n\t add.s64 kb, %2, 2;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 4;\n\t add.s64 kb, %2, 4;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 6;\n\t add.s64 kb, %2, 6;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 1024;\n\t add.s64 kb, %2, 1024;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 1026;\n\t add.s64 kb, %2, 1026;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 1028;\n\t add.s64 kb, %2, 1028;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "add.s64 qa, %1, 1030;\n\t add.s64 kb, %2, 1030;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], qa, kb, %3, pt;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "l"(q_desc), "l"(k_desc), "r"(idesc)
+      : "memory");
+}
+static_assert(kHalfBytes / 16 == 1024, "issue_qk hard-codes the half-tile pitch");
+
+// O (+)= P V for 64 keys (half of a K/V tile): 4 MMAs of 16 keys.  P comes from tensor memory
+// (8 columns per 16 keys); V is read MN-major, 16 keys = 2048 bytes = 128 descriptor units apart.
+// p_tmem and v_desc already point at the half to process.
+__device__ __forceinline__ void issue_pv_half(uint32_t d_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t idesc,
+                                              uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe, pt, p0;\n\t"
+      ".reg .b64 vb;\n\t"
+      ".reg .b32 pa;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.eq.u32 pt, 0, 0;\n\t"
+      "setp.ne.u32 p0, %4, 0;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "add.s64 vb, %2, 128;\n\t add.u32 pa, %1, 8;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
+      "add.s64 vb, %2, 256;\n\t add.u32 pa, %1, 16;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
+      "add.s64 vb, %2, 384;\n\t add.u32 pa, %1, 24;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], vb, %3, pt;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "r"(p_tmem), "l"(v_desc), "r"(idesc), "r"(accumulate_first)
+      : "memory");
+}
+
+}  // namespace mb

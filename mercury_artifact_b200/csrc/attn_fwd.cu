@@ -13,10 +13,9 @@
 // Roles inside the CTA (384 threads, three warpgroups):
 //   warps 0-3  softmax + epilogue for query tile 0 (one thread per row)
 //   warps 4-7  softmax + epilogue for query tile 1
-//   warp  8    tcgen05.mma issuer for query tile 0 and tensor-memory owner
+//   warp  8    tcgen05.mma issuer for the Q.K^T products of both query tiles, tensor-memory owner
 //   warp  9    TMA loader (lane 0)
-//   warp 10    tcgen05.mma issuer for query tile 1; one issuing thread for both tiles
-//              cannot feed the tensor pipe (measured ~95 cycles per MMA instruction issued)
+//   warp 10    tcgen05.mma issuer for the P.V products of both query tiles
 //   warp 11    idle; the auxiliary warpgroup's registers go to the softmax warps (setmaxnreg)
 //
 // Tensor memory (512 columns): S | P0 | P1 | O0 | O1 = 128 + 64 + 64 + 128 + 128.  There is ONE
@@ -24,12 +23,12 @@
 // row into registers as soon as the tile is complete and hands the region on, so the next Q.K^T
 // product (of the other query tile) starts while this tile is still in its exponentials.  The bf16
 // probabilities have a region of their own per query tile, so that the next score tile of a query
-// tile does not have to wait for its P.V product either.  The per-tile dependency chain is then the
-// softmax alone; with the two warpgroups taking turns in the exp2 phase the 16-lane MUFU never
-// idles, and both products of one tile run under the other tile's exponentials.
+// tile does not have to wait for its P.V product either.  What remains serial is the hand-over of
+// the score region: copy-out -> issuing warp wakes -> 8 MMAs -> tensor-pipe latency -> softmax warp
+// wakes, about 1 100-1 300 cycles per use, two uses per K/V tile.
 //
-// K/V tiles are loaded, and consumed by both issuing warps, in the order K0 K1 V0 K2 V1 K3 V2 ...:
-// the score product of iteration g+1 is issued before the P.V product of iteration g.
+// K/V tiles are loaded in the order K0 K1 V0 K2 V1 K3 V2 ...: the score product of K/V tile g+1 is
+// issued before the P.V product of tile g needs its V tile.
 #include "attn_fwd_common.cuh"
 
 namespace mb {
@@ -81,14 +80,13 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     mbar_init(&ctl->q_full, 1);
     for (int s = 0; s < kFwdStages; ++s) {
       mbar_init(&ctl->kv_full[s], 1);
-      mbar_init(&ctl->kv_empty[s], 2);  // one arrival from each of the two MMA-issuing warps
+      mbar_init(&ctl->kv_empty[s], 1);  // released by the one warp that consumes the stage
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ctl->s_full[i], 1);
       mbar_init(&ctl->p_full[i][0], 128);
       mbar_init(&ctl->p_full[i][1], 128);
       mbar_init(&ctl->o_full[i], 1);
-      mbar_init(&ctl->turn[i], 128);
     }
     mbar_init(&ctl->s_free, 4);
     mbar_init(&ctl->drain, 2);
@@ -178,92 +176,92 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
       }
     }
   } else if (warp == 8 || warp == 10) {
-    // ------------------------------------------- MMA issuers: warp 8 -> query tile 0, warp 10 -> tile 1
-    // Each walks every K/V stage in load order (K0 K1 V0 K2 V1 ...): it waits for the stage, uses it if
-    // its query tile takes part in that K/V tile, and arrives on the stage's "empty" barrier either
-    // way, so the barrier always sees one arrival per issuing warp.
+    // ------------------------------------------- MMA issuers: warp 8 issues every Q.K^T product,
+    // warp 10 every P.V product, of both query tiles.  (One warp per query tile issuing both kinds
+    // held its P.V products back while it sat in the issue of its next score product, and the
+    // products of the two tiles then fell into the same stretch of time, with the tensor pipe idle
+    // in between.)  Positions in the ring of K/V stages follow the load order K0 K1 V0 K2 V1 ...
     asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
     if (any_work) {  // whole warp, converged
-      const int i = (warp - 8) >> 1;
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(kBM, kBN, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(kBM, kD, false, true);
-      const uint32_t tS = tmem, tPi = tmem + 128 + i * 64, tOi = tmem + 256 + i * 128;
-      const uint64_t q_desc = umma_smem_desc(smem_u32(sQ) + i * kTileBytes, 16, 1024);
-      const uint64_t k_desc0 = umma_smem_desc(smem_u32(sKV), 16, 1024);          // K-major view of stage 0
-      const uint64_t v_desc0 = umma_smem_desc(smem_u32(sKV), kHalfBytes, 1024);  // MN-major view of stage 0
       constexpr uint32_t kStageUnits = kTileBytes / 16;
-      uint64_t* p_full0 = &ctl->p_full[i][0];
-      uint64_t* p_full1 = &ctl->p_full[i][1];
-      int cnt = 0;   // P.V products of this query tile issued so far
-      int n = 0;     // next stage index in load order
-      int seq = 0;   // uses of the score region so far, by either query tile
-      bool ok = mbar_wait_warp(&ctl->q_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
-      bool first = true;
-
-      // K stage: S = Q K^T into the shared score region, once its previous user has copied its scores out.
-      auto do_k = [&](const TileIter& it) {
-        const int stage = n % kFwdStages;
-        ok = mbar_wait_warp(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
-        if (!ok) return;
-        const int part0 = it.jt < ctl->n_tiles[0][it.s], part1 = it.jt < ctl->n_tiles[1][it.s];
-        if (i ? part1 : part0) {
-          const int my_use = seq + (i ? part0 : 0);
-          if (my_use > 0) {
-            ok = mbar_wait_warp(&ctl->s_free, (my_use - 1) & 1, abort_word, MB_ERR_TIMEOUT_S);
-            if (!ok) return;
+      int total = 0;  // K/V tiles this CTA walks through
+      for (int s = 0; s < a.nseg; ++s) total += seg_tiles(ctl, s);
+      bool ok = true;
+      if (warp == 8) {
+        constexpr uint32_t idesc_qk = umma_idesc_bf16(kBM, kBN, false, false);
+        const uint64_t q_desc = umma_smem_desc(smem_u32(sQ), 16, 1024);
+        const uint64_t k_desc0 = umma_smem_desc(smem_u32(sKV), 16, 1024);  // K-major view of stage 0
+        int g = 0;    // K/V tile index over all segments
+        int use = 0;  // uses of the score region so far, by either query tile
+        ok = mbar_wait_warp(&ctl->q_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
+        for (int s = 0; s < a.nseg && ok; ++s) {
+          const int n0 = ctl->n_tiles[0][s], n1 = ctl->n_tiles[1][s];
+          const int nmax = max(n0, n1);
+          for (int jt = 0; jt < nmax && ok; ++jt, ++g) {
+            const int pos = g == 0 ? 0 : 2 * g - 1;
+            const int stage = pos % kFwdStages;
+            ok = mbar_wait_warp(&ctl->kv_full[stage], (pos / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+            if (!ok) break;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              if (jt < (i ? n1 : n0)) {
+                // the score region's previous user must have copied its scores out
+                if (use > 0) {
+                  ok = mbar_wait_warp(&ctl->s_free, (use - 1) & 1, abort_word, MB_ERR_TIMEOUT_S);
+                  if (!ok) break;
+                }
+                tc_fence_after();
+                issue_qk(tmem, q_desc + i * kStageUnits, k_desc0 + stage * kStageUnits, idesc_qk);
+                umma_commit_elect(&ctl->s_full[i]);
+                MB_TRACE_AT(2, use >> 1, i * 6 + 5);
+                ++use;
+              }
+            }
+            if (!ok) break;
+            umma_commit_elect(&ctl->kv_empty[stage]);
           }
-          tc_fence_after();
-          issue_qk(tS, q_desc, k_desc0 + stage * kStageUnits, idesc_qk);
-          umma_commit_elect(&ctl->s_full[i]);
-          umma_commit_elect(&ctl->kv_empty[stage]);
-          MB_TRACE_AT(2, cnt, i * 6 + 5);
-        } else {
-          mbar_arrive_elect(&ctl->kv_empty[stage]);
         }
-        seq += part0 + part1;
-        ++n;
-      };
-      // V stage: O (+)= P V, in two halves as the probabilities arrive.
-      auto do_v = [&](const TileIter& it) {
-        const int stage = n % kFwdStages;
-        ok = mbar_wait_warp(&ctl->kv_full[stage], (n / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
-        if (!ok) return;
-        if (it.jt < ctl->n_tiles[i][it.s]) {
-          const uint64_t v_desc = v_desc0 + stage * kStageUnits;
-          MB_TRACE_AT(2, cnt, i * 6 + 0);
-          ok = mbar_wait_warp(p_full0, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
-          if (!ok) return;
-          MB_TRACE_AT(2, cnt, i * 6 + 1);
-          tc_fence_after();
-          issue_pv_half(tOi, tPi, v_desc, idesc_pv, first ? 0u : 1u);
-          MB_TRACE_AT(2, cnt, i * 6 + 2);
-          ok = mbar_wait_warp(p_full1, cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
-          if (!ok) return;
-          MB_TRACE_AT(2, cnt, i * 6 + 3);
-          tc_fence_after();
-          issue_pv_half(tOi, tPi + 32, v_desc + 4 * 128, idesc_pv, 1u);
-          umma_commit_elect(&ctl->o_full[i]);
-          umma_commit_elect(&ctl->kv_empty[stage]);
-          MB_TRACE_AT(2, cnt, i * 6 + 4);
-          first = false;
-          ++cnt;
-        } else {
-          mbar_arrive_elect(&ctl->kv_empty[stage]);
+      } else {
+        constexpr uint32_t idesc_pv = umma_idesc_bf16(kBM, kD, false, true);
+        const uint64_t v_desc0 = umma_smem_desc(smem_u32(sKV), kHalfBytes, 1024);  // MN-major view of stage 0
+        int g = 0;
+        int cnt0 = 0, cnt1 = 0;  // P.V products issued per query tile
+        for (int s = 0; s < a.nseg && ok; ++s) {
+          const int n0 = ctl->n_tiles[0][s], n1 = ctl->n_tiles[1][s];
+          const int nmax = max(n0, n1);
+          for (int jt = 0; jt < nmax && ok; ++jt, ++g) {
+            const int pos = g == total - 1 ? 2 * total - 1 : 2 * g + 2;
+            const int stage = pos % kFwdStages;
+            ok = mbar_wait_warp(&ctl->kv_full[stage], (pos / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+            if (!ok) break;
+            const uint64_t v_desc = v_desc0 + stage * kStageUnits;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              if (jt < (i ? n1 : n0)) {
+                const int cnt = i ? cnt1 : cnt0;
+                const uint32_t tPi = tmem + 128 + i * 64, tOi = tmem + 256 + i * 128;
+                MB_TRACE_AT(2, cnt, i * 6 + 0);
+                ok = mbar_wait_warp(&ctl->p_full[i][0], cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+                if (!ok) break;
+                MB_TRACE_AT(2, cnt, i * 6 + 1);
+                tc_fence_after();
+                issue_pv_half(tOi, tPi, v_desc, idesc_pv, cnt == 0 ? 0u : 1u);
+                MB_TRACE_AT(2, cnt, i * 6 + 2);
+                ok = mbar_wait_warp(&ctl->p_full[i][1], cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+                if (!ok) break;
+                MB_TRACE_AT(2, cnt, i * 6 + 3);
+                tc_fence_after();
+                issue_pv_half(tOi, tPi + 32, v_desc + 4 * 128, idesc_pv, 1u);
+                umma_commit_elect(&ctl->o_full[i]);
+                MB_TRACE_AT(2, cnt, i * 6 + 4);
+                if (i) ++cnt1;
+                else ++cnt0;
+              }
+            }
+            if (!ok) break;
+            umma_commit_elect(&ctl->kv_empty[stage]);
+          }
         }
-        ++n;
-      };
-
-      TileIter nxt = iter_first(ctl, a.nseg);
-      TileIter cur = nxt;
-      if (ok && nxt.s < a.nseg) {
-        do_k(nxt);
-        iter_next(ctl, a.nseg, nxt);
-      }
-      while (ok && cur.s < a.nseg) {
-        if (nxt.s < a.nseg) do_k(nxt);
-        if (ok) do_v(cur);
-        cur = nxt;
-        if (nxt.s < a.nseg) iter_next(ctl, a.nseg, nxt);
       }
       if (!ok) {
         // Let tensor-core work already issued finish (bounded) before tensor memory is released.
@@ -291,12 +289,10 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     float m_ref = -INFINITY;  // reference max (raw score units)
     float l = 0.f;            // running sum of exp2
     int cnt = 0;
-    int shared_cnt = 0;       // K/V tiles both query tiles took part in so far
     bool ok = true;
 
     for (int s = 0; s < a.nseg && ok; ++s) {
       const int nt = ctl->n_tiles[i][s];
-      const int nt_both = min(ctl->n_tiles[0][s], ctl->n_tiles[1][s]);
       const int sk = a.seg_sk[s];
       const int koff = a.seg_koff[s];
       for (int jt = 0; jt < nt; ++jt) {
@@ -370,19 +366,9 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
           }
         }
 
-        // The two warpgroups take turns in the exp2 phase: the 16-lane MUFU is the scarce unit, and
-        // if both tiles reach this phase together they share it, finish together and then leave it
-        // idle while both wait for the tensor pipe.  Alternating keeps one tile in its MUFU phase
-        // while the other tile's MMAs run.  Only K/V tiles that both query tiles process take part,
-        // so the two warpgroups always agree on the turn count.
-        const bool take_turns = kTakeTurns && jt < nt_both;
-        if (take_turns) {
-          ok = mbar_wait_warp(&ctl->turn[i], (shared_cnt & 1) ^ (i == 0 ? 1 : 0), abort_word, MB_ERR_TIMEOUT_MISC);
-          if (!ok) break;
-        }
-
-        // p = exp2(s * c - m * c): the scale/subtract and the row sum run as packed pairs; every
-        // kPolyEvery-th pair of exponentials is evaluated on the FMA pipe, the rest on the MUFU.
+        // p = exp2(s * c - m * c): the scale/subtract and the row sum run as packed pairs.  (Taking
+        // turns between the two warpgroups in this MUFU-bound phase, and moving part of the
+        // exponentials to a polynomial on the FMA pipe, were both measured as losses.)
         const float m_scaled = (m_ref == -INFINITY) ? 0.f : m_ref * a.scale_log2;
         const uint64_t c2 = pack2(a.scale_log2, a.scale_log2);
         const uint64_t nm2 = pack2(-m_scaled, -m_scaled);
@@ -396,24 +382,15 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
 #pragma unroll
             for (int e = 0; e < 32; e += 2) {
               const uint64_t x2 = fma2(pack2(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1])), c2, nm2);
-              uint64_t p2;
-              if (kPolyEvery > 0 && ((e >> 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) {
-                p2 = exp2_poly2(x2);
-              } else {
-                float x0, x1;
-                unpack2(x2, x0, x1);
-                p2 = pack2(fast_exp2(x0), fast_exp2(x1));
-              }
+              float x0, x1;
+              unpack2(x2, x0, x1);
+              const uint64_t p2 = pack2(fast_exp2(x0), fast_exp2(x1));
               if ((e >> 1) & 1) sum_b = add2(sum_b, p2);
               else sum_a = add2(sum_a, p2);
               float p0, p1;
               unpack2(p2, p0, p1);
               pk[cc * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
             }
-          }
-          if (half == 1 && take_turns) {
-            mbar_arrive(&ctl->turn[i ^ 1]);  // my exponentials are issued: the other warpgroup's turn
-            ++shared_cnt;
           }
           tmem_st32(tPi + half * 32, pk);
           tmem_wait_st();

@@ -12,23 +12,17 @@ constexpr int kBN = 128;            // keys per tile
 constexpr int kD = 128;             // head dimension
 constexpr int kTileBytes = kBN * kD * 2;  // 32 KiB, stored as two 64-column halves
 constexpr int kHalfBytes = kTileBytes / 2;
-constexpr int kFwdStages = 4;
+#ifndef MB_FWD_STAGES
+#define MB_FWD_STAGES 4
+#endif
+constexpr int kFwdStages = MB_FWD_STAGES;  // 32 KiB K or V tiles in flight (3, 4 and 5 measured alike)
 constexpr int kFwdThreads = 384;  // 8 softmax warps + one auxiliary warpgroup (MMA, loader, 2 idle)
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: tolerate p up to 2^8
-#ifndef MB_POLY_EVERY
-#define MB_POLY_EVERY 0
-#endif
-constexpr int kPolyEvery = MB_POLY_EVERY;  // every n-th pair of exponentials goes to the FMA pipe (0: none)
-#ifndef MB_TAKE_TURNS
-#define MB_TAKE_TURNS 1
-#endif
-constexpr bool kTakeTurns = MB_TAKE_TURNS != 0;  // the softmax warpgroups alternate in the exp2 phase
-
 // Optional timeline capture for kernel tuning (compiled in only with -DMB_TRACE): CTA (0,0,0)
 // records clock64() at fixed points of the first kTraceIters K/V iterations.
 #ifdef MB_TRACE
 constexpr int kTraceIters = 24;
-static __device__ long long g_fwd_trace[3][kTraceIters][12];
+static __device__ long long g_fwd_trace[4][kTraceIters][12];
 #define MB_TRACE_AT(role, it, ev)                                                              \
   do {                                                                                         \
     if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < kTraceIters)           \
@@ -72,7 +66,6 @@ struct FwdSmem {
   uint64_t s_free;        // the one score region is handed from user to user (4 warp arrivals per use)
   uint64_t p_full[2][2];  // [query tile][half of the keys of a K/V tile]
   uint64_t o_full[2];
-  uint64_t turn[2];  // exp2-phase token passed between the two softmax warpgroups
   uint64_t drain;
   uint32_t tmem_base;
   int abort_word;
@@ -81,6 +74,7 @@ struct FwdSmem {
 
 constexpr int kFwdSmemBytes = 2 * kTileBytes + kFwdStages * kTileBytes + 1024 /*alignment slack*/ + 1024 /*FwdSmem*/;
 static_assert(sizeof(FwdSmem) <= 1024, "control block too large");
+static_assert(kFwdSmemBytes <= 232448, "shared memory budget of one CTA");
 
 // Number of K/V tiles of a segment that a query tile starting at row q0 can see.
 __device__ __forceinline__ int visible_tiles(int q0, int Sq, int q_off, int causal, int sk, int koff) {

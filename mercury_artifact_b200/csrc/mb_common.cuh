@@ -358,36 +358,10 @@ __device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
   asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
-__device__ __forceinline__ uint64_t add2_round_down(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
-}
-
-// exp2 of a pair on the FMA pipe instead of the 16-lane MUFU: split x = j + f with j = floor(x)
-// (round-down add of 1.5 * 2^23), evaluate a cubic for 2^f on [0,1) (max relative error 7.5e-5,
-// far below bf16 resolution) and add j into the exponent field.  Inputs are clamped at -126.
-__device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
-  float x0, x1;
-  unpack2(x2, x0, x1);
-  x2 = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-  const uint64_t magic = pack2(12582912.f, 12582912.f);
-  const uint64_t y2 = add2_round_down(x2, magic);
-  const uint64_t f2 = sub2(x2, sub2(y2, magic));
-  uint64_t p2 = fma2(f2, pack2(0.07802430f, 0.07802430f), pack2(0.22606729f, 0.22606729f));
-  p2 = fma2(p2, f2, pack2(0.69583356f, 0.69583356f));
-  p2 = fma2(p2, f2, pack2(0.99992520f, 0.99992520f));
-  float p0, p1, y0, y1;
-  unpack2(p2, p0, p1);
-  unpack2(y2, y0, y1);
-  p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(y0) << 23));
-  p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(y1) << 23));
-  return pack2(p0, p1);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

@@ -29,6 +29,11 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch, from an ncu capture
+# (profiles/attn_fwd_kernel_profile16k.md).  profile_16k was captured directly; cfg2 at one GPU is that
+# capture scaled by 2 (bytes grow linearly in the sequence length at fixed batch, heads and head_dim).
+NCU_DRAM_BYTES_PER_LAUNCH = {("profile_16k", 1): 5.23e8, ("cfg2", 1): 1.046e9}
+
 WORKLOADS = {
     # name: (batch, seqlen, hq, hkv, head_dim, causal)
     "cfg2": (1, 32768, 32, 32, 128, True),
@@ -307,7 +312,7 @@ def run_ours(args):
                         "note": "forward + backward per step, FLOPs = 3.5 x forward (backward counted as 2.5 x)"},
             "gpu_launches": args.steps * op.launches_per_forward * world,
             "roofline": {"bound": "tensor", "achieved": kernel_tf, "peak": peak, "unit": "TFLOP/s",
-                         "frac": kernel_tf / peak, "traffic": None,
+                         "frac": kernel_tf / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((args.workload, world)),
                          "kernel": "attn_fwd_kernel (busiest rank)", "peak_kind": f"bf16_tflops burst, {peak_kind}",
                          "frac_of_sustained": (kernel_tf / sustained) if sustained else None},
             "clocks": clocks, "device_status": status,

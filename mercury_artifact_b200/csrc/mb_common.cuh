@@ -111,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// Whole-warp form: every lane waits and the verdict is made uniform, so that the
+// Whole-warp form: every lane waits and the outcome is made uniform, so that the
 // warp-collective tensor-memory instructions that follow stay converged.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_word, int code) {
   const bool ok = mbar_wait(bar, parity, abort_word, code);

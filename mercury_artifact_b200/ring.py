@@ -410,12 +410,14 @@ class RingAttention:
 
     # ------------------------------------------------------------------ host-buffer entry
     def forward_host(self, q_host: torch.Tensor, kv_host: torch.Tensor, o_host: torch.Tensor, lse_host: torch.Tensor,
-                     softmax_scale: Optional[float] = None, chunks: int = 8) -> None:
+                     softmax_scale: Optional[float] = None, chunks: int = 16) -> None:
         """Forward with pinned HOST tensors in and out (same shapes as forward()).
 
-        Single rank, batch 1: the sequence is cut into up to 8 chunks; chunk i is copied in while
-        chunk i-1 is being computed (its queries against K/V chunks 0..i as segments of one launch)
-        and chunk i-2 is copied out, so the PCIe transfers in both directions overlap the kernels.
+        Single rank, batch 1: the sequence is cut into `chunks` pieces; chunk i is copied in while
+        chunk i-1 is being computed (its queries against the K/V rows that have arrived so far, which
+        are contiguous on the device and go in as one segment) and chunk i-2 is copied out, so the PCIe
+        transfers in both directions overlap the kernels.  What stays exposed is the last chunk's
+        kernel and copy-out, hence many small chunks rather than few large ones.
         Otherwise: copy in, forward(), copy out.  Returns after the results are in host memory.
         """
         dev = torch.device("cuda", torch.cuda.current_device()) if self.ctx is None else self.ctx.device
@@ -430,7 +432,7 @@ class RingAttention:
                                torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
         q, kv, o, lse, s_in, s_out = self._host_bufs
         main = torch.cuda.current_stream()
-        n = min(chunks, 8)
+        n = max(1, min(chunks, 64))
         pipelined = self.world == 1 and self.batch == 1 and L % n == 0 and (L // n) % 128 == 0
         if not pipelined:
             q.copy_(q_host, non_blocking=True)
@@ -458,7 +460,7 @@ class RingAttention:
             rows = slice(i * c, (i + 1) * c)
             main.wait_event(arrived[i])
             if self.causal:
-                segs = [(kv[0][:, j * c:(j + 1) * c], kv[1][:, j * c:(j + 1) * c], j * c) for j in range(i + 1)]
+                segs = [(kv[0][:, :(i + 1) * c], kv[1][:, :(i + 1) * c], 0)]
             else:
                 main.wait_event(arrived[-1])
                 segs = [(kv[0], kv[1], 0)]

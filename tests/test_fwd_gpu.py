@@ -152,6 +152,29 @@ def test_ring_segments_match_full_attention(causal):
     _status_ok()
 
 
+@pytest.mark.parametrize("causal,chunks", [(True, 4), (True, 16), (False, 4), (True, 3)])
+def test_host_buffer_forward_matches_oracle(causal, chunks):
+    """forward_host(): pinned host tensors in and out, sequence chunks pipelined over PCIe (chunks=3 does not
+    divide into 128-row pieces and takes the plain copy-in / forward / copy-out path)."""
+    from oracle import block
+    from mercury_artifact_b200.ring import RingAttention
+
+    B, S, H = 1, 2048, 4
+    q, k, v, _ = seeded_qkv(7, B, S, H, H, 128, device="cpu")
+    fo, fl = block.full_attention(q, k, v, 128 ** -0.5, causal=causal)
+    q_host = q.contiguous().pin_memory()
+    kv_host = torch.stack([k, v]).contiguous().pin_memory()
+    o_host = torch.empty_like(q_host).pin_memory()
+    lse_host = torch.empty((B, H, S), dtype=torch.float32).pin_memory()
+    op = RingAttention((1,), B, S, H, H, 128, causal=causal)
+    for _ in range(2):  # twice: the second call reuses the device buffers and streams
+        o_host.zero_()
+        lse_host.zero_()
+        op.forward_host(q_host, kv_host, o_host, lse_host, chunks=chunks)
+        _check(o_host, lse_host, fo, fl)
+    _status_ok()
+
+
 def test_full_size_properties_config2():
     """BASELINE config 2 shapes (bf16 B1 S32768 H32 D128 causal): size-independent properties.
 

@@ -7,7 +7,11 @@ mercury/backend/pytorch/codegen.py:219):
   * `from mercury.backend import *` executed by the generated text itself:
     SendRecv and the mesh index helpers.
 
-`namespace()` serves the first, `install_backend()` the second.
+`namespace()` serves the first, `install_backend()` the second.  `install_search_hooks()` makes the
+reference's schedule search time these ops: its bench_program(program, namespace, ...) takes the exec
+namespace as an argument (mercury/search/bench.py:15-45) and emits the text through the module-level name
+generate_pytorch_code, which the hook wraps so that a recognised ring loop is replaced by its fused
+one-launch form before it is executed.
 """
 from __future__ import annotations
 
@@ -88,3 +92,35 @@ def load_generated(code: str, extra: Dict[str, object] | None = None) -> Dict[st
     ns = namespace(extra)
     exec(compile(code, "<mercury generated>", "exec"), ns)
     return ns
+
+
+def install_search_hooks(fuse: bool = True) -> Dict[str, object]:
+    """Prepare the reference's schedule search (mercury/search/bench.py: bench_program) for these ops.
+
+    Installs the SendRecv backend, and with fuse=True wraps the name `generate_pytorch_code` that
+    bench_program calls so that the emitted text goes through emitter.fuse_generated (a program whose
+    idiom is not recognised is returned unchanged and runs on the per-step drop-ins).  Returns the
+    namespace to pass as bench_program's second argument.  Needs the reference importable."""
+    install_backend()
+    import mercury.search.bench as ref_bench  # type: ignore
+
+    if fuse and not getattr(ref_bench.generate_pytorch_code, "_mercury_b200_fusing", False):
+        from .emitter import fuse_generated
+
+        inner = ref_bench.generate_pytorch_code
+
+        def generate_pytorch_code(program):
+            return fuse_generated(inner(program))
+
+        generate_pytorch_code._mercury_b200_fusing = True  # type: ignore[attr-defined]
+        generate_pytorch_code._mercury_b200_inner = inner  # type: ignore[attr-defined]
+        ref_bench.generate_pytorch_code = generate_pytorch_code
+    return namespace()
+
+
+def remove_search_hooks() -> None:
+    """Undo install_search_hooks(fuse=True)."""
+    mod = sys.modules.get("mercury.search.bench")
+    fn = getattr(mod, "generate_pytorch_code", None) if mod is not None else None
+    if fn is not None and getattr(fn, "_mercury_b200_fusing", False):
+        mod.generate_pytorch_code = fn._mercury_b200_inner

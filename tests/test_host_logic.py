@@ -158,3 +158,57 @@ def test_emitter_recognises_kv_rings_and_leaves_other_programs_alone():
     assert "def flash_attn_pack_kv(q, kv, o, lse, softmax_scale, dropout_p=0, causal=False" in fused
     assert "for S_kv_ring_idx" not in fused and "RingAttention((4,), 1, 512, 4, 4, 128" in fused
     compile(fused, "<fused>", "exec")
+
+
+@pytest.mark.skipif(not Path("/root/reference/mercury").exists(), reason="reference checkout not present")
+def test_search_hooks_fuse_the_program_the_reference_search_would_time():
+    """install_search_hooks(): the text bench_program (mercury/search/bench.py) execs is the fused form
+    for a ring schedule and the reference's own text for a schedule the emitter does not recognise."""
+    import ast
+    import textwrap
+
+    sys.path.insert(0, "/root/reference")
+    sys.dont_write_bytecode = True
+    try:
+        import mercury.search.bench as ref_bench
+        from mercury.frontend.parser import IRBuilder
+        from mercury.ir.distributed import DeviceMesh
+        from mercury.ir.init_distributed import init_distributed
+        from mercury.ir.loop_eliminating import eliminate_loops
+        from mercury.ir.primitives import parallelize, shift
+        from mercury.ir.utils import collect_axis, collect_loops
+        import utils.flash_attn_dsl as dsl
+    finally:
+        sys.path.pop(0)
+    import mercury_artifact_b200 as mb
+
+    def program(kind):
+        if kind == "ring":
+            src = dsl.flash_attn_pack_kv_template.format(BATCH=1, HEADS=4, SEQ_LEN=2048, HEAD_DIM=128)
+        else:
+            src = dsl.flash_attn_manage_reduction.format(BATCH=1, HEADS=4, SEQ_LEN=2048, HEAD_DIM=128, RED_DIM=129)
+        prog = IRBuilder().visit(ast.parse(textwrap.dedent(src)).body[0])
+        axes, loops = prog.visit(collect_axis), prog.visit(collect_loops)
+        dm = DeviceMesh(list(range(4)), (4,))
+        init_distributed(prog, dm)
+        if kind == "ring":
+            parallelize(prog, loops[0], axes[2], dm, 0, 1)
+            shift(prog, axes[2], dm, 0, 1, 1)
+        else:
+            parallelize(prog, loops[1], axes[3], dm, 0, 1)
+        eliminate_loops(prog)
+        return prog
+
+    plain = ref_bench.generate_pytorch_code
+    try:
+        ns = mb.install_search_hooks()
+        assert {"_flash_attn_forward", "update_out_and_lse", "get_default_args"} <= set(ns)
+        fused = ref_bench.generate_pytorch_code(program("ring"))
+        assert "_RingAttention((4,), 1, 512, 4, 4, 128" in fused and "SendRecv" not in fused
+        tree_prog = program("tree")
+        assert ref_bench.generate_pytorch_code(tree_prog) == plain(tree_prog)
+        mb.install_search_hooks()  # idempotent
+        assert ref_bench.generate_pytorch_code._mercury_b200_inner is plain
+    finally:
+        mb.remove_search_hooks()
+    assert ref_bench.generate_pytorch_code is plain

@@ -95,12 +95,13 @@ class _ShardExchange:
         return ev
 
     def pull(self, origin: int, ranges: Optional[Sequence[Tuple[int, int]]] = None, final: bool = True,
-             raise_flag: bool = True) -> Tuple[torch.Tensor, int]:
+             raise_flag: bool = True, piece: int = 0) -> Tuple[torch.Tensor, int]:
         """Copy `origin`'s slot of this epoch (or the given (offset, nbytes) ranges of it) into that
         origin's staging slot (copy engines over NVLink).  Returns (staging bytes, address of the
         arrival flag that reaches `epoch` behind the copy).  final=False keeps the owner's slot
         reserved for a later pull of the same epoch; raise_flag=False leaves the arrival flag alone
-        (the caller orders its consumers with a stream event instead)."""
+        (the caller orders its consumers with a stream event instead).  piece selects one of the
+        staging slot's eight arrival flags, for a slot that is pulled in several pieces."""
         ctx, comm = self.ctx, self.ctx.comm_stream
         e = self.epoch
         if origin not in self._stage_of:
@@ -112,7 +113,9 @@ class _ShardExchange:
         base = (e % 2) * self.slot_bytes
         for off, nbytes in (ranges if ranges is not None else [(0, self.slot_bytes)]):
             ctx.copy(dst.data_ptr() + off, self.sym.ptr(origin, base + off), nbytes, comm)
-        flag_ptr = self.seg_flags.data_ptr() + 4 * idx
+        if not 0 <= piece < 8:
+            raise ValueError("a staging slot has eight arrival flags")
+        flag_ptr = self.seg_flags.data_ptr() + 4 * (8 * idx + piece)
         if raise_flag:
             ctx.signal(flag_ptr, e, comm)
         if final:
@@ -142,7 +145,7 @@ class RingAttention:
 
     def __init__(self, mesh_shape: Sequence[int], batch: int, seq_local: int, hq: int, hkv: int,
                  head_dim: int = 128, causal: bool = False, ctx: Optional[PeerContext] = None,
-                 balance_causal: bool = True):
+                 balance_causal: bool = True, ring_divide: int = 1):
         self.mesh_shape = tuple(int(n) for n in mesh_shape)
         self.world = 1
         for n in self.mesh_shape:
@@ -170,6 +173,19 @@ class RingAttention:
         self.balanced = bool(balance_causal) and self.causal and self.world > 1 and seq_local % 2 == 0
         if self.balanced:
             self.launches_per_forward = 2
+        # ring_divide (the rounds parameter of the reference's shift primitive, ir/primitives.py:33-45,
+        # 101-102): every K/V shard travels as `ring_divide` sequence pieces, each with its own arrival
+        # flag and its own segment of the launch, so work on a shard starts when its first piece is in.
+        # One launch takes at most eight segments: 1 local + (world - 1) * ring_divide.
+        self.ring_divide = int(ring_divide)
+        if self.ring_divide < 1 or seq_local % self.ring_divide != 0:
+            raise ValueError("ring_divide must divide the local sequence length")
+        if self.ring_divide > 1:
+            if self.balanced:
+                raise ValueError("ring_divide > 1 is implemented for the plain (unbalanced) forward: "
+                                 "pass balance_causal=False")
+            if 1 + (self.world - 1) * self.ring_divide > 8:
+                raise ValueError("1 + (world - 1) * ring_divide segments exceed the eight of one launch")
 
     # ------------------------------------------------------------------ helpers
     def _sees_keys_of(self, origin: int) -> bool:
@@ -182,6 +198,12 @@ class RingAttention:
 
     def _kv_bytes(self) -> int:
         return 2 * self.batch * self.seq_local * self.hkv * self.head_dim * 2
+
+    def _bwd_slot_bytes(self) -> int:
+        """Backward exchange slot: kv | q | dout | row statistics, each 256-byte aligned."""
+        q_b = self.batch * self.seq_local * self.hq * self.head_dim * 2
+        st_b = 2 * self.batch * self.hq * self.stat_pad * 4
+        return _align(self._kv_bytes(), 256) + 2 * _align(q_b, 256) + _align(st_b, 256)
 
     # ------------------------------------------------------------------ forward
     def forward(self, q: torch.Tensor, kv: torch.Tensor, o: Optional[torch.Tensor] = None,
@@ -215,10 +237,21 @@ class RingAttention:
         segs: List[tuple] = [(slot[0], slot[1], me * L)]
         for t in range(1, self.world):
             origin = self.order[t]
-            if self._sees_keys_of(origin):
+            if self._sees_keys_of(origin) and self.ring_divide == 1:
                 buf, flag_ptr = x.pull(origin)
                 rkv, _ = _carve(buf, 0, self.kv_shape, torch.bfloat16)
                 segs.append((rkv[0], rkv[1], origin * L, flag_ptr, x.epoch))
+            elif self._sees_keys_of(origin):
+                d, c = self.ring_divide, L // self.ring_divide
+                row_b = self.hkv * self.head_dim * 2
+                for j in range(d):
+                    # rows [j c, (j+1) c) of K and of V, for every batch entry: 2 B contiguous ranges
+                    ranges = [(((w * self.batch + b) * L + j * c) * row_b, c * row_b)
+                              for w in range(2) for b in range(self.batch)]
+                    buf, flag_ptr = x.pull(origin, ranges, final=(j == d - 1), piece=j)
+                    rkv, _ = _carve(buf, 0, self.kv_shape, torch.bfloat16)
+                    segs.append((rkv[0][:, j * c:(j + 1) * c], rkv[1][:, j * c:(j + 1) * c], origin * L + j * c,
+                                 flag_ptr, x.epoch))
             else:
                 x.release(origin)
 
@@ -362,7 +395,8 @@ class RingAttention:
         off_do = off_q + _align(q_b, 256)
         off_st = off_do + _align(q_b, 256)
         if self._bwd_x is None:
-            self._bwd_x = _ShardExchange(self.ctx, off_st + _align(st_b, 256))
+            assert off_st + _align(st_b, 256) == self._bwd_slot_bytes()
+            self._bwd_x = _ShardExchange(self.ctx, self._bwd_slot_bytes())
         x = self._bwd_x
         main = torch.cuda.current_stream()
         comm = self.ctx.comm_stream
@@ -474,6 +508,35 @@ class RingAttention:
                 if i == n - 1:
                     lse_host.copy_(lse, non_blocking=True)
         s_out.synchronize()
+
+    def memory_bytes(self, backward: bool = False) -> dict:
+        """Device memory this object allocates per rank for its transfers, by kind (the counterpart of
+        the reference's per-card buffer model, mercury/ir/calculate_memory.py:9-66, for symmetric slots
+        and staging instead of the rotating double buffer): `symmetric` is mapped by every peer (two
+        epoch slots per exchange), `staging` holds pulled shards (world - 1 slots per exchange),
+        `inbox` receives results computed elsewhere (balanced causal forward).  Flag regions included."""
+        if self.world == 1:
+            return {"symmetric": 0, "staging": 0, "inbox": 0}
+        q_b = self.batch * self.seq_local * self.hq * self.head_dim * 2
+        lse_b = self.batch * self.hq * self.seq_local * 4
+        kv_b = self._kv_bytes()
+
+        def exchange(slot_bytes):
+            slot = _align(slot_bytes, 1024)
+            return 2 * slot + _FLAG_REGION, max(self.world - 1, 1) * slot
+
+        sym = stage = inbox = 0
+        if self.balanced:
+            a, b = exchange(_align(kv_b, 256) + _align(q_b, 256))
+            sym, stage = sym + a, stage + b
+            inbox = 2 * (_align(q_b, 256) + _align(lse_b, 256)) + _FLAG_REGION
+        else:
+            a, b = exchange(kv_b)
+            sym, stage = sym + a, stage + b
+        if backward:
+            a, b = exchange(self._bwd_slot_bytes())
+            sym, stage = sym + a, stage + b
+        return {"symmetric": sym, "staging": stage, "inbox": inbox}
 
     def check(self) -> None:
         """Synchronise and raise if a device-side wait timed out."""

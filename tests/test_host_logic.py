@@ -212,3 +212,30 @@ def test_search_hooks_fuse_the_program_the_reference_search_would_time():
     finally:
         mb.remove_search_hooks()
     assert ref_bench.generate_pytorch_code is plain
+
+
+def test_ring_divide_validation_and_memory_model():
+    """Constructor checks of ring_divide and the per-rank memory model, without a process group."""
+    from mercury_artifact_b200.ring import RingAttention
+
+    class Ctx:
+        world, rank, device = 8, 3, None
+
+    op = RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx())
+    kv_b, q_b, lse_b = 2 * 4096 * 32 * 128 * 2, 4096 * 32 * 128 * 2, 32 * 4096 * 4
+    m = op.memory_bytes()
+    assert m["symmetric"] == 2 * (kv_b + q_b) + 4096 and m["staging"] == 7 * (kv_b + q_b)
+    assert m["inbox"] == 2 * (q_b + lse_b) + 4096
+    plain = RingAttention((8,), 1, 4096, 32, 32, 128, causal=False, ctx=Ctx())
+    assert plain.memory_bytes() == {"symmetric": 2 * kv_b + 4096, "staging": 7 * kv_b, "inbox": 0}
+    assert plain.memory_bytes(backward=True)["staging"] > 7 * (kv_b + 2 * q_b)
+    with pytest.raises(ValueError, match="divide the local sequence"):
+        RingAttention((8,), 1, 4096, 32, 32, 128, ctx=Ctx(), ring_divide=3)
+    with pytest.raises(ValueError, match="segments exceed"):
+        RingAttention((8,), 1, 4096, 32, 32, 128, ctx=Ctx(), ring_divide=2)
+    with pytest.raises(ValueError, match="balance_causal=False"):
+        RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx(), ring_divide=2)
+    Ctx.world, Ctx.rank = 2, 1
+    assert RingAttention((2,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx(), balance_causal=False,
+                         ring_divide=7 if 4096 % 7 == 0 else 4).ring_divide == 4
+    assert RingAttention((1,), 1, 4096, 32, 32, 128).memory_bytes() == {"symmetric": 0, "staging": 0, "inbox": 0}

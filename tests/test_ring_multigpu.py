@@ -16,7 +16,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=False, balance=True):
+def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=False, balance=True, ring_divide=1):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
@@ -31,7 +31,8 @@ def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=F
     init_p2p(device=torch.device("cuda", rank))
     q, k, v, do = seeded_qkv(1234, B, S, H, hkv, 128)
     qs, kvs = shard_inputs(q, k, v, world)
-    op = RingAttention(mesh_shape, B, S // world, H, hkv, 128, causal=causal, balance_causal=balance)
+    op = RingAttention(mesh_shape, B, S // world, H, hkv, 128, causal=causal, balance_causal=balance,
+                       ring_divide=ring_divide)
     lq, lkv = qs[rank].cuda(), kvs[rank].cuda()
     ldo = do.chunk(world, 1)[rank].contiguous().cuda()
     outs = []
@@ -43,9 +44,38 @@ def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=F
         else:
             outs.append((o.float().cpu(), lse.cpu()))
     op.check()
+    # the memory model against what was actually allocated
+    model = op.memory_bytes(backward=with_bwd)
+    xs = [x for x in (op._fwd_x, op._bal_x, op._bwd_x) if x is not None]
+    assert model["symmetric"] == sum(x.sym.local.bytes().numel() for x in xs)
+    assert model["staging"] == sum(x.staging.numel() for x in xs)
+    assert model["inbox"] == (op._bal_inbox.local.bytes().numel() if op._bal_inbox is not None else 0)
     ret[rank] = outs
     dist.barrier()
     dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("causal,ring_divide", [(False, 2), (True, 4), (False, 7)])
+def test_ring_divide_pieces_two_gpus(causal, ring_divide):
+    """ring_divide > 1: the peer's shard arrives as sequence pieces, each a flagged segment of the launch."""
+    import torch.multiprocessing as mp
+    from oracle import block
+    from tests.helpers import seeded_qkv
+
+    world = min(torch.cuda.device_count(), 2)
+    if world < 2:
+        pytest.skip("needs 2 GPUs")
+    B, S, H, hkv = 2, 1792, 4, 2   # 896 rows per rank: 448-, 224- and 128-row pieces
+    q, k, v, _ = seeded_qkv(1234, B, S, H, hkv, 128)
+    fo, fl = block.full_attention(q, k, v, 128 ** -0.5, causal=causal)
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, False, False, ring_divide),
+             nprocs=world, join=True)
+    L = S // world
+    for r in range(world):
+        for o, lse in ret[r]:
+            assert (o - fo[:, r * L:(r + 1) * L].float()).abs().max().item() <= 2e-2
+            assert (lse - fl[:, :, r * L:(r + 1) * L]).abs().max().item() <= 1e-3
 
 
 @pytest.mark.parametrize("causal,balance", [(False, True), (True, False), (True, True)])

@@ -152,6 +152,27 @@ def test_ring_segments_match_full_attention(causal):
     _status_ok()
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_growing_scores_force_the_output_rescale(causal):
+    """Keys whose scores grow from tile to tile: the running row max rises by far more than the lazy-rescale
+    threshold (2^8 in the exponent), so the accumulated output is rescaled in tensor memory several times; the
+    last segment repeats the growth across a segment boundary."""
+    from oracle import block
+
+    mb = _mb()
+    B, S, H = 1, 1536, 2
+    q, k, v, _ = seeded_qkv(5, B, S, H, H, 128, device="cuda")
+    ramp = torch.linspace(1.0, 24.0, S, device="cuda").view(1, S, 1, 1)   # |score| grows ~24x along the keys
+    k = (k.float() * ramp).bfloat16()
+    fo, fl = block.full_attention(q.cpu(), k.cpu(), v.cpu(), 128 ** -0.5, causal=causal)
+    o, lse = mb.attn_fwd_segments(q, [(k, v, 0)], 128 ** -0.5, causal=causal)
+    _check(o, lse, fo, fl)
+    segs = [(k[:, :640], v[:, :640], 0), (k[:, 640:], v[:, 640:], 640)]
+    o, lse = mb.attn_fwd_segments(q, segs, 128 ** -0.5, causal=causal)
+    _check(o, lse, fo, fl)
+    _status_ok()
+
+
 @pytest.mark.parametrize("causal,chunks", [(True, 4), (True, 16), (False, 4), (True, 3)])
 def test_host_buffer_forward_matches_oracle(causal, chunks):
     """forward_host(): pinned host tensors in and out, sequence chunks pipelined over PCIe (chunks=3 does not

@@ -54,9 +54,19 @@ __device__ __forceinline__ void iter_next(const FwdSmem* ctl, int nseg, TileIter
   }
 }
 
+// Register budgets.  setmaxnreg can only redistribute the registers the CTA was launched with
+// (threads x launch budget); an increase beyond that pool would block forever, hence the check.
+#define MB_FWD_LAUNCH_REGS 160
+#define MB_FWD_SOFTMAX_REGS 216
+#define MB_FWD_AUX_REGS 48
+#define MB_STR2(x) #x
+#define MB_STR(x) MB_STR2(x)
+static_assert(8 * 32 * MB_FWD_SOFTMAX_REGS + 4 * 32 * MB_FWD_AUX_REGS <= kFwdThreads * MB_FWD_LAUNCH_REGS,
+              "setmaxnreg budgets exceed the registers the CTA is launched with");
+
 // 160 registers/thread at launch (not the 168 that 384 threads would allow): the few warps' worth
 // left free on the SM let the transfer stream's one-thread flag kernels start beside a resident CTA.
-__global__ void __maxnreg__(160)
+__global__ void __maxnreg__(MB_FWD_LAUNCH_REGS)
 attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -114,10 +124,10 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
   // Registers move from the auxiliary warpgroup (warps 8-11) to the two softmax
   // warpgroups; each role changes its own budget as the first thing it does.
   if (warp == 11) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_STR(MB_FWD_AUX_REGS) ";");
   } else if (warp == 9) {
     // ------------------------------------------------------------------ loader
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_STR(MB_FWD_AUX_REGS) ";");
     if (lane == 0 && any_work) {
       tma_prefetch_desc(&maps.q);
       const int act0 = q0 < a.Sq, act1 = q0 + kBM < a.Sq;
@@ -181,7 +191,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     // held its P.V products back while it sat in the issue of its next score product, and the
     // products of the two tiles then fell into the same stretch of time, with the tensor pipe idle
     // in between.)  Positions in the ring of K/V stages follow the load order K0 K1 V0 K2 V1 ...
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_STR(MB_FWD_AUX_REGS) ";");
     if (any_work) {  // whole warp, converged
       constexpr uint32_t kStageUnits = kTileBytes / 16;
       int total = 0;  // K/V tiles this CTA walks through
@@ -274,7 +284,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     }
   } else {
     // ------------------------------------------------------ softmax + epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 " MB_STR(MB_FWD_SOFTMAX_REGS) ";");
     // All control flow below is warp-uniform (the tensor-memory loads and
     // stores are warp-collective); only global stores are predicated per row.
     const int i = warp >> 2;                    // query tile

@@ -16,7 +16,7 @@ constexpr int kHalfBytes = kTileBytes / 2;
 #define MB_FWD_STAGES 4
 #endif
 constexpr int kFwdStages = MB_FWD_STAGES;  // 32 KiB K or V tiles in flight (3, 4 and 5 measured alike)
-constexpr int kFwdThreads = 384;  // 8 softmax warps + one auxiliary warpgroup (MMA, loader, 2 idle)
+constexpr int kFwdThreads = 384;  // 8 softmax warps + one auxiliary warpgroup (2 MMA issuers, loader, 1 idle)
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: tolerate p up to 2^8
 // Optional timeline capture for kernel tuning (compiled in only with -DMB_TRACE): CTA (0,0,0)
 // records clock64() at fixed points of the first kTraceIters K/V iterations.

@@ -23,6 +23,8 @@ from typing import Dict, Optional, Tuple
 
 _SHAPE_RE = re.compile(r"assert (\w+)\.shape == \(([^)]*)\)")
 _MESH_RE = re.compile(r"one_dim_to_n_dim\(dist\.get_rank\(\), \(([^)]*)\)\)")
+# shift(..., ring_divide=d) makes the reference emit an outer loop over K/V sub-blocks around the ring loop
+_DIVIDE_RE = re.compile(r"for S_kv in range\(0, (\d+), (\d+)\):\s*\n\s*for S_kv_ring_idx in range")
 
 
 def _shapes(code: str) -> Dict[str, Tuple[int, ...]]:
@@ -68,7 +70,14 @@ def recognise(code: str) -> Optional[dict]:
     want = ["q", "kv", "o", "lse", "dout", "dq", "dkv", "softmax_scale"] if backward else ["q", "kv", "o", "lse", "softmax_scale"]
     if args[:len(want)] != want:
         return None
+    ring_divide = 1
+    dm = _DIVIDE_RE.search(code)
+    if dm is not None and not backward:
+        total, step = int(dm.group(1)), int(dm.group(2))
+        if total == kv[2] and step > 0 and total % step == 0:
+            ring_divide = total // step
     return dict(name=fn.name, args=args, defaults=fn.args.defaults, mesh=mesh, batch=q[0], seq_local=q[1], hq=q[2],
+                ring_divide=ring_divide,
                 hkv=kv[3], head_dim=q[3], backward=backward, signature=ast.get_source_segment(code, fn.args))
 
 
@@ -81,6 +90,12 @@ def fuse_generated(code: str) -> str:
     fn = [n for n in tree.body if isinstance(n, ast.FunctionDef)][0]
     header = f"def {fn.name}({ast.unparse(fn.args)}):"
     key = (d["mesh"], d["batch"], d["seq_local"], d["hq"], d["hkv"], d["head_dim"])
+    world = 1
+    for n in d["mesh"]:
+        world *= n
+    # the program's ring_divide carries over when its pieces fit the eight segments of one launch
+    rd = d.get("ring_divide", 1)
+    divide = f", ring_divide={rd}, balance_causal=False" if rd > 1 and 1 + (world - 1) * rd <= 8 else ""
     lines = [
         "import torch",
         "from mercury_artifact_b200.ring import RingAttention as _RingAttention",
@@ -95,7 +110,7 @@ def fuse_generated(code: str) -> str:
         "    op = _fused_ops.get(bool(causal))",
         "    if op is None:",
         f"        op = _fused_ops[bool(causal)] = _RingAttention({d['mesh']!r}, {d['batch']}, {d['seq_local']}, "
-        f"{d['hq']}, {d['hkv']}, {d['head_dim']}, causal=bool(causal))",
+        f"{d['hq']}, {d['hkv']}, {d['head_dim']}, causal=bool(causal){divide})",
     ]
     if d["backward"]:
         lines.append("    op.backward(dout, q, kv, o, lse, dq, dkv, softmax_scale)")

@@ -42,7 +42,8 @@ def _imports(ref_root: str):
     sys.dont_write_bytecode = True
 
 
-def generate(ref_root: str, kind: str, world: int, B: int, S: int, H: int, D: int, hkv: int = 0, mesh=None) -> str:
+def generate(ref_root: str, kind: str, world: int, B: int, S: int, H: int, D: int, hkv: int = 0, mesh=None,
+             ring_divide: int = 1) -> str:
     """Emit the per-rank program for one schedule with the reference compiler."""
     _imports(ref_root)
     from mercury.backend import generate_pytorch_code
@@ -85,7 +86,7 @@ def generate(ref_root: str, kind: str, world: int, B: int, S: int, H: int, D: in
     elif world > 1:
         outer = loops[1] if kind == "bwd" else loops[0]
         parallelize(prog, outer, axes[2], dm, 0, len(shape))
-        shift(prog, axes[2], dm, 0, len(shape), 1)
+        shift(prog, axes[2], dm, 0, len(shape), ring_divide)
     eliminate_loops(prog)
     return generate_pytorch_code(prog)
 
@@ -186,6 +187,9 @@ TEXT_ONLY = [
     ("gpu_ring_over_q_p2", "ring_over_q", 2, None, (1, 1024, 4, 4, 128)),
     ("gpu_ring_over_q_p4", "ring_over_q", 4, None, (2, 1024, 4, 4, 128)),
     ("gpu_tree_p2", "tree", 2, None, (1, 1024, 4, 4, 128)),
+    # ring_divide = 2 and 4: the shift primitive halves / quarters the K/V block of a ring round
+    ("gpu_ring_p2_div2", "ring", 2, None, (1, 1024, 4, 4, 128), 2),
+    ("gpu_ring_p2_div4", "ring", 2, None, (1, 1024, 4, 4, 128), 4),
 ]
 
 
@@ -211,11 +215,11 @@ def main():
                 arrays[f"{key}_rank{r}"] = val
         np.savez_compressed(HERE / f"{name}.npz", **arrays)
         print("wrote", name, {k: v.shape for k, v in arrays.items() if k != "meta"})
-    for name, kind, world, mesh, dims in TEXT_ONLY:
+    for name, kind, world, mesh, dims, *rest in TEXT_ONLY:
         if only and name not in only:
             continue
         B, S, H, hkv, D = dims
-        code = generate(ref_root, kind, world, B, S, H, D, hkv=hkv, mesh=mesh)
+        code = generate(ref_root, kind, world, B, S, H, D, hkv=hkv, mesh=mesh, ring_divide=rest[0] if rest else 1)
         (HERE / f"{name}.gen.txt").write_text(code)
         print("wrote", name)
 

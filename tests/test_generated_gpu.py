@@ -55,6 +55,13 @@ def test_ring_program_four_ranks():
     _run_forward("gpu_ring_p4", "flash_attn_pack_kv", 4, 1, 2048, 4, 4)
 
 
+@pytest.mark.parametrize("name", ["gpu_ring_p2_div2", "gpu_ring_p2_div4"])
+def test_ring_divide_programs(name):
+    """shift(..., ring_divide=2 | 4): the reference emits an outer loop over K/V sub-blocks with one ring
+    round each; the text runs unchanged on the drop-in ops (more, smaller block calls and merges)."""
+    _run_forward(name, "flash_attn_pack_kv", 2, 1, 1024, 4, 4)
+
+
 def test_gqa_ring_program():
     _run_forward("gpu_gqa_p2", "gqa_pack_kv", 2, 2, 1024, 8, 2)
 

@@ -157,6 +157,12 @@ def test_emitter_recognises_kv_rings_and_leaves_other_programs_alone():
     fused = emitter.fuse_generated(golden_text("gpu_ring_p4"))
     assert "def flash_attn_pack_kv(q, kv, o, lse, softmax_scale, dropout_p=0, causal=False" in fused
     assert "for S_kv_ring_idx" not in fused and "RingAttention((4,), 1, 512, 4, 4, 128" in fused
+    assert "ring_divide" not in fused
+    compile(fused, "<fused>", "exec")
+    # shift(..., ring_divide=4): the outer sub-block loop is recognised and carried into the fused call
+    assert emitter.recognise(golden_text("gpu_ring_p2_div4"))["ring_divide"] == 4
+    fused = emitter.fuse_generated(golden_text("gpu_ring_p2_div4"))
+    assert "causal=bool(causal), ring_divide=4, balance_causal=False)" in fused and "for S_kv" not in fused
     compile(fused, "<fused>", "exec")
 
 

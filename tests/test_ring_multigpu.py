@@ -142,7 +142,7 @@ def test_ring_backward_two_gpus(causal):
             assert (dkv[1] - gv.chunk(world, 1)[r]).abs().max().item() <= 2e-2
 
 
-def _generated_worker(rank, world, port, ret, fused=False):
+def _generated_worker(rank, world, port, ret, fused=False, fwd_text="gpu_ring_p2"):
     """The reference-emitted per-step programs with the real peer transport (SendRecv over NVLink)."""
     import torch.distributed as dist
 
@@ -164,10 +164,10 @@ def _generated_worker(rank, world, port, ret, fused=False):
     if fused:
         from mercury_artifact_b200 import emitter
 
-        fwd = mb.load_generated(emitter.fuse_generated(golden_text("gpu_ring_p2")))["flash_attn_pack_kv"]
+        fwd = mb.load_generated(emitter.fuse_generated(golden_text(fwd_text)))["flash_attn_pack_kv"]
         bwd = mb.load_generated(emitter.fuse_generated(golden_text("gpu_bwd_p2")))["flash_attn_backward"]
     else:
-        fwd = mb.load_generated(golden_text("gpu_ring_p2"))["flash_attn_pack_kv"]
+        fwd = mb.load_generated(golden_text(fwd_text))["flash_attn_pack_kv"]
         bwd = mb.load_generated(golden_text("gpu_bwd_p2"))["flash_attn_backward"]
     outs = []
     for _ in range(2):
@@ -183,9 +183,11 @@ def _generated_worker(rank, world, port, ret, fused=False):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", [False, True])
-def test_generated_programs_with_peer_transport_two_gpus(fused):
-    """fused=True: the same emitted programs after emitter.fuse_generated (one launch per rank)."""
+@pytest.mark.parametrize("fused,fwd_text", [(False, "gpu_ring_p2"), (True, "gpu_ring_p2"), (False, "gpu_ring_p2_div2"),
+                                            (True, "gpu_ring_p2_div4")])
+def test_generated_programs_with_peer_transport_two_gpus(fused, fwd_text):
+    """fused=True: the same emitted programs after emitter.fuse_generated (one launch per rank).  The _div
+    texts are the ring_divide = 2 / 4 forms of the forward program (sub-block loop around the ring loop)."""
     import torch.multiprocessing as mp
     from oracle import block
     from tests.helpers import seeded_qkv
@@ -193,7 +195,9 @@ def test_generated_programs_with_peer_transport_two_gpus(fused):
     world, B, S, H = 2, 1, 1024, 4
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_generated_worker, args=(world, _free_port(), ret, fused), nprocs=world, join=True)
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_generated_worker, args=(world, _free_port(), ret, fused, fwd_text), nprocs=world, join=True)
     q, k, v, do = seeded_qkv(1234, B, S, H, H, 128)
     scale = 128 ** -0.5
     fo, fl = block.full_attention(q, k, v, scale)

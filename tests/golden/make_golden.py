@@ -2,7 +2,9 @@
 
 Run where the reference checkout is available (it is not needed afterwards):
 
-    python tests/golden/make_golden.py /path/to/mercury_artifact
+    python tests/golden/make_golden.py /path/to/mercury_artifact [case ...]
+
+(the path may also come from MERCURY_REFERENCE; default: a directory "reference" beside this repository)
 
 For each schedule the reference's own compiler (frontend parser -> IR passes ->
 mercury.backend.generate_pytorch_code) emits the per-rank program, which is then
@@ -56,7 +58,7 @@ def generate(ref_root: str, kind: str, world: int, B: int, S: int, H: int, D: in
     import utils.flash_attn_dsl as dsl
     from utils.attn_bwd_dsl import attn_backward_template
 
-    if kind == "ring":
+    if kind in ("ring", "hybrid"):
         src = dsl.flash_attn_pack_kv_template.format(BATCH=B, HEADS=H, SEQ_LEN=S, HEAD_DIM=D)
     elif kind == "gqa":
         src = dsl.gqa_pack_kv_template.format(BATCH=B, HEADS=H, SEQ_LEN=S, HEAD_DIM=D, KV_HEADS=hkv,
@@ -79,6 +81,12 @@ def generate(ref_root: str, kind: str, world: int, B: int, S: int, H: int, D: in
     if world > 1 and kind == "tree":
         # K/V sharded, queries replicated: partial results merged by the all-reduce collective
         parallelize(prog, loops[1], axes[3], dm, 0, len(shape))
+    elif kind == "hybrid":
+        # mesh (ring, heads): K/V ring over the sequence along mesh dimension 0 only, the heads split
+        # along mesh dimension 1 without communication (the shape of tests/test_attn_bwd.py:402-404)
+        parallelize(prog, loops[0], axes[2], dm, 0, 1)
+        shift(prog, axes[2], dm, 0, 1, 1)
+        parallelize(prog, loops[0], axes[1], dm, 1, 2)
     elif world > 1 and kind == "ring_over_q":
         # K/V sharded and stationary; the queries and the packed reduce buffer rotate
         parallelize(prog, loops[1], axes[3], dm, 0, len(shape))
@@ -190,11 +198,24 @@ TEXT_ONLY = [
     # ring_divide = 2 and 4: the shift primitive halves / quarters the K/V block of a ring round
     ("gpu_ring_p2_div2", "ring", 2, None, (1, 1024, 4, 4, 128), 2),
     ("gpu_ring_p2_div4", "ring", 2, None, (1, 1024, 4, 4, 128), 4),
+    # a hybrid schedule: ring over mesh dimension 0, heads parallelised over dimension 1 (must NOT be fused)
+    ("gpu_hybrid_ring2_heads2", "hybrid", 4, (2, 2), (1, 1024, 4, 4, 128)),
+    # bench.py: the reference's shipped path (flash-attn block + merge + NCCL messages) and this package's
+    # per-step drop-ins run these texts at the headline shape (bf16 B1 S32768 H32 D128) on 1/2/4/8 ranks ...
+    ("bench_ring_p1", "ring", 1, None, (1, 32768, 32, 32, 128)),
+    ("bench_ring_p2", "ring", 2, None, (1, 32768, 32, 32, 128)),
+    ("bench_ring_p4", "ring", 4, None, (1, 32768, 32, 32, 128)),
+    ("bench_ring_p8", "ring", 8, None, (1, 32768, 32, 32, 128)),
+    # ... and its CPU arm runs them as gloo ranks on a shortened sequence (same batch, heads, head_dim)
+    ("cpu_ring_p1", "ring", 1, None, (1, 4096, 32, 32, 128)),
+    ("cpu_ring_p2", "ring", 2, None, (1, 4096, 32, 32, 128)),
+    ("cpu_ring_p4", "ring", 4, None, (1, 4096, 32, 32, 128)),
+    ("cpu_ring_p8", "ring", 8, None, (1, 4096, 32, 32, 128)),
 ]
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MERCURY_REFERENCE", str(REPO.parent / "reference"))
     only = set(sys.argv[2:])  # optional: regenerate just the named cases
     port = 29611
     for name, kind, fn_name, world, mesh, dims, seed in CASES:

@@ -62,6 +62,41 @@ def test_ring_divide_programs(name):
     _run_forward(name, "flash_attn_pack_kv", 2, 1, 1024, 4, 4)
 
 
+def test_hybrid_program_ring_by_heads_2x2():
+    """Mesh (2, 2): K/V ring along dimension 0, heads split along dimension 1.  The emitter leaves it alone
+    (see test_emitter_leaves_hybrid_schedules_unfused) and it runs on the per-step drop-ins: rank
+    (i0, i1) holds sequence shard i0 of head group i1."""
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200 import emitter
+    from oracle import block
+
+    text = golden_text("gpu_hybrid_ring2_heads2")
+    assert emitter.fuse_generated(text) == text
+    mb.install_backend(send_recv_cls=MailboxSendRecv, force_stub=True)
+    fn = mb.load_generated(text)["flash_attn_pack_kv"]
+    B, S, H = 1, 1024, 4
+    q, k, v, _ = seeded_qkv(1234, B, S, H, H, 128)
+    scale = 128 ** -0.5
+
+    def rank_body(r):
+        i0, i1 = r % 2, r // 2
+        rows, heads = slice(i0 * 512, (i0 + 1) * 512), slice(i1 * 2, (i1 + 1) * 2)
+        lq = q[:, rows, heads].contiguous().cuda()
+        lkv = torch.stack([k[:, rows, heads], v[:, rows, heads]]).contiguous().cuda()
+        o = torch.zeros_like(lq)
+        lse = torch.zeros(B, 2, 512, device="cuda")
+        fn(lq, lkv, o, lse, scale)
+        return o.float().cpu(), lse.cpu()
+
+    res = run_ranks(4, rank_body)
+    fo, fl = block.full_attention(q, k, v, scale)
+    for r in range(4):
+        i0, i1 = r % 2, r // 2
+        rows, heads = slice(i0 * 512, (i0 + 1) * 512), slice(i1 * 2, (i1 + 1) * 2)
+        assert (res[r][0] - fo[:, rows, heads].float()).abs().max().item() <= O_TOL
+        assert (res[r][1] - fl[:, heads, rows]).abs().max().item() <= LSE_TOL
+
+
 def test_gqa_ring_program():
     _run_forward("gpu_gqa_p2", "gqa_pack_kv", 2, 2, 1024, 8, 2)
 

@@ -52,10 +52,48 @@ def test_oracle_rank_ring_over_gloo_matches_reference_vectors(name):
         assert torch.allclose(ret[r][1], g["t"][f"lse_rank{r}"], atol=2e-6)
 
 
+def _emitted_worker(rank, world, port, name, ret):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    from oracle import refexec
+    from tests.helpers import golden_text, load_golden, shard_inputs
+
+    g = load_golden(name)
+    qs, kvs = shard_inputs(g["t"]["q"], g["t"]["k"], g["t"]["v"], world)
+    ns = refexec.load_emitted(golden_text(name), refexec.cpu_block_forward)
+    fn = ns["gqa_pack_kv" if name.startswith("gqa") else "flash_attn_pack_kv"]
+    o = torch.zeros_like(qs[rank])
+    lse = torch.zeros(g["B"], g["H"], qs[rank].shape[1])
+    fn(qs[rank], kvs[rank], o, lse, g["D"] ** -0.5)
+    ret[rank] = (o, lse)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name", ["ring_p2", "gqa_p2"])
+def test_emitted_program_on_restated_runtime_matches_reference_vectors(name):
+    """The runtime bench.py's CPU arm and GPU baseline use to execute reference-emitted text
+    (oracle/refexec.py: restated SendRecv, index helpers, get_default_args, merge) reproduces what
+    the reference's own runtime produced for the same text and inputs."""
+    import torch.multiprocessing as mp
+    from tests.helpers import load_golden
+
+    g = load_golden(name)
+    ret = mp.Manager().dict()
+    mp.spawn(_emitted_worker, args=(g["world"], _free_port(), name, ret), nprocs=g["world"], join=True)
+    for r in range(g["world"]):
+        assert torch.allclose(ret[r][0], g["t"][f"o_rank{r}"], atol=2e-6)
+        assert torch.allclose(ret[r][1], g["t"][f"lse_rank{r}"], atol=2e-6)
+
+
 def test_bench_reference_arm_under_two_ranks():
     """`bench.py --impl reference --gpus 2` as the driver launches it: rank 0 prints one JSON line,
     the other rank exits 0 silently."""
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE="2", MB_CPU_BUDGET_S="1")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE="2")
     outs = []
     for rank in (0, 1):
         e = dict(env, RANK=str(rank), LOCAL_RANK=str(rank))
@@ -66,6 +104,7 @@ def test_bench_reference_arm_under_two_ranks():
     line = json.loads(outs[0].stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["value"] > 0
     assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
+    assert line["cpu_baseline"]["cores"] >= 2 and "2 CPU/gloo process(es)" in line["cpu_baseline"]["sample"]
     assert line["unit"] == "TFLOP/s" and line["higher_is_better"] is True
 
 

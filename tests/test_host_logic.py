@@ -1,5 +1,6 @@
 """CPU tests: mesh helpers, schedules, the exported C ABI, the drop-in namespace."""
 import ctypes
+import os
 import re
 import subprocess
 import sys
@@ -9,6 +10,9 @@ import pytest
 import torch
 
 ROOT = Path(__file__).resolve().parent.parent
+# the reference checkout (needed only by the tests that compare with its own functions):
+# MERCURY_REFERENCE, else a directory named "reference" beside this repository
+REFERENCE = Path(os.environ.get("MERCURY_REFERENCE") or (ROOT.parent / "reference"))
 
 
 def test_library_exports_every_declared_symbol():
@@ -60,9 +64,9 @@ def test_mesh_helpers_match_oracle_and_reference_semantics():
     assert mesh.shift_tuple_element((3, 1), 0, 1, 4) == (0, 1)
 
 
-@pytest.mark.skipif(not Path("/root/reference/mercury").exists(), reason="reference checkout not present")
+@pytest.mark.skipif(not (REFERENCE / "mercury").exists(), reason="reference checkout not present (MERCURY_REFERENCE)")
 def test_mesh_helpers_equal_reference_functions():
-    sys.path.insert(0, "/root/reference")
+    sys.path.insert(0, str(REFERENCE))
     sys.dont_write_bytecode = True
     try:
         from mercury.backend.pytorch import utils as ref
@@ -166,14 +170,48 @@ def test_emitter_recognises_kv_rings_and_leaves_other_programs_alone():
     compile(fused, "<fused>", "exec")
 
 
-@pytest.mark.skipif(not Path("/root/reference/mercury").exists(), reason="reference checkout not present")
+def test_emitter_leaves_hybrid_schedules_unfused(caplog):
+    """A K/V ring along mesh dimension 0 with the heads parallelised along dimension 1 (text emitted by the
+    reference's compiler for mesh (2, 2)): the ranks along dimension 1 hold other heads, not further K/V
+    shards, so a RingAttention over all four ranks would be wrong.  The text must come back unchanged, and
+    the log says why."""
+    import logging
+
+    from mercury_artifact_b200 import emitter
+    from tests.helpers import golden_text
+
+    text = golden_text("gpu_hybrid_ring2_heads2")
+    with caplog.at_level(logging.INFO, logger="mercury_artifact_b200.emitter"):
+        emitter._reported.clear()
+        assert emitter.recognise(text) is None
+        assert emitter.fuse_generated(text) == text
+        assert emitter.fuse_generated(text) == text           # reported once, not per call
+    said = [r.getMessage() for r in caplog.records]
+    assert len(said) == 1 and "left as emitted" in said[0] and "hybrid" in said[0]
+    # the same for a single-ring text whose mesh gains a second dimension nothing rotates along ...
+    widened = golden_text("gpu_ring_p2").replace("(2,))", "(2, 2))")
+    assert emitter.recognise(widened) is None and emitter.fuse_generated(widened) == widened
+    # ... and for a double ring whose loops are nested the other way round (dimension 1 innermost)
+    swapped = golden_text("gpu_double_ring_4x2").replace("shift_tuple_element(indices, 0,", "shift_tuple_element(indices, 9,") \
+        .replace("shift_tuple_element(indices, 1,", "shift_tuple_element(indices, 0,") \
+        .replace("shift_tuple_element(indices, 9,", "shift_tuple_element(indices, 1,")
+    assert emitter.recognise(swapped) is None
+    # a recognised program is reported as fused
+    with caplog.at_level(logging.INFO, logger="mercury_artifact_b200.emitter"):
+        caplog.clear()
+        emitter._reported.clear()
+        emitter.fuse_generated(golden_text("gpu_double_ring_4x2"))
+    assert any("fused into one RingAttention.forward call over mesh (4, 2)" in r.getMessage() for r in caplog.records)
+
+
+@pytest.mark.skipif(not (REFERENCE / "mercury").exists(), reason="reference checkout not present (MERCURY_REFERENCE)")
 def test_search_hooks_fuse_the_program_the_reference_search_would_time():
     """install_search_hooks(): the text bench_program (mercury/search/bench.py) execs is the fused form
     for a ring schedule and the reference's own text for a schedule the emitter does not recognise."""
     import ast
     import textwrap
 
-    sys.path.insert(0, "/root/reference")
+    sys.path.insert(0, str(REFERENCE))
     sys.dont_write_bytecode = True
     try:
         import mercury.search.bench as ref_bench

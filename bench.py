@@ -280,6 +280,18 @@ class Job:
         t1 = time.time()
         return self.max_over_ranks(e0.elapsed_time(e1) / steps), t0, t1
 
+    def inputs_in(self, op, B, L, H, hkv, D, with_dout=False, seed=1234):
+        """The same seeded shard, produced inside the op's symmetric buffers (no staging copies when they
+        are passed to forward() / backward()), plus its o and lse result tensors."""
+        bufs = op.symmetric_buffers()
+        q, kv, dout = self.inputs(B, L, H, hkv, D, with_dout=with_dout, seed=seed)
+        bufs["q"].copy_(q)
+        bufs["kv"].copy_(kv)
+        if with_dout:
+            bufs["dout"].copy_(dout)
+        self.torch.cuda.synchronize()
+        return bufs["q"], bufs["kv"], bufs.get("dout"), bufs["o"], bufs["lse"]
+
     def inputs(self, B, L, H, hkv, D, with_dout=False, seed=1234):
         """Seeded synthetic shard of this rank, generated on the device: q, kv (and dout) ~ N(0,1)*0.5."""
         torch = self.torch
@@ -326,10 +338,8 @@ def run_extra(job, name, peak, sustained, steps=3, warmup=2):
     scale = D ** -0.5
     mesh = mesh_for(name, world)
     backward = name.endswith("_bwd")
-    q, kv, dout = job.inputs(B, L, H, hkv, D, with_dout=backward, seed=4321)
-    op = RingAttention(mesh, B, L, H, hkv, D, causal=causal)
-    o = torch.empty_like(q)
-    lse = torch.empty(B, H, L, dtype=torch.float32, device=job.dev)
+    op = RingAttention(mesh, B, L, H, hkv, D, causal=causal, backward=backward)
+    q, kv, dout, o, lse = job.inputs_in(op, B, L, H, hkv, D, with_dout=backward, seed=4321)
     fl = flops_fwd(B, S, H, D, causal)
     res = {"workload": workload_name(name, world).replace("forward", "backward" if backward else "forward"),
            "mesh": list(mesh), "steps": steps, "warmup": warmup}
@@ -465,16 +475,15 @@ def run_ours(args):
     scale = D ** -0.5
     mesh = mesh_for(args.workload, world)
 
-    q, kv, dout = job.inputs(B, L, H, hkv, D, with_dout=True)
+    if world > 1:
+        mb.comm.init_p2p()
+    op = RingAttention(mesh, B, L, H, hkv, D, causal=causal, backward=True)
+    # resident inputs live in the op's symmetric buffers (its documented zero-copy mode): peers pull
+    # q / kv straight from there and results arrive in o / lse without staging copies
+    q, kv, dout, o, lse = job.inputs_in(op, B, L, H, hkv, D, with_dout=True)
     q_host, kv_host = q.cpu().pin_memory(), kv.cpu().pin_memory()
     o_host = torch.empty(B, L, H, D, dtype=torch.bfloat16).pin_memory()
     lse_host = torch.empty(B, H, L, dtype=torch.float32).pin_memory()
-    o = torch.empty_like(q)
-    lse = torch.empty(B, H, L, dtype=torch.float32, device=dev)
-
-    if world > 1:
-        mb.comm.init_p2p()
-    op = RingAttention(mesh, B, L, H, hkv, D, causal=causal)
     stream = job.stream
 
     def step_resident():
@@ -496,7 +505,19 @@ def run_ours(args):
     ms, t0, t1 = job.timed(step_resident, args.steps, warm)
     clocks = sampler.stop(t0, t1) if rank == 0 else None
     status = _lib.status_fetch(stream.cuda_stream)
+    launches_per_step = op.last_launches if world > 1 else 1
     parity = parity_forward(job, q, kv, o, lse, causal, scale)
+
+    # the same forward with ORDINARY tensors in and out: one device-to-device staging copy per tensor
+    ms_plain = None
+    if world > 1:
+        pq, pkv = q.clone(), kv.clone()
+        po, pl = torch.empty_like(q), torch.empty_like(lse)
+        ms_plain, _, _ = job.timed(lambda: op.forward(pq, pkv, po, pl, scale), max(3, args.steps // 2), 3)
+        status |= _lib.status_fetch(stream.cuda_stream)
+        parity["plain_tensors_o_max_abs_vs_resident"] = job.max_over_ranks((po.float() - o.float()).abs().max().item())
+        parity["ok"] = bool(parity["ok"] and parity["plain_tensors_o_max_abs_vs_resident"] <= O_TOL)
+        del pq, pkv, po, pl
 
     ms_e2e, _, _ = job.timed(step_e2e, max(3, args.steps // 2), 3)
     status |= _lib.status_fetch(stream.cuda_stream)
@@ -563,6 +584,8 @@ def run_ours(args):
                        "(%.0f MiB) through this GPU" % (3 * B * L * H * D * 2 / 2 ** 20, world,
                                                        2 * B * S * hkv * D * 2 / 2 ** 20)),
                 "per_gpu_tflops": per_gpu,
+                "buffers": "q / kv / o / lse in the op's symmetric buffers (zero-copy mode)" if world > 1 else "ordinary tensors",
+                "ms_per_step_with_ordinary_tensors": ms_plain,
                 "causal_balance": bool(getattr(op, "balanced", False)),
                 "frac_of_bf16_peak_per_gpu": per_gpu / peak,
             },
@@ -571,7 +594,9 @@ def run_ours(args):
                     "d2h_bytes_per_step": (o_host.numel() * 2 + lse_host.numel() * 4) * world},
             "fwd_bwd": {"value": 3.5 * fl_total / (ms_fb * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_fb,
                         "note": "forward + backward per step, FLOPs = 3.5 x forward (backward counted as 2.5 x)"},
-            "gpu_launches": args.steps * op.launches_per_forward * world,
+            # kernels of this package inside the timed region: per step and rank one attention launch plus, on
+            # more than one rank, the one-warp flag kernels of the transfer protocol (copies are copy-engine work)
+            "gpu_launches": args.steps * launches_per_step * world,
             # tensor roofline of the attention launch.  At one GPU the launch is the step; at N > 1 the step is
             # one attention launch per rank whose loader waits in-kernel for shards still in flight, so the
             # figure is the per-GPU rate of the whole step (kernel + exposed transfer), not a bare kernel rate.

@@ -35,7 +35,8 @@ extern "C" {
 #define MB_E_DEVICE (-5)      /* the status word reported a device-side timeout */
 #define MB_E_TOO_LARGE (-6)   /* problem exceeds the fixed scratch of an allocation-free entry point */
 
-#define MB_MAX_SEGMENTS 8
+#define MB_MAX_SEGMENTS 32 /* K/V (or stream) shards per launch: 8 ranks x ring_divide 4, or a 32-way mesh */
+#define MB_MAX_JOBS 4      /* query shards per mb_attn_fwd_multi launch */
 
 /* One sequence shard of K and V: [batch, sk, hkv, head_dim] views. */
 typedef struct mb_kv_segment {
@@ -77,6 +78,49 @@ typedef struct mb_attn_fwd_args {
  * (utils/flash_attn_dsl.py:51-71) -- once the shards are reachable.
  * A row that sees no key gets o = 0 and lse = -inf. */
 MB_API int mb_attn_fwd(const mb_attn_fwd_args* args, void* cuda_stream);
+
+/* One query shard of a multi-shard forward launch, with where its results go. */
+typedef struct mb_fwd_job {
+  const void* q; /* [batch, sq, hq, head_dim] */
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  void* o; /* [batch, sq, hq, head_dim] bf16, written; may be a peer GPU's memory mapped here */
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  float* lse; /* [batch, hq, sq] fp32, written; may be peer memory */
+  int64_t lse_stride_b, lse_stride_h; /* 0, 0 selects the contiguous layout */
+  int32_t sq;
+  int32_t q_off;     /* global position of query row 0 (causal rule only) */
+  uint32_t seg_mask; /* bit s set: this job attends to segment s (0 selects all segments) */
+  int32_t reserved;
+  /* Optional arrival flag of the query shard (a word on this GPU), as ready_flag of mb_kv_segment. */
+  const int32_t* q_ready_flag;
+  int32_t q_ready_value;
+  /* Optional completion flag: once every CTA of this job has stored its rows, the kernel stores
+   * done_value to *done_flag with release semantics at system scope (the word may live on the GPU that
+   * owns the rows).  Needs done_counter: a zero-initialised word on this GPU that the kernel uses to
+   * count finished CTAs and leaves at zero again. */
+  int32_t done_value;
+  int32_t* done_flag;
+  int32_t* done_counter;
+} mb_fwd_job;
+
+typedef struct mb_attn_fwd_multi_args {
+  int32_t batch, hq, hkv, head_dim;
+  int32_t causal;
+  float softmax_scale;
+  int32_t njobs;
+  int32_t nseg;
+  mb_fwd_job job[MB_MAX_JOBS];
+  mb_kv_segment seg[MB_MAX_SEGMENTS];
+  int32_t* status;
+} mb_attn_fwd_multi_args;
+
+/* mb_attn_fwd for up to MB_MAX_JOBS query shards in ONE launch (CTAs of the jobs are scheduled together,
+ * first job first).  The balanced causal ring uses it: a rank computes two query half-shards that belong
+ * to other ranks against the K/V shards they can see, writes o / lse straight into the owners' memory and
+ * raises each owner's completion flag from the kernel.  It replaces the same reference calls as
+ * mb_attn_fwd; the re-assignment of query rows has no counterpart in the reference (whose generated
+ * loop is only correct for causal = False, utils/flash_attn_dsl.py:167). */
+MB_API int mb_attn_fwd_multi(const mb_attn_fwd_multi_args* args, void* cuda_stream);
 
 /* ---- backward ------------------------------------------------------------------------- */
 
@@ -248,6 +292,23 @@ MB_API int mb_flag_signal(int32_t* flag, int32_t value, void* cuda_stream);
  * timeout code to `status` (NULL: the library's word) and lets the stream continue. */
 MB_API int mb_flag_wait(const int32_t* flag, int32_t value, uint64_t timeout_ns, int32_t* status,
                         void* cuda_stream);
+
+/* The same for up to 32 flags with ONE kernel launch: flags / values are HOST arrays of n entries. */
+MB_API int mb_flags_signal(int32_t* const* flags, const int32_t* values, int32_t n, void* cuda_stream);
+MB_API int mb_flags_wait(const int32_t* const* flags, const int32_t* values, int32_t n, uint64_t timeout_ns,
+                         int32_t* status, void* cuda_stream);
+
+/* How long a kernel waits for a shard that another GPU has to deliver (the ready_flag of a segment or of
+ * a job's queries) before it gives up with status 109.  Process-wide, applies to launches made afterwards.
+ * Default 30 000 ms: ranks of a job may be seconds apart (first-call module load, data loading, a
+ * checkpoint on one rank), and the reference's NCCL path would simply wait.  Waits inside one CTA keep
+ * their fixed budget of about a second. */
+MB_API int mb_set_peer_wait_ms(uint32_t milliseconds);
+
+/* Enqueue a copy of the status word of the current device into *pinned_host_dst (page-locked host
+ * memory) on `cuda_stream`, without synchronising and without clearing the word.  Lets a caller notice a
+ * timed-out wait of an earlier call at its next call instead of paying a synchronisation per call. */
+MB_API int mb_status_peek_async(int32_t* pinned_host_dst, void* cuda_stream);
 
 /* Synchronise `cuda_stream`, copy the library's status word of the current
  * device into *out (0 = no device-side timeout so far) and clear it. */

@@ -9,7 +9,8 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-MB_MAX_SEGMENTS = 8
+MB_MAX_SEGMENTS = 32
+MB_MAX_JOBS = 4
 
 MB_SUCCESS = 0
 ERROR_NAMES = {
@@ -71,6 +72,47 @@ class AttnFwdArgs(C.Structure):
         ("causal", C.c_int32),
         ("softmax_scale", C.c_float),
         ("nseg", C.c_int32),
+        ("seg", KVSegment * MB_MAX_SEGMENTS),
+        ("status", C.c_void_p),
+    ]
+
+
+class FwdJob(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p),
+        ("q_stride_b", C.c_int64),
+        ("q_stride_s", C.c_int64),
+        ("q_stride_h", C.c_int64),
+        ("o", C.c_void_p),
+        ("o_stride_b", C.c_int64),
+        ("o_stride_s", C.c_int64),
+        ("o_stride_h", C.c_int64),
+        ("lse", C.c_void_p),
+        ("lse_stride_b", C.c_int64),
+        ("lse_stride_h", C.c_int64),
+        ("sq", C.c_int32),
+        ("q_off", C.c_int32),
+        ("seg_mask", C.c_uint32),
+        ("reserved", C.c_int32),
+        ("q_ready_flag", C.c_void_p),
+        ("q_ready_value", C.c_int32),
+        ("done_value", C.c_int32),
+        ("done_flag", C.c_void_p),
+        ("done_counter", C.c_void_p),
+    ]
+
+
+class AttnFwdMultiArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32),
+        ("hq", C.c_int32),
+        ("hkv", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("causal", C.c_int32),
+        ("softmax_scale", C.c_float),
+        ("njobs", C.c_int32),
+        ("nseg", C.c_int32),
+        ("job", FwdJob * MB_MAX_JOBS),
         ("seg", KVSegment * MB_MAX_SEGMENTS),
         ("status", C.c_void_p),
     ]
@@ -226,6 +268,7 @@ class MercuryB200Error(RuntimeError):
 _SIGNATURES = {
     "mb_version": [],
     "mb_attn_fwd": [C.POINTER(AttnFwdArgs), C.c_void_p],
+    "mb_attn_fwd_multi": [C.POINTER(AttnFwdMultiArgs), C.c_void_p],
     "mb_attn_bwd_preprocess": [C.POINTER(BwdPreprocessArgs), C.c_void_p],
     "mb_attn_bwd": [C.POINTER(AttnBwdArgs), C.c_void_p],
     "mb_attn_bwd_block_noalloc": [C.POINTER(AttnBwdBlockArgs), C.c_void_p],
@@ -241,6 +284,10 @@ _SIGNATURES = {
     "mb_copy_async": [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p],
     "mb_flag_signal": [C.c_void_p, C.c_int32, C.c_void_p],
     "mb_flag_wait": [C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p],
+    "mb_flags_signal": [C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int32, C.c_void_p],
+    "mb_flags_wait": [C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p],
+    "mb_set_peer_wait_ms": [C.c_uint32],
+    "mb_status_peek_async": [C.c_void_p, C.c_void_p],
     "mb_status_fetch": [C.POINTER(C.c_int32), C.c_void_p],
 }
 
@@ -261,20 +308,27 @@ def _bind(path: Path) -> C.CDLL:
 
 
 def _load() -> C.CDLL:
-    """Load libmercury_b200.so; if it is missing or older than this binding, rebuild it once
-    with nvcc.  There is no other path: without the library the import fails."""
+    """Load libmercury_b200.so; if it is missing, older than this binding, or -- where nvcc and the
+    sources are at hand -- built from other sources than the ones on disk, rebuild it once with nvcc
+    (under a file lock, so that the ranks of a job do not all compile into the same file).
+    There is no other path: without the library the import fails."""
     from . import build as _build
 
+    custom = bool(_os.environ.get("MERCURY_B200_LIB"))
+    reason = None
     try:
         if LIB_PATH.exists():
-            return _bind(LIB_PATH)
-        reason = f"{LIB_PATH} is missing"
+            if custom or _build.find_nvcc() is None or _build.is_current():
+                return _bind(LIB_PATH)
+            reason = f"{LIB_PATH} was built from other sources than the ones on disk"
+        else:
+            reason = f"{LIB_PATH} is missing"
     except AttributeError as e:
         reason = f"{LIB_PATH} is stale ({e})"
-    if _build.find_nvcc() is None:
+    if custom or _build.find_nvcc() is None:
         raise ImportError(f"{reason} and nvcc is not available to build it "
                           "(python -m mercury_artifact_b200.build); there is no fallback path")
-    _build.build(force=True)
+    _build.build()
     return _bind(LIB_PATH)
 
 
@@ -291,6 +345,64 @@ def status_fetch(stream_ptr: int) -> int:
     out = C.c_int32(0)
     check(lib.mb_status_fetch(C.byref(out), C.c_void_p(stream_ptr)), "mb_status_fetch")
     return int(out.value)
+
+
+def set_peer_wait_ms(ms: int) -> None:
+    """Budget of in-kernel waits for shards that other GPUs deliver (launches made afterwards)."""
+    check(lib.mb_set_peer_wait_ms(C.c_uint32(int(ms))), "mb_set_peer_wait_ms")
+
+
+# MB_PEER_WAIT_MS: how long a kernel (and a stream-level flag wait) waits for another rank before it
+# gives up with a status code.  Default 30 s, far above the skew that first-call module loading, data
+# loading or a checkpoint on one rank produce.
+PEER_WAIT_MS = int(float(_os.environ.get("MB_PEER_WAIT_MS", "30000")))
+set_peer_wait_ms(PEER_WAIT_MS)
+
+
+class StatusMonitor:
+    """Notices a timed-out device-side wait of an EARLIER call without synchronising.
+
+    post(stream) enqueues a copy of the device status word into pinned host memory behind the work
+    just queued; poll() looks at the copies that have completed and raises if one is non-zero.  Ops
+    call poll() when they begin and post() when they have enqueued their work, so a timeout surfaces
+    as an exception at the latest at the next call that finds the copy complete, or at check()."""
+
+    def __init__(self):
+        import torch
+
+        self._torch = torch
+        self._slots = []   # (pinned int32 tensor, event recorded behind the copy into it)
+        self._free = []
+        self._bad = 0
+
+    def _reap(self) -> None:
+        keep = []
+        for host, ev in self._slots:
+            if ev.query():
+                self._bad = self._bad or int(host.item())
+                self._free.append(host)
+            else:
+                keep.append((host, ev))
+        self._slots = keep
+
+    def post(self, stream) -> None:
+        torch = self._torch
+        self._reap()
+        host = self._free.pop() if self._free else torch.zeros(1, dtype=torch.int32).pin_memory()
+        check(lib.mb_status_peek_async(C.c_void_p(host.data_ptr()), C.c_void_p(stream.cuda_stream)),
+              "mb_status_peek_async")
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        self._slots.append((host, ev))
+
+    def poll(self) -> None:
+        self._reap()
+        if self._bad:
+            bad, self._bad = self._bad, 0
+            status_fetch(self._torch.cuda.current_stream().cuda_stream)   # synchronise and clear the device word
+            raise MercuryB200Error(
+                f"a device-side wait of an earlier call timed out: {STATUS_NAMES.get(bad, bad)} (code {bad}); "
+                "the results of that call are invalid")
 
 
 def raise_on_status(stream_ptr: int) -> None:

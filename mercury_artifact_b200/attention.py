@@ -108,15 +108,74 @@ def attn_fwd_segments(
     return (None, None) if raw else (out, lse)
 
 
+def attn_fwd_multi(jobs: Sequence[dict], segments: Sequence[tuple], softmax_scale: float, causal: bool,
+                   batch: int, hq: int, hkv: int, head_dim: int, device: torch.device) -> None:
+    """Several query shards against one list of K/V segments in ONE launch (mb_attn_fwd_multi).
+
+    jobs: dicts with
+      q            tensor [batch, sq, hq, d] (a view is fine)
+      q_off        global position of its row 0
+      out_raw      (address, stride_b, stride_s, stride_h) of the bf16 result, lse_raw (address, stride_b,
+                   stride_h) of the fp32 log-sum-exp -- raw addresses, so that they can point into another
+                   rank's memory mapped into this process
+      q_flag       optional (address, value): arrival flag of the query shard
+      done         optional (flag address, value, counter address): completion flag raised by the kernel
+      seg_mask     optional bit mask of the segments the job attends to (default: all)
+    segments: as in attn_fwd_segments.  CTAs of job 0 are scheduled first."""
+    if not 1 <= len(jobs) <= _lib.MB_MAX_JOBS:
+        raise ValueError(f"1..{_lib.MB_MAX_JOBS} jobs per launch")
+    if len(segments) > _lib.MB_MAX_SEGMENTS:
+        raise ValueError(f"at most {_lib.MB_MAX_SEGMENTS} K/V segments per call")
+    a = _lib.AttnFwdMultiArgs()
+    a.batch, a.hq, a.hkv, a.head_dim = batch, hq, hkv, head_dim
+    a.causal = 1 if causal else 0
+    a.softmax_scale = float(softmax_scale)
+    a.njobs, a.nseg = len(jobs), len(segments)
+    a.status = None
+    for i, jb in enumerate(jobs):
+        q = jb["q"]
+        _check_bshd(q, "q")
+        if q.shape[0] != batch or q.shape[2] != hq or q.shape[3] != head_dim:
+            raise ValueError("job q does not match batch / hq / head_dim")
+        j = a.job[i]
+        j.q = q.data_ptr()
+        j.q_stride_b, j.q_stride_s, j.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
+        j.o, j.o_stride_b, j.o_stride_s, j.o_stride_h = jb["out_raw"]
+        j.lse, j.lse_stride_b, j.lse_stride_h = jb["lse_raw"]
+        j.sq, j.q_off = q.shape[1], int(jb.get("q_off", 0))
+        j.seg_mask = int(jb.get("seg_mask", 0))
+        if jb.get("q_flag"):
+            j.q_ready_flag, j.q_ready_value = jb["q_flag"][0], int(jb["q_flag"][1])
+        if jb.get("done"):
+            j.done_flag, j.done_value, j.done_counter = jb["done"][0], int(jb["done"][1]), jb["done"][2]
+    for i, segment in enumerate(segments):
+        k, v, k_off = segment[:3]
+        flag_ptr, flag_value = (segment[3], segment[4]) if len(segment) >= 5 and segment[3] else (None, 0)
+        _check_bshd(k, "k")
+        _check_bshd(v, "v")
+        if k.shape != v.shape or k.stride() != v.stride():
+            raise ValueError("k and v of one segment must share shape and strides")
+        if k.shape[0] != batch or k.shape[2] != hkv or k.shape[3] != head_dim:
+            raise ValueError("segment does not match batch / hkv / head_dim")
+        seg = a.seg[i]
+        seg.k, seg.v = k.data_ptr(), v.data_ptr()
+        seg.stride_b, seg.stride_s, seg.stride_h = k.stride(0), k.stride(1), k.stride(2)
+        seg.sk, seg.k_off = k.shape[1], int(k_off)
+        seg.ready_flag, seg.ready_value = flag_ptr, int(flag_value)
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib.mb_attn_fwd_multi(C.byref(a), C.c_void_p(_stream_ptr())), "mb_attn_fwd_multi")
+
+
 # ------------------------------------------------------------------------------------------
 # backward
 # ------------------------------------------------------------------------------------------
 class RowStats:
     """lse2 = -lse*log2(e) (stored negated) and delta = rowsum(dout*out) of one query shard, padded to 64 rows."""
 
-    def __init__(self, lse2: torch.Tensor, delta: torch.Tensor, rows: int):
+    def __init__(self, lse2: torch.Tensor, delta: torch.Tensor, rows: int, pad: Optional[int] = None):
         self.lse2, self.delta, self.rows = lse2, delta, rows
-        self.pad = lse2.shape[-1]
+        # row pitch of the [batch, hq, pad] arrays; a view that starts at a later row keeps the pitch
+        self.pad = lse2.shape[-1] if pad is None else pad
 
 
 def _pad64(n: int) -> int:

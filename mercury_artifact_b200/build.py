@@ -50,25 +50,49 @@ def find_nvcc() -> str | None:
     return None
 
 
+def is_current() -> bool:
+    """Whether the library on disk was built from the sources on disk (digest stamp written by build())."""
+    try:
+        return LIB_PATH.exists() and STAMP.exists() and STAMP.read_text().strip() == _digest()
+    except OSError:
+        return False
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every .cu under csrc/ into one shared library; no-op if up to date."""
-    digest = _digest()
-    if not force and LIB_PATH.exists() and STAMP.exists() and STAMP.read_text().strip() == digest:
+    """Compile every .cu under csrc/ into one shared library; no-op if up to date.
+
+    Safe to call from several processes at once (the ranks of a job importing the package): the
+    compile runs under an exclusive file lock into a temporary file that is renamed into place, so
+    nobody ever loads a half-written library, and whoever gets the lock second finds it up to date."""
+    import fcntl
+
+    if not force and is_current():
         return LIB_PATH
     nvcc = find_nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found: libmercury_b200.so cannot be built")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", str(INCLUDE), "-o", str(LIB_PATH), *map(str, sources())]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-        print(" ".join(cmd), file=sys.stderr)
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
-    if verbose:
-        print(res.stderr, file=sys.stderr)
-    STAMP.write_text(digest + "\n")
+    with open(PKG_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            digest = _digest()
+            if not force and is_current():
+                return LIB_PATH
+            tmp = LIB_PATH.with_suffix(f".tmp{os.getpid()}.so")
+            cmd = [nvcc, *NVCC_FLAGS, "-I", str(INCLUDE), "-o", str(tmp), *map(str, sources())]
+            if verbose:
+                cmd.insert(1, "-Xptxas")
+                cmd.insert(2, "-v")
+                print(" ".join(cmd), file=sys.stderr)
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                tmp.unlink(missing_ok=True)
+                raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
+            if verbose:
+                print(res.stderr, file=sys.stderr)
+            os.replace(tmp, LIB_PATH)
+            STAMP.write_text(digest + "\n")
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH
 
 

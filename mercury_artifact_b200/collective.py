@@ -18,9 +18,9 @@ import torch
 
 from . import _lib
 from .comm import default_context
-from .ring import _ShardExchange
+from .ring import _Exchange
 
-_exchanges: Dict[Tuple[int, Tuple[int, ...]], _ShardExchange] = {}
+_exchanges: Dict[Tuple[int, Tuple[int, ...]], _Exchange] = {}
 
 
 def _members(group) -> Tuple[int, ...]:
@@ -60,24 +60,21 @@ def update_out_and_lse_collective(tensor: torch.Tensor, op, group, dst: Optional
     key = (nbytes, ranks)
     x = _exchanges.get(key)
     if x is None:
-        x = _exchanges[key] = _ShardExchange(ctx, nbytes)  # collective: every rank of the job creates it
+        # collective: every rank of the job creates it.  No staging: the merge kernel reads peers' slots directly.
+        x = _exchanges[key] = _Exchange(ctx, nbytes, 0, staging=False)
     main = torch.cuda.current_stream()
     comm = ctx.comm_stream
-    slot = x.begin(main, peers=ranks)
+    e = x.begin(main)
+    x.wait_slot_free(ranks)       # every member has finished reading my buffer of the previous merge
     with torch.cuda.stream(comm):
-        slot[:nbytes].view(torch.float32).view(tensor.shape).copy_(tensor, non_blocking=True)
-    published = x.publish(peers=ranks)
+        x.slot()[:nbytes].view(torch.float32).view(tensor.shape).copy_(tensor, non_blocking=True)
+    published = x.publish(ranks)
     main.wait_event(published)
-    e = x.epoch
-    for r in ranks:
-        if r != me:
-            ctx.wait_flag(x._ready_ptr(me, r), e, main)
+    ctx.wait_many([(x.ready_ptr(me, r), e) for r in ranks if r != me], main)
     if op == dist.all_reduce or dst == me:
-        srcs = (C.c_void_p * len(ranks))(*[x.sym.ptr(r, (e % 2) * x.slot_bytes) for r in ranks])
+        srcs = (C.c_void_p * len(ranks))(*[x.sym.ptr(r, 0) for r in ranks])
         with torch.cuda.device(tensor.device):
             _lib.check(_lib.lib.mb_tree_merge(srcs, len(ranks), tensor.data_ptr(), rows, width,
                                               C.c_void_p(main.cuda_stream)), "mb_tree_merge")
-    for r in ranks:
-        if r != me:
-            ctx.signal(x._done_ptr(r, me), e, main)
+    ctx.signal_many([(x.done_ptr(r, me), e) for r in ranks if r != me], main)
     return tensor

@@ -21,7 +21,9 @@ import torch
 
 from . import _lib
 
-_FLAG_TIMEOUT_NS = int(float(os.environ.get("MB_FLAG_TIMEOUT_MS", "5000")) * 1e6)
+# Stream-level flag waits give up after MB_FLAG_TIMEOUT_MS (default: the peer-wait budget MB_PEER_WAIT_MS,
+# 30 s) and leave status 107 behind; see _lib.StatusMonitor for how that reaches the caller.
+_FLAG_TIMEOUT_NS = int(float(os.environ.get("MB_FLAG_TIMEOUT_MS", str(_lib.PEER_WAIT_MS))) * 1e6)
 
 
 def _align(n: int, a: int = 256) -> int:
@@ -120,7 +122,13 @@ class PeerContext:
         # flag kernels would sit behind the pending CTAs of a running attention kernel that is itself
         # waiting for them.
         self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        # further transfer streams: copies queued on different streams can use different copy engines
+        n_extra = max(0, int(os.environ.get("MB_COPY_STREAMS", "2")) - 1)
+        self.comm_streams = [self.comm_stream] + [torch.cuda.Stream(device=self.device, priority=-1)
+                                                  for _ in range(n_extra)]
         self._channels: Dict[Tuple[int, int], "_Channel"] = {}
+        self.monitor = _lib.StatusMonitor()
+        self.launch_count = 0   # flag kernels launched through this context (copies are not kernels)
 
     # -- primitive, stream-ordered operations ----------------------------------------------
     def copy(self, dst_ptr: int, src_ptr: int, nbytes: int, stream: torch.cuda.Stream) -> None:
@@ -128,13 +136,37 @@ class PeerContext:
                                           C.c_void_p(stream.cuda_stream)), "mb_copy_async")
 
     def signal(self, flag_ptr: int, value: int, stream: torch.cuda.Stream) -> None:
+        self.launch_count += 1
         _lib.check(_lib.lib.mb_flag_signal(C.c_void_p(flag_ptr), C.c_int32(value), C.c_void_p(stream.cuda_stream)),
                    "mb_flag_signal")
 
     def wait_flag(self, flag_ptr: int, value: int, stream: torch.cuda.Stream, timeout_ns: Optional[int] = None) -> None:
+        self.launch_count += 1
         _lib.check(_lib.lib.mb_flag_wait(C.c_void_p(flag_ptr), C.c_int32(value),
                                          C.c_uint64(_FLAG_TIMEOUT_NS if timeout_ns is None else timeout_ns),
                                          None, C.c_void_p(stream.cuda_stream)), "mb_flag_wait")
+
+    def signal_many(self, flags, stream: torch.cuda.Stream) -> None:
+        """[(flag address, value), ...] raised by ONE kernel launch (at most 32 per launch)."""
+        flags = list(flags)
+        for i in range(0, len(flags), 32):
+            self.launch_count += 1
+            part = flags[i:i + 32]
+            ptrs = (C.c_void_p * len(part))(*[p for p, _ in part])
+            vals = (C.c_int32 * len(part))(*[int(v) for _, v in part])
+            _lib.check(_lib.lib.mb_flags_signal(ptrs, vals, len(part), C.c_void_p(stream.cuda_stream)), "mb_flags_signal")
+
+    def wait_many(self, flags, stream: torch.cuda.Stream, timeout_ns: Optional[int] = None) -> None:
+        """Wait until every (flag address, value) has been reached, with ONE kernel launch per 32 flags."""
+        flags = list(flags)
+        for i in range(0, len(flags), 32):
+            self.launch_count += 1
+            part = flags[i:i + 32]
+            ptrs = (C.c_void_p * len(part))(*[p for p, _ in part])
+            vals = (C.c_int32 * len(part))(*[int(v) for _, v in part])
+            _lib.check(_lib.lib.mb_flags_wait(ptrs, vals, len(part),
+                                              C.c_uint64(_FLAG_TIMEOUT_NS if timeout_ns is None else timeout_ns), None,
+                                              C.c_void_p(stream.cuda_stream)), "mb_flags_wait")
 
     def check(self) -> None:
         """Synchronise and raise if any device-side wait timed out since the last check."""
@@ -156,16 +188,41 @@ class PeerContext:
             idx += 1
 
 
+MAX_PEERS = 64
+
+
+def message_words(seq: int, me: int, to_rank: int, from_rank: int):
+    """Flag words and value of message `seq` of a channel, as (rank whose memory holds the word, kind,
+    peer index, slot) tuples -- the protocol in one place, so that it can be checked without a GPU.
+
+    Message m uses inbox slot m % 2 and flag value m + 1.  Every word has exactly ONE writer: a
+    `ready` word is indexed by the sending peer, a `credit` word by the granting peer.  In nested
+    rings successive messages of one slot come from different neighbours (inner ring, then the outer
+    hop), and those neighbours are not ordered with respect to each other; with a word per slot only,
+    a late store of a smaller value by one of them could lower the word under a waiter, and an early
+    grant by the other could satisfy a wait it was not meant for.
+
+      grant       (from_rank, "credit", me, slot)   I tell my sender that my slot is free again
+      wait_credit (me, "credit", to_rank, slot)     I wait for my receiver's grant before copying
+      raise_ready (to_rank, "ready", me, slot)      I tell my receiver that the copy has landed
+      wait_ready  (me, "ready", from_rank, slot)    I wait for my sender's copy
+    """
+    slot = seq % 2
+    return dict(slot=slot, value=seq + 1,
+                grant=(from_rank, "credit", me, slot), wait_credit=(me, "credit", to_rank, slot),
+                raise_ready=(to_rank, "ready", me, slot), wait_ready=(me, "ready", from_rank, slot))
+
+
 class _Channel:
     """Two inbox slots plus flags for one stream of same-sized messages.
 
-    Flag words (int32), all in the receiver's memory:
-      ready[slot]  raised by the sender after its copy into inbox[slot] landed
-      credit[slot] raised by the receiver when inbox[slot] may be overwritten
-    Message m of the channel uses slot m % 2 and flag value m + 1 (never reset).
+    Flag words (int32), all in the receiver's memory, one per (peer, slot) -- see message_words():
+      ready[peer][slot]  raised by sender `peer` after its copy into inbox[slot] landed
+      credit[peer][slot] raised by receiver `peer` when ITS inbox[slot] may be overwritten by this rank
+    Flag values only grow (message number + 1) and are never reset.
     """
 
-    FLAG_BYTES = 256
+    FLAG_BYTES = 2 * MAX_PEERS * 2 * 4
 
     def __init__(self, ctx: PeerContext, slot_bytes: int):
         self.ctx = ctx
@@ -177,11 +234,13 @@ class _Channel:
     def inbox_ptr(self, rank: int, slot: int) -> int:
         return self.buf.ptr(rank, slot * self.slot_bytes)
 
-    def ready_ptr(self, rank: int, slot: int) -> int:
-        return self.buf.ptr(rank, 2 * self.slot_bytes + 4 * slot)
-
-    def credit_ptr(self, rank: int, slot: int) -> int:
-        return self.buf.ptr(rank, 2 * self.slot_bytes + 16 + 4 * slot)
+    def word_ptr(self, word) -> int:
+        """Address (in this process) of a flag word named by a message_words() tuple."""
+        rank, kind, peer, slot = word
+        if not 0 <= peer < MAX_PEERS:
+            raise ValueError(f"at most {MAX_PEERS} ranks per channel")
+        base = 2 * self.slot_bytes + (0 if kind == "ready" else MAX_PEERS * 2 * 4)
+        return self.buf.ptr(rank, base + 4 * (2 * peer + slot))
 
 
 _default_ctx: Optional[PeerContext] = None
@@ -235,20 +294,23 @@ class SendRecv:
         if self._pending is not None:
             raise RuntimeError("commit called twice")
         ctx = self._ctx or default_context()
+        ctx.monitor.poll()   # a wait of an earlier exchange that ran out raises here
         main = torch.cuda.current_stream()
         comm = ctx.comm_stream
         comm.wait_stream(main)
         pending = []
         for to_rank, from_rank, send_tensor, inbox, recv_tensor, seq, nbytes in self._ops:
-            ch, slot, val = self._channel, seq % 2, seq + 1
+            ch = self._channel
+            w = message_words(seq, ctx.rank, to_rank, from_rank)
+            slot, val = w["slot"], w["value"]
             # Grant my sender the slot (everything queued so far on my stream has run by now);
             # the credit word lives in the SENDER's memory, so this store crosses NVLink.
-            ctx.signal(ch.credit_ptr(from_rank, slot), val, comm)
-            # Wait for the grant of the rank I send to (a word in my own memory).
-            ctx.wait_flag(ch.credit_ptr(ctx.rank, slot), val, comm)
+            ctx.signal(ch.word_ptr(w["grant"]), val, comm)
+            # Wait for the grant of the rank I send to (a word in my own memory, written only by it).
+            ctx.wait_flag(ch.word_ptr(w["wait_credit"]), val, comm)
             ctx.copy(ch.inbox_ptr(to_rank, slot), send_tensor.data_ptr(), nbytes, comm)
-            ctx.signal(ch.ready_ptr(to_rank, slot), val, comm)
-            pending.append((ch, slot, val, inbox, recv_tensor, send_tensor))
+            ctx.signal(ch.word_ptr(w["raise_ready"]), val, comm)
+            pending.append((ch, w, inbox, recv_tensor, send_tensor))
         self._pending = pending
 
     def wait(self) -> None:
@@ -256,11 +318,12 @@ class SendRecv:
             raise RuntimeError("wait called before commit")
         ctx = self._ctx or default_context()
         comm = ctx.comm_stream
-        for ch, slot, val, inbox, recv_tensor, _send in self._pending:
-            ctx.wait_flag(ch.ready_ptr(ctx.rank, slot), val, comm)
+        for ch, w, inbox, recv_tensor, _send in self._pending:
+            ctx.wait_flag(ch.word_ptr(w["wait_ready"]), w["value"], comm)
             if recv_tensor is not None:
                 with torch.cuda.stream(comm):
                     recv_tensor.copy_(inbox)
         torch.cuda.current_stream().wait_stream(comm)
+        ctx.monitor.post(torch.cuda.current_stream())
         self._pending = None
         self._ops = []

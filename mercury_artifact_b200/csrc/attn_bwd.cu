@@ -67,6 +67,8 @@ struct BwdArgs {
   int seg_stat_pad[MB_MAX_SEGMENTS];            // padded row count of those arrays
   const int* seg_flag[MB_MAX_SEGMENTS];
   int seg_flag_value[MB_MAX_SEGMENTS];
+  long long peer_wait_cycles;                   // budget of a wait for a shard another GPU delivers
+  long long wait_cycles;                        // budget of a wait inside the CTA (plus the above with flags)
   const float* own_lse2;                        // dQ mode: stats of the owner's queries [B,Hq,own_pad]
   const float* own_delta;
   int own_stat_pad;
@@ -241,7 +243,8 @@ __device__ __forceinline__ void ew_compute(const uint32_t (&xr)[32], const uint3
 }
 
 template <int kDummy>
-__global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps maps, const BwdArgs a) {
+__global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps maps,
+                                                 const __grid_constant__ BwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sOwn = smem;
@@ -270,6 +273,7 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
     mbar_init(&ctl->acc_full, 1);
     mbar_init(&ctl->drain, 1);
     ctl->abort_word = 0;
+#pragma unroll 1
     for (int s = 0; s < MB_MAX_SEGMENTS; ++s) {
       int f = 0, l = 0;
       if (s < a.nseg) step_range(a, own0, s, &f, &l);
@@ -304,7 +308,8 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
       for (int s = 0; s < a.nseg && ok; ++s) {
         const int f = ctl->seg_first[s], l = ctl->seg_last[s];
         if (l > f && a.seg_flag[s] != nullptr) {
-          ok = flag_wait_ge(a.seg_flag[s], a.seg_flag_value[s], abort_word, MB_ERR_TIMEOUT_SEGMENT);
+          ok = flag_wait_ge(a.seg_flag[s], a.seg_flag_value[s], abort_word, MB_ERR_TIMEOUT_SEGMENT,
+                            a.peer_wait_cycles);
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int g = 0; g < n_sub && ok; ++g) {
@@ -312,7 +317,7 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
           for (int t = f; t < l; ++t) {
             const int stage = n % kBwdStages, round = n / kBwdStages;
             if (round > 0 &&
-                !mbar_wait(&ctl->str_empty[stage], (round - 1) & 1, abort_word, MB_ERR_TIMEOUT_KV_EMPTY)) {
+                !mbar_wait(&ctl->str_empty[stage], (round - 1) & 1, abort_word, MB_ERR_TIMEOUT_KV_EMPTY, a.wait_cycles)) {
               ok = false;
               break;
             }
@@ -355,7 +360,7 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
       constexpr uint32_t kStageUnits = kBwdStageBytes / 16, kStrGUnits = kStrTileBytes / 16;
       const int T = total_steps;
       const bool dkv = a.mode_dkv != 0;
-      bool ok = mbar_wait_warp(&ctl->own_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
+      bool ok = mbar_wait_warp(&ctl->own_full, 0, abort_word, MB_ERR_TIMEOUT_Q, a.wait_cycles);
 
       auto issue_xy = [&](int t) {
         const uint32_t su = (t % kBwdStages) * kStageUnits;
@@ -375,21 +380,21 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
       };
 
       for (int t = 0; t < 2 && t < T && ok; ++t) {
-        ok = mbar_wait_warp(&ctl->str_full[t % kBwdStages], 0, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+        ok = mbar_wait_warp(&ctl->str_full[t % kBwdStages], 0, abort_word, MB_ERR_TIMEOUT_KV_FULL, a.wait_cycles);
         if (ok) {
           tc_fence_after();
           issue_xy(t);
         }
       }
       for (int t = 0; t < T && ok; ++t) {
-        ok = mbar_wait_warp(&ctl->pd_full[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_P);
+        ok = mbar_wait_warp(&ctl->pd_full[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_P, a.wait_cycles);
         if (!ok) break;
         tc_fence_after();
         issue_acc(t);
         if (t + 2 < T) {
           const int n = t + 2;
           ok = mbar_wait_warp(&ctl->str_full[n % kBwdStages], (n / kBwdStages) & 1, abort_word,
-                              MB_ERR_TIMEOUT_KV_FULL);
+                              MB_ERR_TIMEOUT_KV_FULL, a.wait_cycles);
           if (!ok) break;
           tc_fence_after();
           issue_xy(n);
@@ -429,11 +434,11 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
       for (int g = 0; g < n_sub && ok; ++g) {
         for (int st = f; st < l; ++st, ++t) {
           const int buf = t & 1, stage = t % kBwdStages;
-          ok = mbar_wait_warp(&ctl->xy_full[buf], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_S);
+          ok = mbar_wait_warp(&ctl->xy_full[buf], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_S, a.wait_cycles);
           if (!ok) break;
           // the stage's statistics arrived with the stream tile (completed long ago; cheap re-check)
           if (a.mode_dkv) {
-            ok = mbar_wait_warp(&ctl->str_full[stage], (t / kBwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+            ok = mbar_wait_warp(&ctl->str_full[stage], (t / kBwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL, a.wait_cycles);
             if (!ok) break;
           }
           tc_fence_after();
@@ -474,7 +479,7 @@ __global__ void __maxnreg__(160) attn_bwd_kernel(const __grid_constant__ BwdMaps
     // epilogue: each warp stores its lane quarter x column half of the accumulators
     if (ok && own0 < a.own_rows) {
       const bool have = total_steps > 0;
-      if (have) ok = mbar_wait_warp(&ctl->acc_full, 0, abort_word, MB_ERR_TIMEOUT_O);
+      if (have) ok = mbar_wait_warp(&ctl->acc_full, 0, abort_word, MB_ERR_TIMEOUT_O, a.wait_cycles);
       if (ok) {
         if (have) tc_fence_after();
         const bool store = own0 + row < a.own_rows;
@@ -637,10 +642,10 @@ int launch_attn_bwd(const mb_attn_bwd_args* x, cudaStream_t stream) {
   int rc = set_smem_attr_once();
   if (rc != MB_SUCCESS) return rc;
 
-  BwdMaps maps;
-  BwdArgs a;
-  memset(&maps, 0, sizeof(maps));
+  static thread_local BwdMaps maps;  // 8.4 KB of tensor maps: the launch copies them
+  static thread_local BwdArgs a;
   memset(&a, 0, sizeof(a));
+  a.peer_wait_cycles = peer_wait_cycles();
   const int h_own = dkv ? x->hkv : x->hq;
   const int h_str = dkv ? x->hq : x->hkv;
   if (make_map(&maps.own, x->own, h_own, x->own_rows, x->batch, x->own_stride_b, x->own_stride_s, x->own_stride_h,
@@ -669,6 +674,9 @@ int launch_attn_bwd(const mb_attn_bwd_args* x, cudaStream_t stream) {
     ++nseg;
   }
   a.nseg = nseg;
+  bool has_flags = false;
+  for (int s = 0; s < nseg; ++s) has_flags |= a.seg_flag[s] != nullptr;
+  a.wait_cycles = kWaitCycleLimit + (has_flags ? a.peer_wait_cycles : 0);
   a.mode_dkv = dkv ? 1 : 0;
   a.B = x->batch;
   a.own_rows = x->own_rows;

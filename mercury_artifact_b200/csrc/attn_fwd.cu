@@ -29,6 +29,12 @@
 //
 // K/V tiles are loaded in the order K0 K1 V0 K2 V1 K3 V2 ...: the score product of K/V tile g+1 is
 // issued before the P.V product of tile g needs its V tile.
+//
+// A launch may carry several "jobs": query shards with their own output pointers, sharing the segment
+// list.  blockIdx.x runs through the query-tile pairs of job 0, then of job 1, ...  A job can name an
+// arrival flag for its queries (they may still be in flight from another GPU) and a completion flag,
+// which the job's last CTA raises with a release store at system scope once every row of the job has
+// been stored -- the rows, and the flag, may live in another GPU's memory.
 #include "attn_fwd_common.cuh"
 
 namespace mb {
@@ -67,7 +73,7 @@ static_assert(8 * 32 * MB_FWD_SOFTMAX_REGS + 4 * 32 * MB_FWD_AUX_REGS <= kFwdThr
 // 160 registers/thread at launch (not the 168 that 384 threads would allow): the few warps' worth
 // left free on the SM let the transfer stream's one-thread flag kernels start beside a resident CTA.
 __global__ void __maxnreg__(MB_FWD_LAUNCH_REGS)
-attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
+attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ FwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -79,8 +85,16 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
-  // Heavier (later) query rows first when causal.
-  const int pair = a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  // Which job this CTA belongs to; within a job the heavier (later) query rows come first when causal.
+  if (tid == 0) {
+    int jid = 0;
+    while (jid + 1 < a.njobs && (int)blockIdx.x >= a.job[jid + 1].x_begin) ++jid;
+    ctl->jid = jid;
+    ctl->job = a.job[jid];
+  }
+  __syncthreads();
+  const FwdJob& J = ctl->job;
+  const int pair = a.causal ? (J.n_pairs - 1 - ((int)blockIdx.x - J.x_begin)) : ((int)blockIdx.x - J.x_begin);
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int hkv = h / a.group;
@@ -101,10 +115,13 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     mbar_init(&ctl->s_free, 4);
     mbar_init(&ctl->drain, 2);
     ctl->abort_word = 0;
+#pragma unroll 1
     for (int i = 0; i < 2; ++i)
+#pragma unroll 1
       for (int s = 0; s < MB_MAX_SEGMENTS; ++s)
-        ctl->n_tiles[i][s] =
-            s < a.nseg ? visible_tiles(q0 + i * kBM, a.Sq, a.q_off, a.causal, a.seg_sk[s], a.seg_koff[s]) : 0;
+        ctl->n_tiles[i][s] = (s < a.nseg && ((J.seg_mask >> s) & 1u))
+                                 ? visible_tiles(q0 + i * kBM, J.Sq, J.q_off, a.causal, a.seg_sk[s], a.seg_koff[s])
+                                 : 0;
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -129,29 +146,39 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     // ------------------------------------------------------------------ loader
     asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_STR(MB_FWD_AUX_REGS) ";");
     if (lane == 0 && any_work) {
-      tma_prefetch_desc(&maps.q);
-      const int act0 = q0 < a.Sq, act1 = q0 + kBM < a.Sq;
-      mbar_expect_tx(&ctl->q_full, (act0 + act1) * kTileBytes);
-      for (int i = 0; i < 2; ++i) {
-        if (q0 + i * kBM < a.Sq) {
-          tma_load_4d(sQ + i * kTileBytes, &maps.q, &ctl->q_full, 0, h, q0 + i * kBM, b);
-          tma_load_4d(sQ + i * kTileBytes + kHalfBytes, &maps.q, &ctl->q_full, 64, h, q0 + i * kBM, b);
+      bool ok = true;
+      const CUtensorMap* qmap = &maps.q[ctl->jid];
+      tma_prefetch_desc(qmap);
+      if (J.q_flag != nullptr) {
+        // The queries are being staged from another GPU: wait (bounded) for their arrival flag.  On a
+        // timeout the Q load is skipped; every other role then runs into the abort word and returns.
+        ok = flag_wait_ge(J.q_flag, J.q_flag_value, abort_word, MB_ERR_TIMEOUT_SEGMENT, a.peer_wait_cycles);
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
+      if (ok) {
+        const int act0 = q0 < J.Sq, act1 = q0 + kBM < J.Sq;
+        mbar_expect_tx(&ctl->q_full, (act0 + act1) * kTileBytes);
+        for (int i = 0; i < 2; ++i) {
+          if (q0 + i * kBM < J.Sq) {
+            tma_load_4d(sQ + i * kTileBytes, qmap, &ctl->q_full, 0, h, q0 + i * kBM, b);
+            tma_load_4d(sQ + i * kTileBytes + kHalfBytes, qmap, &ctl->q_full, 64, h, q0 + i * kBM, b);
+          }
         }
       }
       int n = 0;
-      bool ok = true;
       // One K or V tile into the next stage of the ring.
       auto load_tile = [&](int which, const TileIter& it) {
         if (which == 0 && it.jt == 0 && a.seg_flag[it.s] != nullptr) {
           // The shard is being staged by another stream: wait (bounded) for its arrival flag,
           // then order the TMA reads (async proxy) after the flag read.
-          ok = flag_wait_ge(a.seg_flag[it.s], a.seg_flag_value[it.s], abort_word, MB_ERR_TIMEOUT_SEGMENT);
+          ok = flag_wait_ge(a.seg_flag[it.s], a.seg_flag_value[it.s], abort_word, MB_ERR_TIMEOUT_SEGMENT,
+                            a.peer_wait_cycles);
           asm volatile("fence.proxy.async;" ::: "memory");
           if (!ok) return;
         }
         const int stage = n % kFwdStages;
         const int round = n / kFwdStages;
-        if (round > 0 && !mbar_wait(&ctl->kv_empty[stage], (round - 1) & 1, abort_word, MB_ERR_TIMEOUT_KV_EMPTY)) {
+        if (round > 0 && !mbar_wait(&ctl->kv_empty[stage], (round - 1) & 1, abort_word, MB_ERR_TIMEOUT_KV_EMPTY, a.wait_cycles)) {
           ok = false;
           return;
         }
@@ -164,7 +191,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
       };
       TileIter nxt = iter_first(ctl, a.nseg);
       TileIter cur = nxt;
-      if (nxt.s < a.nseg) {
+      if (ok && nxt.s < a.nseg) {
         load_tile(0, nxt);
         iter_next(ctl, a.nseg, nxt);
       }
@@ -203,27 +230,26 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
         const uint64_t k_desc0 = umma_smem_desc(smem_u32(sKV), 16, 1024);  // K-major view of stage 0
         int g = 0;    // K/V tile index over all segments
         int use = 0;  // uses of the score region so far, by either query tile
-        ok = mbar_wait_warp(&ctl->q_full, 0, abort_word, MB_ERR_TIMEOUT_Q);
+        ok = mbar_wait_warp(&ctl->q_full, 0, abort_word, MB_ERR_TIMEOUT_Q, a.wait_cycles);
         for (int s = 0; s < a.nseg && ok; ++s) {
           const int n0 = ctl->n_tiles[0][s], n1 = ctl->n_tiles[1][s];
           const int nmax = max(n0, n1);
           for (int jt = 0; jt < nmax && ok; ++jt, ++g) {
             const int pos = g == 0 ? 0 : 2 * g - 1;
             const int stage = pos % kFwdStages;
-            ok = mbar_wait_warp(&ctl->kv_full[stage], (pos / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+            ok = mbar_wait_warp(&ctl->kv_full[stage], (pos / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL, a.wait_cycles);
             if (!ok) break;
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
               if (jt < (i ? n1 : n0)) {
                 // the score region's previous user must have copied its scores out
                 if (use > 0) {
-                  ok = mbar_wait_warp(&ctl->s_free, (use - 1) & 1, abort_word, MB_ERR_TIMEOUT_S);
+                  ok = mbar_wait_warp(&ctl->s_free, (use - 1) & 1, abort_word, MB_ERR_TIMEOUT_S, a.wait_cycles);
                   if (!ok) break;
                 }
                 tc_fence_after();
                 issue_qk(tmem, q_desc + i * kStageUnits, k_desc0 + stage * kStageUnits, idesc_qk);
                 umma_commit_elect(&ctl->s_full[i]);
-                MB_TRACE_AT(2, use >> 1, i * 6 + 5);
                 ++use;
               }
             }
@@ -242,7 +268,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
           for (int jt = 0; jt < nmax && ok; ++jt, ++g) {
             const int pos = g == total - 1 ? 2 * total - 1 : 2 * g + 2;
             const int stage = pos % kFwdStages;
-            ok = mbar_wait_warp(&ctl->kv_full[stage], (pos / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL);
+            ok = mbar_wait_warp(&ctl->kv_full[stage], (pos / kFwdStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL, a.wait_cycles);
             if (!ok) break;
             const uint64_t v_desc = v_desc0 + stage * kStageUnits;
 #pragma unroll
@@ -250,20 +276,15 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
               if (jt < (i ? n1 : n0)) {
                 const int cnt = i ? cnt1 : cnt0;
                 const uint32_t tPi = tmem + 128 + i * 64, tOi = tmem + 256 + i * 128;
-                MB_TRACE_AT(2, cnt, i * 6 + 0);
-                ok = mbar_wait_warp(&ctl->p_full[i][0], cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+                ok = mbar_wait_warp(&ctl->p_full[i][0], cnt & 1, abort_word, MB_ERR_TIMEOUT_P, a.wait_cycles);
                 if (!ok) break;
-                MB_TRACE_AT(2, cnt, i * 6 + 1);
                 tc_fence_after();
                 issue_pv_half(tOi, tPi, v_desc, idesc_pv, cnt == 0 ? 0u : 1u);
-                MB_TRACE_AT(2, cnt, i * 6 + 2);
-                ok = mbar_wait_warp(&ctl->p_full[i][1], cnt & 1, abort_word, MB_ERR_TIMEOUT_P);
+                ok = mbar_wait_warp(&ctl->p_full[i][1], cnt & 1, abort_word, MB_ERR_TIMEOUT_P, a.wait_cycles);
                 if (!ok) break;
-                MB_TRACE_AT(2, cnt, i * 6 + 3);
                 tc_fence_after();
                 issue_pv_half(tOi, tPi + 32, v_desc + 4 * 128, idesc_pv, 1u);
                 umma_commit_elect(&ctl->o_full[i]);
-                MB_TRACE_AT(2, cnt, i * 6 + 4);
                 if (i) ++cnt1;
                 else ++cnt0;
               }
@@ -293,8 +314,8 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     const uint32_t tS = tmem + lane_field;
     const uint32_t tPi = tmem + 128 + i * 64 + lane_field;
     const uint32_t tOi = tmem + 256 + i * 128 + lane_field;
-    const int qrow = q0 + i * kBM + row;        // row inside this rank's Q
-    const int qpos = a.q_off + qrow;            // global position used by the causal rule
+    // global position used by the causal rule; the row inside the job's Q is qpos - J.q_off
+    const int qpos = J.q_off + q0 + i * kBM + row;
 
     float m_ref = -INFINITY;  // reference max (raw score units)
     float l = 0.f;            // running sum of exp2
@@ -306,10 +327,8 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
       const int sk = a.seg_sk[s];
       const int koff = a.seg_koff[s];
       for (int jt = 0; jt < nt; ++jt) {
-        if (row == 0) MB_TRACE_AT(i, cnt, 0);
-        ok = mbar_wait_warp(&ctl->s_full[i], cnt & 1, abort_word, MB_ERR_TIMEOUT_S);
+        ok = mbar_wait_warp(&ctl->s_full[i], cnt & 1, abort_word, MB_ERR_TIMEOUT_S, a.wait_cycles);
         if (!ok) break;
-        if (row == 0) MB_TRACE_AT(i, cnt, 1);
         tc_fence_after();
         uint32_t sr[4][32];
         tmem_ld32(tS + 0, sr[0]);
@@ -320,12 +339,11 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
         // The scores are in registers: hand the score region to its next user.
         tc_fence_before();
         mbar_arrive_elect(&ctl->s_free);
-        if (row == 0) MB_TRACE_AT(i, cnt, 2);
 
         // masking: only tiles that cross the segment end or the causal diagonal
         const int k0 = jt * kBN;
         const bool tile_needs_mask =
-            (k0 + kBN > sk) || (a.causal && (koff + k0 + kBN - 1 > a.q_off + q0 + i * kBM));
+            (k0 + kBN > sk) || (a.causal && (koff + k0 + kBN - 1 > qpos - row));  // qpos - row: the tile's first row
         if (tile_needs_mask) {
           int limit = sk - k0;  // columns >= limit are invisible
           if (a.causal) limit = min(limit, qpos - koff - k0 + 1);
@@ -345,14 +363,13 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
           mx3 = max3(mx3, __uint_as_float(sr[3][e]), __uint_as_float(sr[3][e + 1]));
         }
         const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        if (row == 0) MB_TRACE_AT(i, cnt, 3);
 
         if (cnt == 0) {
           m_ref = m_tile;
         } else {
           // The previous P.V product of this query tile must be complete before its probabilities
           // are overwritten, and before O is rescaled.
-          ok = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O);
+          ok = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O, a.wait_cycles);
           if (!ok) break;
           tc_fence_after();
           const float m_new = fmaxf(m_ref, m_tile);
@@ -406,7 +423,6 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(&ctl->p_full[i][half]);
-          if (row == 0) MB_TRACE_AT(i, cnt, 4 + half);
         }
         {
           float s0, s1;
@@ -418,16 +434,17 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     }
 
     // epilogue: O / l -> bf16, LSE = ln(sum exp(scale * s)).  Tiles whose rows all lie past Sq skip it.
-    if (ok && q0 + i * kBM < a.Sq) {
+    const int qrow = qpos - J.q_off;
+    if (ok && qrow - row < J.Sq) {
       bool have = cnt > 0;
       if (have) {
-        have = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O);
+        have = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O, a.wait_cycles);
         ok = have;
       }
       if (ok) {
-        const bool store = qrow < a.Sq;
+        const bool store = qrow < J.Sq;
         const float inv_l = (have && l > 0.f) ? 1.f / l : 0.f;
-        __nv_bfloat16* optr = a.o + (long long)b * a.o_sb + (long long)qrow * a.o_ss + (long long)h * a.o_sh;
+        __nv_bfloat16* optr = J.o + (long long)b * J.o_sb + (long long)qrow * J.o_ss + (long long)h * J.o_sh;
         if (have) tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -454,7 +471,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
         }
         if (store) {
           const float lse = (have && l > 0.f) ? (m_ref * a.scale + __logf(l)) : -INFINITY;
-          a.lse[(long long)b * a.lse_sb + (long long)h * a.lse_sh + qrow] = lse;
+          J.lse[(long long)b * J.lse_sb + (long long)h * J.lse_sh + qrow] = lse;
         }
       }
     }
@@ -467,6 +484,20 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdArgs a) {
     tmem_dealloc(tmem, 512);
   }
   if (tid == 0 && ctl->abort_word != 0 && a.status != nullptr) atomicCAS(a.status, 0, ctl->abort_word);
+  if (tid == 0 && J.done_flag != nullptr) {
+    // Every thread's result stores precede the barrier above; this fence makes them visible at system
+    // scope (they may have gone to another GPU) before the arrival is counted.  The CTA that counts the
+    // last arrival publishes the job: the flag's reader then sees every row of every CTA.  A CTA that
+    // gave up still counts, so that the word returns to zero; the status word tells the host.
+    __threadfence_system();
+    int prev;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(J.done_counter) : "memory");
+    if (prev == J.n_ctas - 1) {
+      *J.done_counter = 0;
+      __threadfence_system();
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(J.done_flag), "r"(J.done_value) : "memory");
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -481,14 +512,20 @@ static int make_tile_map(CUtensorMap* map, const void* ptr, int D, int H, int S,
   return encode_tiled_bf16(map, const_cast<void*>(ptr), 4, dims, strides, box, estr);
 }
 
-int launch_attn_fwd(const mb_attn_fwd_args* x, cudaStream_t stream) {
+static long long g_peer_wait_ms = 30000;
+
+void set_peer_wait_ms(unsigned ms) { g_peer_wait_ms = ms == 0 ? 1 : ms; }
+
+// Cycle budget of waits for data other GPUs deliver: the SM clock never exceeds 2 GHz here, so
+// 2e6 cycles per millisecond is at least the requested time.
+long long peer_wait_cycles() { return g_peer_wait_ms * 2000000LL; }
+
+int launch_attn_fwd_multi(const mb_attn_fwd_multi_args* x, cudaStream_t stream) {
   if (x == nullptr) return MB_E_INVALID;
   if (x->head_dim != kD) return MB_E_UNSUPPORTED;
   if (x->batch <= 0 || x->hq <= 0 || x->hkv <= 0 || x->hq % x->hkv != 0) return MB_E_INVALID;
   if (x->nseg < 0 || x->nseg > MB_MAX_SEGMENTS) return MB_E_INVALID;
-  if (x->sq < 0) return MB_E_INVALID;
-  if (x->sq == 0) return MB_SUCCESS;
-  if (x->q == nullptr || x->o == nullptr || x->lse == nullptr) return MB_E_INVALID;
+  if (x->njobs < 1 || x->njobs > MB_MAX_JOBS) return MB_E_INVALID;
 
   static bool attr_set[64] = {};
   int dev = 0;
@@ -500,15 +537,17 @@ int launch_attn_fwd(const mb_attn_fwd_args* x, cudaStream_t stream) {
     attr_set[dev] = true;
   }
 
-  FwdMaps maps;
-  FwdArgs a;
-  memset(&maps, 0, sizeof(maps));
+  // Kernel parameters (8.7 KB of tensor maps + 1.3 KB of scalars) are assembled in static storage:
+  // the launch copies them, and launches of one process are issued from one thread at a time per device.
+  static thread_local FwdMaps maps;
+  static thread_local FwdArgs a;
   memset(&a, 0, sizeof(a));
-  if (make_tile_map(&maps.q, x->q, kD, x->hq, x->sq, x->batch, x->q_stride_b, x->q_stride_s, x->q_stride_h))
-    return MB_E_TENSORMAP;
+  // empty segments are dropped; a job's segment mask is re-indexed accordingly
+  int seg_new[MB_MAX_SEGMENTS];
   int nseg = 0;
   for (int s = 0; s < x->nseg; ++s) {
     const mb_kv_segment& g = x->seg[s];
+    seg_new[s] = -1;
     if (g.sk < 0) return MB_E_INVALID;
     if (g.sk == 0) continue;  // an empty shard contributes nothing
     if (g.k == nullptr || g.v == nullptr) return MB_E_INVALID;
@@ -520,36 +559,91 @@ int launch_attn_fwd(const mb_attn_fwd_args* x, cudaStream_t stream) {
     a.seg_koff[nseg] = g.k_off;
     a.seg_flag[nseg] = g.ready_flag;
     a.seg_flag_value[nseg] = g.ready_value;
-    ++nseg;
+    seg_new[s] = nseg++;
   }
   a.nseg = nseg;
-  a.o = reinterpret_cast<__nv_bfloat16*>(x->o);
-  a.o_sb = x->o_stride_b;
-  a.o_ss = x->o_stride_s;
-  a.o_sh = x->o_stride_h;
-  a.lse = x->lse;
-  a.lse_sh = x->lse_stride_h ? x->lse_stride_h : x->sq;
-  a.lse_sb = x->lse_stride_b ? x->lse_stride_b : (long long)x->hq * x->sq;
+  int njobs = 0, x_total = 0;
+  for (int j = 0; j < x->njobs; ++j) {
+    const mb_fwd_job& g = x->job[j];
+    if (g.sq < 0) return MB_E_INVALID;
+    if (g.sq == 0) {
+      // nothing to compute, but a completion flag must still be raised: only allowed without one
+      if (g.done_flag != nullptr) return MB_E_INVALID;
+      continue;
+    }
+    if (g.q == nullptr || g.o == nullptr || g.lse == nullptr) return MB_E_INVALID;
+    if (g.done_flag != nullptr && g.done_counter == nullptr) return MB_E_INVALID;
+    if (make_tile_map(&maps.q[njobs], g.q, kD, x->hq, g.sq, x->batch, g.q_stride_b, g.q_stride_s, g.q_stride_h))
+      return MB_E_TENSORMAP;
+    FwdJob& J = a.job[njobs];
+    J.o = reinterpret_cast<__nv_bfloat16*>(g.o);
+    J.o_sb = g.o_stride_b;
+    J.o_ss = g.o_stride_s;
+    J.o_sh = g.o_stride_h;
+    J.lse = g.lse;
+    J.lse_sh = g.lse_stride_h ? g.lse_stride_h : g.sq;
+    J.lse_sb = g.lse_stride_b ? g.lse_stride_b : (long long)x->hq * g.sq;
+    J.Sq = g.sq;
+    J.q_off = g.q_off;
+    unsigned mask = 0;
+    for (int s = 0; s < x->nseg; ++s)
+      if (seg_new[s] >= 0 && (g.seg_mask == 0 || ((g.seg_mask >> s) & 1u))) mask |= 1u << seg_new[s];
+    J.seg_mask = mask;
+    J.x_begin = x_total;
+    J.n_pairs = (g.sq + 2 * kBM - 1) / (2 * kBM);
+    J.q_flag = g.q_ready_flag;
+    J.q_flag_value = g.q_ready_value;
+    J.done_flag = g.done_flag;
+    J.done_value = g.done_value;
+    J.done_counter = g.done_counter;
+    J.n_ctas = J.n_pairs * x->hq * x->batch;
+    x_total += J.n_pairs;
+    ++njobs;
+  }
+  if (njobs == 0) return MB_SUCCESS;
+  a.njobs = njobs;
   a.B = x->batch;
-  a.Sq = x->sq;
   a.Hq = x->hq;
   a.group = x->hq / x->hkv;
-  a.q_off = x->q_off;
   a.causal = x->causal ? 1 : 0;
   a.scale = x->softmax_scale;
   a.scale_log2 = x->softmax_scale * 1.4426950408889634f;
+  a.peer_wait_cycles = peer_wait_cycles();
+  bool has_flags = false;
+  for (int s = 0; s < nseg; ++s) has_flags |= a.seg_flag[s] != nullptr;
+  for (int j = 0; j < njobs; ++j) has_flags |= a.job[j].q_flag != nullptr;
+  a.wait_cycles = kWaitCycleLimit + (has_flags ? a.peer_wait_cycles : 0);
   a.status = x->status ? x->status : default_status_word();
   if (a.status == nullptr) return MB_E_CUDA;
 
-  dim3 grid((x->sq + 2 * kBM - 1) / (2 * kBM), x->hq, x->batch);
+  dim3 grid(x_total, x->hq, x->batch);
   attn_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(maps, a);
   return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
 }
 
-}  // namespace mb
-
-#ifdef MB_TRACE
-extern "C" __attribute__((visibility("default"))) int mb_debug_fetch_fwd_trace(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, mb::g_fwd_trace, sizeof(mb::g_fwd_trace)) == cudaSuccess ? 0 : -3;
+// One query shard: the single-job form of the launch above.
+int launch_attn_fwd(const mb_attn_fwd_args* x, cudaStream_t stream) {
+  if (x == nullptr) return MB_E_INVALID;
+  if (x->nseg < 0 || x->nseg > MB_MAX_SEGMENTS) return MB_E_INVALID;
+  if (x->sq < 0) return MB_E_INVALID;
+  if (x->sq == 0) {
+    if (x->head_dim != kD) return MB_E_UNSUPPORTED;
+    if (x->batch <= 0 || x->hq <= 0 || x->hkv <= 0 || x->hq % x->hkv != 0) return MB_E_INVALID;
+    return MB_SUCCESS;
+  }
+  static thread_local mb_attn_fwd_multi_args m;
+  memset(&m, 0, sizeof(m));
+  m.batch = x->batch; m.hq = x->hq; m.hkv = x->hkv; m.head_dim = x->head_dim;
+  m.causal = x->causal; m.softmax_scale = x->softmax_scale;
+  m.njobs = 1; m.nseg = x->nseg;
+  mb_fwd_job& j = m.job[0];
+  j.q = x->q; j.q_stride_b = x->q_stride_b; j.q_stride_s = x->q_stride_s; j.q_stride_h = x->q_stride_h;
+  j.o = x->o; j.o_stride_b = x->o_stride_b; j.o_stride_s = x->o_stride_s; j.o_stride_h = x->o_stride_h;
+  j.lse = x->lse; j.lse_stride_b = x->lse_stride_b; j.lse_stride_h = x->lse_stride_h;
+  j.sq = x->sq; j.q_off = x->q_off;
+  for (int s = 0; s < x->nseg; ++s) m.seg[s] = x->seg[s];
+  m.status = x->status;
+  return launch_attn_fwd_multi(&m, stream);
 }
-#endif
+
+}  // namespace mb

@@ -18,43 +18,45 @@ constexpr int kHalfBytes = kTileBytes / 2;
 constexpr int kFwdStages = MB_FWD_STAGES;  // 32 KiB K or V tiles in flight (3, 4 and 5 measured alike)
 constexpr int kFwdThreads = 384;  // 8 softmax warps + one auxiliary warpgroup (2 MMA issuers, loader, 1 idle)
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: tolerate p up to 2^8
-// Optional timeline capture for kernel tuning (compiled in only with -DMB_TRACE): CTA (0,0,0)
-// records clock64() at fixed points of the first kTraceIters K/V iterations.
-#ifdef MB_TRACE
-constexpr int kTraceIters = 24;
-static __device__ long long g_fwd_trace[4][kTraceIters][12];
-#define MB_TRACE_AT(role, it, ev)                                                              \
-  do {                                                                                         \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < kTraceIters)           \
-      g_fwd_trace[role][it][ev] = clock64();                                                   \
-  } while (0)
-#else
-#define MB_TRACE_AT(role, it, ev) \
-  do {                            \
-  } while (0)
-#endif
+constexpr int kMaxJobs = MB_MAX_JOBS;
 
 struct FwdMaps {
-  CUtensorMap q;
+  CUtensorMap q[kMaxJobs];
   CUtensorMap k[MB_MAX_SEGMENTS];
   CUtensorMap v[MB_MAX_SEGMENTS];
 };
 
-struct FwdArgs {
+// One query shard of the launch and where its results go.
+struct FwdJob {
   __nv_bfloat16* o;
   long long o_sb, o_ss, o_sh;  // element strides
   float* lse;                  // [B, Hq, Sq], row-contiguous
   long long lse_sb, lse_sh;    // element strides of lse
-  int B, Sq, Hq, group;
+  int Sq, q_off;
+  unsigned seg_mask;           // segments this job attends to
+  int x_begin, n_pairs;        // its range of blockIdx.x
+  const int* q_flag;           // arrival flag of the query shard (nullptr: in place)
+  int q_flag_value;
+  int done_value;              // stored to *done_flag by the job's last CTA
+  int* done_flag;
+  int* done_counter;
+  int n_ctas;
+};
+
+struct FwdArgs {
+  FwdJob job[kMaxJobs];
+  int njobs;
+  int B, Hq, group;
   int nseg;
   int seg_sk[MB_MAX_SEGMENTS];
   int seg_koff[MB_MAX_SEGMENTS];
   const int* seg_flag[MB_MAX_SEGMENTS];  // arrival flag of a staged shard (nullptr: already in place)
   int seg_flag_value[MB_MAX_SEGMENTS];
-  int q_off;
   int causal;
   float scale;       // softmax scale
   float scale_log2;  // softmax scale * log2(e)
+  long long peer_wait_cycles;  // budget of a wait for data another GPU delivers
+  long long wait_cycles;       // budget of a wait inside the CTA (plus the above when the launch has flags)
   int* status;
 };
 
@@ -69,7 +71,9 @@ struct FwdSmem {
   uint64_t drain;
   uint32_t tmem_base;
   int abort_word;
+  int jid;
   int n_tiles[2][MB_MAX_SEGMENTS];  // K/V tiles of each segment that query tile i takes part in
+  FwdJob job;                       // this CTA's job (a copy: read with fixed offsets, no registers held)
 };
 
 constexpr int kFwdSmemBytes = 2 * kTileBytes + kFwdStages * kTileBytes + 1024 /*alignment slack*/ + 1024 /*FwdSmem*/;

@@ -47,6 +47,25 @@ int mb_attn_fwd(const mb_attn_fwd_args* args, void* cuda_stream) {
   return mb::launch_attn_fwd(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int mb_attn_fwd_multi(const mb_attn_fwd_multi_args* args, void* cuda_stream) {
+  return mb::launch_attn_fwd_multi(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int mb_set_peer_wait_ms(uint32_t milliseconds) {
+  mb::set_peer_wait_ms(milliseconds);
+  return MB_SUCCESS;
+}
+
+int mb_status_peek_async(int32_t* pinned_host_dst, void* cuda_stream) {
+  if (pinned_host_dst == nullptr) return MB_E_INVALID;
+  int* word = mb::default_status_word();
+  if (word == nullptr) return MB_E_CUDA;
+  return cudaMemcpyAsync(pinned_host_dst, word, sizeof(int), cudaMemcpyDeviceToHost,
+                         static_cast<cudaStream_t>(cuda_stream)) == cudaSuccess
+             ? MB_SUCCESS
+             : MB_E_CUDA;
+}
+
 int mb_attn_bwd_preprocess(const mb_bwd_preprocess_args* args, void* cuda_stream) {
   return mb::launch_bwd_preprocess(args, static_cast<cudaStream_t>(cuda_stream));
 }

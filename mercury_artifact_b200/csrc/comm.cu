@@ -39,6 +39,41 @@ __global__ void flag_wait_kernel(const int* flag, int value, unsigned long long 
   }
 }
 
+// Up to 32 flags per launch: lane i handles flag i.
+struct FlagBatch {
+  int* flag[32];
+  int value[32];
+  int n;
+};
+
+__global__ void flags_signal_kernel(const __grid_constant__ FlagBatch b) {
+  __threadfence_system();
+  const int i = threadIdx.x;
+  if (i < b.n) asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(b.flag[i]), "r"(b.value[i]) : "memory");
+}
+
+__global__ void flags_wait_kernel(const __grid_constant__ FlagBatch b, unsigned long long timeout_ns, int* status) {
+  const int i = threadIdx.x;
+  if (i >= b.n) return;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  unsigned spins = 0;
+  for (;;) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(b.flag[i]) : "memory");
+    if (seen >= b.value[i]) return;
+    if (((++spins) & 255u) == 0u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (now - t0 > timeout_ns) {
+        if (status != nullptr) atomicCAS(status, 0, MB_ERR_TIMEOUT_FLAG);
+        return;
+      }
+    }
+    __nanosleep(200);
+  }
+}
+
 // The flag kernels must be able to start while an attention kernel fills every SM.  An SM
 // only co-hosts kernels that agree on its shared-memory carve-out, and the attention
 // kernels run with the largest one, so the flag kernels ask for the same.
@@ -49,6 +84,10 @@ static void prefer_max_smem_carveout_once() {
   cudaFuncSetAttribute(flag_signal_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                        cudaSharedmemCarveoutMaxShared);
   cudaFuncSetAttribute(flag_wait_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(flags_signal_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(flags_wait_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                        cudaSharedmemCarveoutMaxShared);
   done[dev] = true;
 }
@@ -118,6 +157,38 @@ int mb_flag_wait(const int32_t* flag, int32_t value, uint64_t timeout_ns, int32_
   int* st = status ? status : mb::default_status_word();
   mb::prefer_max_smem_carveout_once();
   mb::flag_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(flag, value, timeout_ns, st);
+  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+}
+
+static int fill_batch(mb::FlagBatch* b, const int32_t* const* flags, const int32_t* values, int32_t n) {
+  if (flags == nullptr || values == nullptr || n < 0 || n > 32) return MB_E_INVALID;
+  memset(b, 0, sizeof(*b));
+  for (int i = 0; i < n; ++i) {
+    if (flags[i] == nullptr) return MB_E_INVALID;
+    b->flag[i] = const_cast<int*>(flags[i]);
+    b->value[i] = values[i];
+  }
+  b->n = n;
+  return MB_SUCCESS;
+}
+
+int mb_flags_signal(int32_t* const* flags, const int32_t* values, int32_t n, void* cuda_stream) {
+  mb::FlagBatch b;
+  int rc = fill_batch(&b, flags, values, n);
+  if (rc != MB_SUCCESS || n == 0) return rc;
+  mb::prefer_max_smem_carveout_once();
+  mb::flags_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(b);
+  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+}
+
+int mb_flags_wait(const int32_t* const* flags, const int32_t* values, int32_t n, uint64_t timeout_ns, int32_t* status,
+                  void* cuda_stream) {
+  mb::FlagBatch b;
+  int rc = fill_batch(&b, flags, values, n);
+  if (rc != MB_SUCCESS || n == 0) return rc;
+  int* st = status ? status : mb::default_status_word();
+  mb::prefer_max_smem_carveout_once();
+  mb::flags_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(b, timeout_ns, st);
   return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
 }
 

@@ -98,13 +98,16 @@ constexpr uint32_t kParkNs = 200000;  // 0.2 ms per parked attempt; the cycle bu
 
 // Bounded wait on one phase of an mbarrier.  Returns false when the CTA has
 // aborted (this wait or another one ran out of budget).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int code) {
+// `limit_cycles`: waits inside a CTA get about a second, unless the launch also waits for data from other
+// GPUs -- then a role can be held up for as long as the loader is, and gets that budget on top.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int code,
+                                          long long limit_cycles = kWaitCycleLimit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
     if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
     if (*abort_word != 0) return false;
-    if (clock64() - t0 > kWaitCycleLimit) {
+    if (clock64() - t0 > limit_cycles) {
       *abort_word = code;
       return false;
     }
@@ -113,22 +116,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 
 // Whole-warp form: every lane waits and the outcome is made uniform, so that the
 // warp-collective tensor-memory instructions that follow stay converged.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_word, int code) {
-  const bool ok = mbar_wait(bar, parity, abort_word, code);
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_word, int code,
+                                               long long limit_cycles = kWaitCycleLimit) {
+  const bool ok = mbar_wait(bar, parity, abort_word, code, limit_cycles);
   return __all_sync(0xffffffffu, ok);
 }
 
-// Bounded wait until a device-memory flag word reaches `value` (acquire, GPU scope).
-__device__ __forceinline__ bool flag_wait_ge(const int* flag, int value, volatile int* abort_word, int code) {
+// Bounded wait until a device-memory flag word reaches `value`.  Acquire at system scope: the word may be
+// raised by a kernel or a copy stream of this GPU or by a store from another GPU.  `limit_cycles` is the
+// budget for data that other ranks deliver (set by the host from mb_set_peer_wait_ms).
+__device__ __forceinline__ bool flag_wait_ge(const int* flag, int value, volatile int* abort_word, int code,
+                                             long long limit_cycles = kWaitCycleLimit) {
   const long long t0 = clock64();
   uint32_t spins = 0;
   for (;;) {
     int seen;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
     if (seen >= value) return true;
     if (((++spins) & 15u) == 0u) {
       if (*abort_word != 0) return false;
-      if (clock64() - t0 > kWaitCycleLimit) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_word = code;
         return false;
       }

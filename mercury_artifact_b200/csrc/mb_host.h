@@ -17,6 +17,11 @@ int encode_tiled_bf16(CUtensorMap* map, void* base, int rank, const cuuint64_t* 
 int* default_status_word();
 
 int launch_attn_fwd(const mb_attn_fwd_args* args, cudaStream_t stream);
+int launch_attn_fwd_multi(const mb_attn_fwd_multi_args* args, cudaStream_t stream);
+
+// Budget of in-kernel waits for data that other GPUs deliver (mb_set_peer_wait_ms), in SM cycles.
+void set_peer_wait_ms(unsigned ms);
+long long peer_wait_cycles();
 int launch_merge(const mb_merge_args* args, cudaStream_t stream);
 int launch_tree_merge(const float* const* srcs, int n, float* out, long long rows, int width, cudaStream_t stream);
 int launch_flash_reduce(const float* lhs, const float* rhs, float* out, long long rows, int width, cudaStream_t stream);

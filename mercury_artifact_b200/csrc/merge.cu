@@ -85,8 +85,11 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeArgs a) {
 // the reference's flash_reduce (utils/flash_attn_dsl.py:293-305), used by the ring-over-Q
 // schedule whose reduce buffer rotates with the queries.  One warp per row; rows of D+1 floats
 // are not 16-byte aligned, so lanes read consecutive floats (coalesced 128-byte lines).
-__global__ void __launch_bounds__(256) flash_reduce_kernel(const float* __restrict__ lhs, const float* __restrict__ rhs,
-                                                           float* __restrict__ out, long long rows, int width) {
+// `out` may be the same buffer as `lhs` (the C ABI says so), hence no __restrict__ on those two: every
+// element is read and written by the same lane, and the row's lse word is read by all lanes before the
+// __syncwarp() that precedes lane 0's store of the merged value.
+__global__ void __launch_bounds__(256) flash_reduce_kernel(const float* lhs, const float* __restrict__ rhs,
+                                                           float* out, long long rows, int width) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -96,6 +99,7 @@ __global__ void __launch_bounds__(256) flash_reduce_kernel(const float* __restri
     const float* r = rhs + row * width;
     float* o = out + row * width;
     const float ll = l[d], rl = r[d];
+    __syncwarp();
     float w, new_l;
     if (ll == -INFINITY) {
       w = 1.f;

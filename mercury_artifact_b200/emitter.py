@@ -195,9 +195,11 @@ def fuse_generated(code: str) -> str:
     world = 1
     for n in d["mesh"]:
         world *= n
-    # the program's ring_divide carries over when its pieces fit the eight segments of one launch
+    # the program's ring_divide carries over when its pieces fit the 32 segments of one launch
     rd = d.get("ring_divide", 1)
-    divide = f", ring_divide={rd}, balance_causal=False" if rd > 1 and 1 + (world - 1) * rd <= 8 else ""
+    divide = f", ring_divide={rd}" if rd > 1 and 1 + (world - 1) * rd <= 32 else ""
+    if d["backward"]:
+        divide += ", backward=True"
     lines = [
         "import torch",
         "from mercury_artifact_b200.ring import RingAttention as _RingAttention",

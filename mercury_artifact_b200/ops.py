@@ -37,10 +37,13 @@ def get_default_args(func):
     return _defaults_of(func if inspect.isfunction(func) else func._init_fn)
 
 
-def _reject_unsupported(dropout_p, window_size_left, window_size_right, softcap, alibi_slopes):
+def _reject_unsupported(dropout_p, window_size_left, window_size_right, softcap, alibi_slopes, causal=False):
     if dropout_p:
         raise NotImplementedError("dropout_p must be 0 (the ring schedules never set it)")
-    if window_size_left not in (-1, None) or window_size_right not in (-1, 0, None):
+    # window_size_right == 0 is how flash-attn spells "causal" internally; without causal=True it would be
+    # a window, which these kernels do not implement
+    right_ok = (-1, 0, None) if causal else (-1, None)
+    if window_size_left not in (-1, None) or window_size_right not in right_ok:
         raise NotImplementedError("sliding-window attention is not implemented")
     if softcap:
         raise NotImplementedError("softcap must be 0")
@@ -69,7 +72,7 @@ def _flash_attn_forward(
     causal=True aligns the mask to the bottom-right corner like the flash-attn op.
     Unlike flash-attn, a row without any visible key returns lse = -inf (not +inf).
     """
-    _reject_unsupported(dropout_p, window_size_left, window_size_right, softcap, alibi_slopes)
+    _reject_unsupported(dropout_p, window_size_left, window_size_right, softcap, alibi_slopes, causal)
     if return_softmax:
         raise NotImplementedError("return_softmax is only meaningful with dropout")
     if softmax_scale is None:
@@ -105,7 +108,7 @@ def _flash_attn_backward(
     a packed [2,...] buffer) and returns softmax_d = rowsum(dout * out) as [B, Hq, pad64(Sq)].
     `out` and `softmax_lse` are the final forward results of the query rows, which need not come
     from this K/V block alone.  Always deterministic (no atomics)."""
-    _reject_unsupported(dropout_p, window_size_left, window_size_right, softcap, alibi_slopes)
+    _reject_unsupported(dropout_p, window_size_left, window_size_right, softcap, alibi_slopes, causal)
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** -0.5
     if dq is None:

@@ -3,8 +3,8 @@
 `RingAttention.forward` computes what the generated per-rank loop computes
 (mercury/backend/pytorch/codegen.py:443-494 + utils/flash_attn_dsl.py:160-179 of
 the reference) with ONE attention launch: the K/V shards of all ranks are the
-segments of a single mb_attn_fwd call in the rank's arrival order, so the
-online-softmax state stays on chip and no out/LSE merge kernel runs.
+segments of a single launch in the rank's arrival order, so the online-softmax
+state stays on chip and no out/LSE merge kernel runs.
 `RingAttention.backward` replaces the generated backward loop
 (codegen.py:99-190, utils/attn_bwd_dsl.py:70-134) with two launches: dQ of the
 local queries over all K/V shards, and dK/dV of the local keys over all query
@@ -14,117 +14,37 @@ fp32 dK/dV accumulator and its write-back hop have no counterpart here.
 Transport.  On an NVSwitch box every peer is one hop away, so a shard is pulled
 straight from the rank that owns it instead of being relayed around the ring;
 the order in which a rank consumes shards is still the reference's (single ring:
-(r - t) mod P; nested rings: mesh.kv_origin_schedule).  The copy engines move
-each remote shard over NVLink into a local staging buffer on a high-priority
-side stream and a per-segment flag is raised behind it; the kernel's loader
-waits (bounded) on that flag before its first TMA load of the segment, so
-compute on the shards already here overlaps the transfers of the later ones
-inside one launch.
+(r - t) mod P; nested rings: mesh.kv_origin_schedule).  Every rank keeps ONE
+symmetric slot [kv | q | dout | row statistics] that all peers map.  The copy
+engines move each remote shard (or each of its `ring_divide` pieces) over NVLink
+into a local staging buffer on high-priority side streams and raise a per-piece
+arrival flag behind it; the kernel's loader waits (bounded) on that flag before
+its first TMA load of the piece, so compute on what is already here overlaps the
+transfers of what is not, inside one launch.  Completion travels the other way
+without any host or stream involvement: the last CTA of a job stores the owner's
+result flag from the kernel.
+
+Zero-copy operation: `symmetric_buffers()` hands out q / kv / dout / o / lse
+tensors that live inside the symmetric memory.  A caller that produces its
+inputs there and reads its results from there pays no staging copy at all;
+ordinary tensors work too and cost one device-to-device copy per tensor.
 
 World size 1 is the unsharded program: one segment, no transport.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from . import mesh
-from .attention import (RowStats, _pad64, attn_bwd_dkv, attn_bwd_dq, attn_fwd_segments, bwd_preprocess)
+from . import _lib, mesh
+from .attention import (RowStats, _pad64, attn_bwd_dkv, attn_bwd_dq, attn_fwd_multi, attn_fwd_segments,
+                        bwd_preprocess)
 from .comm import PeerContext, SymmetricBuffer, _align, default_context
 
 _FLAG_REGION = 4096
-
-
-class _ShardExchange:
-    """Publish one byte-slot per rank and epoch; pull peers' slots into local staging.
-
-    Symmetric memory per rank: two slots (epoch parity) + flag words
-        ready[origin] at +0     raised on every peer once `origin` has published its slot
-        done[reader]  at +1024  raised on the owner once `reader` no longer needs the slot
-    Local memory: world-1 staging slots and one arrival flag per staging slot.
-    All flag values are epoch numbers, which only grow.
-    """
-
-    def __init__(self, ctx: PeerContext, slot_bytes: int):
-        self.ctx = ctx
-        self.world, self.rank = ctx.world, ctx.rank
-        self.slot_bytes = _align(slot_bytes, 1024)
-        self.sym = SymmetricBuffer(ctx, 2 * self.slot_bytes + _FLAG_REGION)
-        self._flag_off = 2 * self.slot_bytes
-        self.staging = torch.empty((max(self.world - 1, 1), self.slot_bytes), dtype=torch.uint8, device=ctx.device)
-        self.seg_flags = torch.zeros(64, dtype=torch.int32, device=ctx.device)
-        self.epoch = 0
-        self._next_stage = 0
-        self._stage_of = {}
-        torch.cuda.synchronize(ctx.device)
-
-    def _ready_ptr(self, on_rank: int, origin: int) -> int:
-        return self.sym.ptr(on_rank, self._flag_off + 4 * origin)
-
-    def _done_ptr(self, on_rank: int, reader: int) -> int:
-        return self.sym.ptr(on_rank, self._flag_off + 1024 + 4 * reader)
-
-    def local_slot(self) -> torch.Tensor:
-        off = (self.epoch % 2) * self.slot_bytes
-        return self.sym.local.bytes()[off:off + self.slot_bytes]
-
-    def begin(self, main: torch.cuda.Stream, peers: Optional[Sequence[int]] = None) -> torch.Tensor:
-        """Start a new epoch; returns this rank's byte slot to fill on the transfer stream.
-        peers restricts the exchange to a sub-group of ranks (default: every rank)."""
-        ctx, comm = self.ctx, self.ctx.comm_stream
-        self.epoch += 1
-        self._next_stage = 0
-        self._stage_of = {}
-        e = self.epoch
-        comm.wait_stream(main)
-        if e > 2:  # the slot was last used at epoch e-2: every peer has released it by now or soon
-            for p in (peers if peers is not None else range(self.world)):
-                if p != self.rank:
-                    ctx.wait_flag(self._done_ptr(self.rank, p), e - 2, comm)
-        return self.local_slot()
-
-    def publish(self, peers: Optional[Sequence[int]] = None) -> torch.cuda.Event:
-        """Announce the filled slot to every peer; the event fires once the local copy is in place."""
-        ctx, comm = self.ctx, self.ctx.comm_stream
-        ev = torch.cuda.Event()
-        ev.record(comm)
-        for p in (peers if peers is not None else range(self.world)):
-            if p != self.rank:
-                ctx.signal(self._ready_ptr(p, self.rank), self.epoch, comm)
-        return ev
-
-    def pull(self, origin: int, ranges: Optional[Sequence[Tuple[int, int]]] = None, final: bool = True,
-             raise_flag: bool = True, piece: int = 0) -> Tuple[torch.Tensor, int]:
-        """Copy `origin`'s slot of this epoch (or the given (offset, nbytes) ranges of it) into that
-        origin's staging slot (copy engines over NVLink).  Returns (staging bytes, address of the
-        arrival flag that reaches `epoch` behind the copy).  final=False keeps the owner's slot
-        reserved for a later pull of the same epoch; raise_flag=False leaves the arrival flag alone
-        (the caller orders its consumers with a stream event instead).  piece selects one of the
-        staging slot's eight arrival flags, for a slot that is pulled in several pieces."""
-        ctx, comm = self.ctx, self.ctx.comm_stream
-        e = self.epoch
-        if origin not in self._stage_of:
-            self._stage_of[origin] = self._next_stage
-            self._next_stage += 1
-            ctx.wait_flag(self._ready_ptr(self.rank, origin), e, comm)
-        idx = self._stage_of[origin]
-        dst = self.staging[idx]
-        base = (e % 2) * self.slot_bytes
-        for off, nbytes in (ranges if ranges is not None else [(0, self.slot_bytes)]):
-            ctx.copy(dst.data_ptr() + off, self.sym.ptr(origin, base + off), nbytes, comm)
-        if not 0 <= piece < 8:
-            raise ValueError("a staging slot has eight arrival flags")
-        flag_ptr = self.seg_flags.data_ptr() + 4 * (8 * idx + piece)
-        if raise_flag:
-            ctx.signal(flag_ptr, e, comm)
-        if final:
-            ctx.signal(self._done_ptr(origin, self.rank), e, comm)
-        return dst, flag_ptr
-
-    def release(self, origin: int) -> None:
-        """Tell `origin` that this rank will not read its slot of this epoch."""
-        self.ctx.signal(self._done_ptr(origin, self.rank), self.epoch, self.ctx.comm_stream)
+_MAX_PIECES = 32          # arrival flags per staging slot
+_READY, _DONE, _RES = 0, 256, 512   # byte offsets of the flag groups inside the flag region
 
 
 def _carve(buf: torch.Tensor, offset: int, shape, dtype) -> Tuple[torch.Tensor, int]:
@@ -135,17 +55,134 @@ def _carve(buf: torch.Tensor, offset: int, shape, dtype) -> Tuple[torch.Tensor, 
     return buf[offset:offset + nbytes].view(dtype).view(*shape), offset + _align(nbytes, 256)
 
 
+class _Exchange:
+    """One symmetric slot per rank plus an optional result inbox, local staging, and the flags.
+
+    Symmetric memory of a rank: [slot | inbox | flag region].  Flag words (int32, values are epoch
+    numbers, which only grow):
+        ready[origin]  on every rank   `origin` has published its slot for this epoch
+        done[reader]   on the owner    `reader` has finished pulling the owner's slot of this epoch
+        res[i]         on the owner    result part i of this epoch is complete in the owner's inbox
+    Local memory: world - 1 staging slots, and int32 words for piece arrival flags
+    [stage * 32 + piece], query arrival flags and the kernels' completion counters.
+    """
+
+    def __init__(self, ctx: PeerContext, slot_bytes: int, inbox_bytes: int, staging: bool = True):
+        self.ctx = ctx
+        self.world, self.rank = ctx.world, ctx.rank
+        self.slot_bytes = _align(slot_bytes, 1024)
+        self.inbox_bytes = _align(inbox_bytes, 1024) if inbox_bytes else 0
+        self.sym = SymmetricBuffer(ctx, self.slot_bytes + self.inbox_bytes + _FLAG_REGION)
+        self._flag_off = self.slot_bytes + self.inbox_bytes
+        self.staging = torch.empty((max(self.world - 1, 1) if staging else 0, self.slot_bytes), dtype=torch.uint8,
+                                   device=ctx.device)
+        self.words = torch.zeros(max(self.world - 1, 1) * _MAX_PIECES + 16, dtype=torch.int32, device=ctx.device)
+        self.epoch = 0
+        self._waited = set()
+        torch.cuda.synchronize(ctx.device)
+
+    # -- addresses ---------------------------------------------------------------------------
+    def ready_ptr(self, on_rank: int, origin: int) -> int:
+        return self.sym.ptr(on_rank, self._flag_off + _READY + 4 * origin)
+
+    def done_ptr(self, on_rank: int, reader: int) -> int:
+        return self.sym.ptr(on_rank, self._flag_off + _DONE + 4 * reader)
+
+    def res_ptr(self, on_rank: int, part: int) -> int:
+        return self.sym.ptr(on_rank, self._flag_off + _RES + 4 * part)
+
+    def inbox_ptr(self, on_rank: int, offset: int = 0) -> int:
+        return self.sym.ptr(on_rank, self.slot_bytes + offset)
+
+    def slot(self) -> torch.Tensor:
+        return self.sym.local.bytes()[:self.slot_bytes]
+
+    def inbox(self) -> torch.Tensor:
+        return self.sym.local.bytes()[self.slot_bytes:self.slot_bytes + self.inbox_bytes]
+
+    def stage_index(self, origin: int) -> int:
+        return origin if origin < self.rank else origin - 1
+
+    def stage(self, origin: int) -> torch.Tensor:
+        return self.staging[self.stage_index(origin)]
+
+    def piece_flag_ptr(self, origin: int, piece: int = 0) -> int:
+        if not 0 <= piece < _MAX_PIECES:
+            raise ValueError(f"a staging slot has {_MAX_PIECES} arrival flags")
+        return self.words.data_ptr() + 4 * (self.stage_index(origin) * _MAX_PIECES + piece)
+
+    def aux_ptr(self, i: int) -> int:
+        """Sixteen further local words: query arrival flags (0..7) and completion counters (8..15)."""
+        return self.words.data_ptr() + 4 * (max(self.world - 1, 1) * _MAX_PIECES + i)
+
+    def stream_of(self, origin: int) -> torch.cuda.Stream:
+        """Every pull from one origin runs on one stream, so its last pull is behind all the others."""
+        s = self.ctx.comm_streams
+        return s[origin % len(s)]
+
+    # -- protocol ----------------------------------------------------------------------------
+    def begin(self, main: torch.cuda.Stream) -> int:
+        """Start a new epoch: transfers are ordered behind everything queued on `main` so far (the
+        previous epoch's kernels read the staging slots that are about to be overwritten)."""
+        self.epoch += 1
+        self._waited = set()
+        for s in self.ctx.comm_streams:
+            s.wait_stream(main)
+        return self.epoch
+
+    def wait_slot_free(self, peers: Sequence[int]) -> None:
+        """Before overwriting my slot: every peer has finished pulling the previous epoch."""
+        if self.epoch > 1:
+            flags = [(self.done_ptr(self.rank, p), self.epoch - 1) for p in peers if p != self.rank]
+            self.ctx.wait_many(flags, self.ctx.comm_stream)
+
+    def publish(self, peers: Sequence[int]) -> torch.cuda.Event:
+        """Announce my slot to every peer (one launch); the event fires once the slot is in place."""
+        comm = self.ctx.comm_stream
+        ev = torch.cuda.Event()
+        ev.record(comm)
+        self.ctx.signal_many([(self.ready_ptr(p, self.rank), self.epoch) for p in peers if p != self.rank], comm)
+        return ev
+
+    def pull(self, origin: int, ranges: Sequence[Tuple[int, int]], raise_after: Sequence[Tuple[int, int]] = (),
+             last: bool = False) -> torch.Tensor:
+        """Copy (offset, nbytes) ranges of `origin`'s slot into its staging slot over NVLink (copy
+        engines), then raise the given (flag address, value) pairs with one launch.  last=True also
+        tells the owner that this rank is done with its slot."""
+        ctx, st = self.ctx, self.stream_of(origin)
+        if origin not in self._waited:
+            self._waited.add(origin)
+            ctx.wait_flag(self.ready_ptr(self.rank, origin), self.epoch, st)
+        dst = self.stage(origin)
+        for off, nbytes in ranges:
+            ctx.copy(dst.data_ptr() + off, self.sym.ptr(origin, off), nbytes, st)
+        flags = list(raise_after)
+        if last:
+            flags.append((self.done_ptr(origin, self.rank), self.epoch))
+        if flags:
+            ctx.signal_many(flags, st)
+        return dst
+
+    def release(self, origins: Sequence[int]) -> None:
+        """Tell these owners that this rank will not read their slots of this epoch (one launch)."""
+        flags = [(self.done_ptr(o, self.rank), self.epoch) for o in origins if o != self.rank]
+        if flags:
+            self.ctx.signal_many(flags, self.ctx.comm_stream)
+
+
 class RingAttention:
     """Attention of one rank of a sequence-sharded job.
 
     mesh_shape (P,) is the single ring, (n_inner, n_outer) the double ring (inner ring over
     mesh dimension 0, rank = inner + n_inner * outer).  Shard k of the sequence lives on rank k.
     With causal=True a key is visible iff its global position is <= the query's.
+    backward=True reserves room for dout and the row statistics in the symmetric slot; it is needed
+    to call backward() on more than one rank.
     """
 
     def __init__(self, mesh_shape: Sequence[int], batch: int, seq_local: int, hq: int, hkv: int,
                  head_dim: int = 128, causal: bool = False, ctx: Optional[PeerContext] = None,
-                 balance_causal: bool = True, ring_divide: int = 1):
+                 balance_causal: bool = True, ring_divide: int = 1, backward: bool = False):
         self.mesh_shape = tuple(int(n) for n in mesh_shape)
         self.world = 1
         for n in self.mesh_shape:
@@ -159,33 +196,50 @@ class RingAttention:
         self.order = mesh.kv_origin_schedule(self.rank, self.mesh_shape)
         self.q_shape = (batch, seq_local, hq, head_dim)
         self.kv_shape = (2, batch, seq_local, hkv, head_dim)
+        self.lse_shape = (batch, hq, seq_local)
         self.stat_pad = _pad64(seq_local)
         self.stat_shape = (2, batch, hq, self.stat_pad)
+        self.with_backward = bool(backward)
         self.launches_per_forward = 1
         self.launches_per_backward = 3
-        self._fwd_x: Optional[_ShardExchange] = None
-        self._bwd_x: Optional[_ShardExchange] = None
-        self._bal_x: Optional[_ShardExchange] = None
-        self._bal_inbox: Optional[SymmetricBuffer] = None
-        # Causal attention over contiguous shards gives rank r (r + 1/2) blocks of work.  With
+        self._x: Optional[_Exchange] = None
+        self._monitor = getattr(self.ctx, "monitor", None) or _lib.StatusMonitor()
+        # Causal attention over contiguous shards gives rank r (r + 1/2) blocks of forward work.  With
         # balancing, the forward re-assigns query half-shards so that every rank computes the same
-        # amount (see _forward_balanced); inputs and outputs keep the contiguous layout.
+        # amount (see _jobs_balanced); inputs and outputs keep the contiguous layout.  The backward
+        # needs no such re-assignment: rank r does (r + 1/2) blocks of dQ work and (P - r - 1/2) blocks
+        # of dK/dV work, P blocks on every rank.
         self.balanced = bool(balance_causal) and self.causal and self.world > 1 and seq_local % 2 == 0
-        if self.balanced:
-            self.launches_per_forward = 2
         # ring_divide (the rounds parameter of the reference's shift primitive, ir/primitives.py:33-45,
         # 101-102): every K/V shard travels as `ring_divide` sequence pieces, each with its own arrival
         # flag and its own segment of the launch, so work on a shard starts when its first piece is in.
-        # One launch takes at most eight segments: 1 local + (world - 1) * ring_divide.
+        # One launch takes at most MB_MAX_SEGMENTS segments: 1 local + (world - 1) * ring_divide.
         self.ring_divide = int(ring_divide)
         if self.ring_divide < 1 or seq_local % self.ring_divide != 0:
             raise ValueError("ring_divide must divide the local sequence length")
-        if self.ring_divide > 1:
-            if self.balanced:
-                raise ValueError("ring_divide > 1 is implemented for the plain (unbalanced) forward: "
-                                 "pass balance_causal=False")
-            if 1 + (self.world - 1) * self.ring_divide > 8:
-                raise ValueError("1 + (world - 1) * ring_divide segments exceed the eight of one launch")
+        if 1 + (self.world - 1) * self.ring_divide > _lib.MB_MAX_SEGMENTS or self.ring_divide > _MAX_PIECES:
+            raise ValueError(f"1 + (world - 1) * ring_divide segments exceed the {_lib.MB_MAX_SEGMENTS} of one launch")
+        # byte layout of the slot and of the inbox
+        self._kv_b = 2 * batch * seq_local * hkv * head_dim * 2
+        self._q_b = batch * seq_local * hq * head_dim * 2
+        self._lse_b = batch * hq * seq_local * 4
+        self._st_b = 2 * batch * hq * self.stat_pad * 4
+        self._off_kv = 0
+        self._off_q = _align(self._kv_b, 256)
+        self._off_do = self._off_q + _align(self._q_b, 256)
+        self._off_st = self._off_do + _align(self._q_b, 256)
+        # the slot holds what peers pull: K/V always; the queries when peers compute some of this rank's rows
+        # (balanced forward) or its keys' gradients (backward); dout and the statistics for the backward
+        if self.with_backward:
+            self._slot_bytes = self._off_st + _align(self._st_b, 256)
+        else:
+            self._slot_bytes = self._off_do if self.balanced else self._off_q
+        self._inbox_o, self._inbox_lse = 0, _align(self._q_b, 256)
+        self._inbox_bytes = (self._inbox_lse + _align(self._lse_b, 256)) if self.balanced else 0
+        if self.with_backward and self.ring_divide > 1 and (seq_local // self.ring_divide) % 64 != 0:
+            raise ValueError("with backward=True the pieces of ring_divide must be multiples of 64 rows "
+                             "(the row statistics travel in 64-row blocks)")
+        self.last_launches = 0   # kernels this object launched in its latest forward() / backward()
 
     # ------------------------------------------------------------------ helpers
     def _sees_keys_of(self, origin: int) -> bool:
@@ -196,173 +250,185 @@ class RingAttention:
         """Whether `origin`'s queries can see any key of this rank's shard."""
         return (not self.causal) or origin >= self.rank
 
-    def _kv_bytes(self) -> int:
-        return 2 * self.batch * self.seq_local * self.hkv * self.head_dim * 2
+    def _exchange(self) -> _Exchange:
+        if self._x is None:
+            self._x = _Exchange(self.ctx, self._slot_bytes, self._inbox_bytes)
+            slot, inbox = self._x.slot(), self._x.inbox()
+            self._s_kv, _ = _carve(slot, self._off_kv, self.kv_shape, torch.bfloat16)
+            if self._slot_bytes > self._off_q:
+                self._s_q, _ = _carve(slot, self._off_q, self.q_shape, torch.bfloat16)
+            else:   # nobody pulls this rank's queries: an ordinary tensor serves symmetric_buffers()
+                self._s_q = torch.empty(self.q_shape, dtype=torch.bfloat16, device=self.ctx.device)
+            if self.with_backward:
+                self._s_do, _ = _carve(slot, self._off_do, self.q_shape, torch.bfloat16)
+                self._s_st, _ = _carve(slot, self._off_st, self.stat_shape, torch.float32)
+            if self.balanced:
+                self._s_o, _ = _carve(inbox, self._inbox_o, self.q_shape, torch.bfloat16)
+                self._s_lse, _ = _carve(inbox, self._inbox_lse, self.lse_shape, torch.float32)
+            else:   # results are written by this rank's own kernel: ordinary tensors
+                self._s_o, self._s_lse = self._plain_outputs(self.ctx.device)
+        return self._x
 
-    def _bwd_slot_bytes(self) -> int:
-        """Backward exchange slot: kv | q | dout | row statistics, each 256-byte aligned."""
-        q_b = self.batch * self.seq_local * self.hq * self.head_dim * 2
-        st_b = 2 * self.batch * self.hq * self.stat_pad * 4
-        return _align(self._kv_bytes(), 256) + 2 * _align(q_b, 256) + _align(st_b, 256)
+    def _stage_views(self, origin: int):
+        buf = self._x.stage(origin)
+        kv, _ = _carve(buf, self._off_kv, self.kv_shape, torch.bfloat16)
+        q, _ = _carve(buf, self._off_q, self.q_shape, torch.bfloat16)
+        if not self.with_backward:
+            return kv, q, None, None
+        do, _ = _carve(buf, self._off_do, self.q_shape, torch.bfloat16)
+        st, _ = _carve(buf, self._off_st, self.stat_shape, torch.float32)
+        return kv, q, do, st
+
+    def symmetric_buffers(self) -> Dict[str, torch.Tensor]:
+        """Tensors inside this rank's symmetric memory: q, kv (and dout with backward=True) to produce
+        the inputs in, o and lse to read the results from.  Passing exactly these to forward() /
+        backward() skips every staging copy.  Peers read q / kv / dout straight from here, so before
+        OVERWRITING them after a call, call inputs_writable(); o and lse are rewritten by the next
+        forward() (by kernels on other ranks), so consume them on the current stream before calling it.
+        World size 1 has no symmetric memory: ordinary tensors are returned."""
+        if self.world == 1:
+            dev = torch.device("cuda", torch.cuda.current_device())
+            out = {"q": torch.empty(self.q_shape, dtype=torch.bfloat16, device=dev),
+                   "kv": torch.empty(self.kv_shape, dtype=torch.bfloat16, device=dev),
+                   "o": torch.empty(self.q_shape, dtype=torch.bfloat16, device=dev),
+                   "lse": torch.empty(self.lse_shape, dtype=torch.float32, device=dev)}
+            if self.with_backward:
+                out["dout"] = torch.empty(self.q_shape, dtype=torch.bfloat16, device=dev)
+            return out
+        self._exchange()
+        # o / lse: the symmetric inbox when results are computed on other ranks (balanced causal forward),
+        # ordinary tensors of this object otherwise
+        out = {"q": self._s_q, "kv": self._s_kv, "o": self._s_o, "lse": self._s_lse}
+        if self.with_backward:
+            out["dout"] = self._s_do
+        return out
+
+    def inputs_writable(self) -> None:
+        """Make the current stream wait until every peer has finished reading this rank's symmetric
+        q / kv / dout of the last call (one small kernel).  Call before overwriting those tensors."""
+        if self.world > 1 and self._x is not None and self._x.epoch > 0:
+            x = self._x
+            flags = [(x.done_ptr(self.rank, p), x.epoch) for p in range(self.world) if p != self.rank]
+            self.ctx.wait_many(flags, torch.cuda.current_stream())
+
+    @staticmethod
+    def _same(a: torch.Tensor, b: torch.Tensor) -> bool:
+        return a.data_ptr() == b.data_ptr() and a.shape == b.shape and a.stride() == b.stride()
+
+    def _kv_piece_ranges(self, j: int) -> List[Tuple[int, int]]:
+        """Byte ranges of rows [j c, (j+1) c) of K and of V inside a slot, for every batch entry."""
+        c = self.seq_local // self.ring_divide
+        row_b = self.hkv * self.head_dim * 2
+        return [(self._off_kv + ((w * self.batch + b) * self.seq_local + j * c) * row_b, c * row_b)
+                for w in range(2) for b in range(self.batch)]
+
+    def _q_rows_ranges(self, base_off: int, r0: int, r1: int) -> List[Tuple[int, int]]:
+        """Byte ranges of query rows [r0, r1) of a [B, L, Hq, D] bf16 tensor at base_off in a slot."""
+        row_b = self.hq * self.head_dim * 2
+        return [(base_off + (b * self.seq_local + r0) * row_b, (r1 - r0) * row_b) for b in range(self.batch)]
 
     # ------------------------------------------------------------------ forward
     def forward(self, q: torch.Tensor, kv: torch.Tensor, o: Optional[torch.Tensor] = None,
                 lse: Optional[torch.Tensor] = None, softmax_scale: Optional[float] = None
                 ) -> Tuple[torch.Tensor, torch.Tensor]:
         """q [B,S/P,Hq,D], kv [2,B,S/P,Hkv,D] bf16 on this rank's device -> (o, lse [B,Hq,S/P])."""
-        if tuple(kv.shape) != self.kv_shape:
-            raise ValueError(f"kv must have shape {self.kv_shape}, got {tuple(kv.shape)}")
+        if tuple(kv.shape) != self.kv_shape or tuple(q.shape) != self.q_shape:
+            raise ValueError(f"q / kv must have shapes {self.q_shape} / {self.kv_shape}, "
+                             f"got {tuple(q.shape)} / {tuple(kv.shape)}")
         if softmax_scale is None:
             softmax_scale = self.head_dim ** -0.5
+        self._monitor.poll()
         L = self.seq_local
         if self.world == 1:
-            return attn_fwd_segments(q, [(kv[0], kv[1], 0)], softmax_scale, causal=self.causal, q_off=0, out=o, lse=lse)
+            res = attn_fwd_segments(q, [(kv[0], kv[1], 0)], softmax_scale, causal=self.causal, q_off=0, out=o, lse=lse)
+            self._monitor.post(torch.cuda.current_stream())
+            return res
 
-        if self.balanced:
-            return self._forward_balanced(q, kv, o, lse, softmax_scale)
-
-        if self._fwd_x is None:
-            self._fwd_x = _ShardExchange(self.ctx, self._kv_bytes())
-        x = self._fwd_x
-        main = torch.cuda.current_stream()
-        comm = self.ctx.comm_stream
-        me = self.rank
-
-        slot_bytes = x.begin(main)
-        slot, _ = _carve(slot_bytes, 0, self.kv_shape, torch.bfloat16)
-        with torch.cuda.stream(comm):
-            slot.copy_(kv, non_blocking=True)
-        local_ready = x.publish()
-
-        segs: List[tuple] = [(slot[0], slot[1], me * L)]
-        for t in range(1, self.world):
-            origin = self.order[t]
-            if self._sees_keys_of(origin) and self.ring_divide == 1:
-                buf, flag_ptr = x.pull(origin)
-                rkv, _ = _carve(buf, 0, self.kv_shape, torch.bfloat16)
-                segs.append((rkv[0], rkv[1], origin * L, flag_ptr, x.epoch))
-            elif self._sees_keys_of(origin):
-                d, c = self.ring_divide, L // self.ring_divide
-                row_b = self.hkv * self.head_dim * 2
-                for j in range(d):
-                    # rows [j c, (j+1) c) of K and of V, for every batch entry: 2 B contiguous ranges
-                    ranges = [(((w * self.batch + b) * L + j * c) * row_b, c * row_b)
-                              for w in range(2) for b in range(self.batch)]
-                    buf, flag_ptr = x.pull(origin, ranges, final=(j == d - 1), piece=j)
-                    rkv, _ = _carve(buf, 0, self.kv_shape, torch.bfloat16)
-                    segs.append((rkv[0][:, j * c:(j + 1) * c], rkv[1][:, j * c:(j + 1) * c], origin * L + j * c,
-                                 flag_ptr, x.epoch))
-            else:
-                x.release(origin)
-
-        main.wait_event(local_ready)
-        return attn_fwd_segments(q, segs, softmax_scale, causal=self.causal, q_off=me * L, out=o, lse=lse)
-
-    # ------------------------------------------------------------------ balanced causal forward
-    def _forward_balanced(self, q, kv, o, lse, softmax_scale):
-        """Causal forward with equal work per rank.
-
-        The sequence is cut into 2P half-shards; rank r computes the queries of half-shards r and
-        2P-1-r (work (r + 1/2) + (2P-1-r + 1/2) = 2P units on every rank).  A rank pulls the query
-        half-shards it computes and the K/V shards they can see, and its kernels write o and lse
-        straight into the owning rank's result inbox through the peer mapping (stores over NVLink);
-        a flag per half tells the owner when its rows are complete.  Layout seen by the caller is
-        unchanged: shard k of q, kv, o, lse lives on rank k.
-        """
-        ctx, P, me, L = self.ctx, self.world, self.rank, self.seq_local
-        Lh = L // 2
-        B, Hq, D = self.batch, self.hq, self.head_dim
-        kv_b = self._kv_bytes()
-        q_b = B * L * Hq * D * 2
-        lse_b = B * Hq * L * 4
-        off_q = _align(kv_b, 256)
-        if self._bal_x is None:
-            self._bal_x = _ShardExchange(ctx, off_q + _align(q_b, 256))
-            self._res_bytes = _align(q_b, 256) + _align(lse_b, 256)
-            self._bal_inbox = SymmetricBuffer(ctx, 2 * self._res_bytes + _FLAG_REGION)
-        x, inbox = self._bal_x, self._bal_inbox
+        ctx, P, me = self.ctx, self.world, self.rank
+        x = self._exchange()
+        launches0 = ctx.launch_count
         main = torch.cuda.current_stream()
         comm = ctx.comm_stream
+        e = x.begin(main)
+        peers = range(P)
+        zero_in = self._same(kv, self._s_kv) and (not self.balanced or self._same(q, self._s_q))
+        if not zero_in:
+            x.wait_slot_free(peers)
+            with torch.cuda.stream(comm):
+                self._s_kv.copy_(kv, non_blocking=True)
+                if self.balanced:
+                    self._s_q.copy_(q, non_blocking=True)
+        x.publish(peers)
 
-        slot = x.begin(main)
-        s_kv, _ = _carve(slot, 0, self.kv_shape, torch.bfloat16)
-        s_q, _ = _carve(slot, off_q, self.q_shape, torch.bfloat16)
-        with torch.cuda.stream(comm):
-            s_kv.copy_(kv, non_blocking=True)
-            s_q.copy_(q, non_blocking=True)
-        local_ready = x.publish()
-        e = x.epoch
-        par = e % 2
-
-        chunks = [2 * P - 1 - me, me]          # heavier half-shard first; its first segment is local
-        max_shard = chunks[0] // 2               # K/V shards 0..max_shard are needed
-        owners = {c: c // 2 for c in chunks}
-
-        def q_ranges(c):
-            half = c % 2
-            row_b = Hq * D * 2
-            return [(off_q + (b * L + half * Lh) * row_b, Lh * row_b) for b in range(B)]
-
-        # 1. the query half-shards first (small), ordered before the kernels by a stream event
-        for c in chunks:
-            if owners[c] != me:
-                x.pull(owners[c], q_ranges(c), final=False, raise_flag=False)
-        q_ready = torch.cuda.Event()
-        q_ready.record(comm)
-        # 2. the K/V shards, staggered so that ranks start on different sources
-        kv_of = {me: (s_kv, None)}
-        for t in range(1, P):
-            origin = (me - t) % P
-            if origin <= max_shard:
-                buf, flag_ptr = x.pull(origin, [(0, kv_b)])
-                rkv, _ = _carve(buf, 0, self.kv_shape, torch.bfloat16)
-                kv_of[origin] = (rkv, flag_ptr)
-            elif origin in x._stage_of:
-                x.release(origin)   # only its queries were needed
-            else:
-                x.release(origin)
-        pull_order = [me] + [(me - t) % P for t in range(1, P)]
-
-        res_o_off = par * self._res_bytes
-        res_l_off = res_o_off + _align(q_b, 256)
-
-        def res_flag(rank, half):
-            return inbox.ptr(rank, 2 * self._res_bytes + 8 * par + 4 * half)
-
-        main.wait_event(local_ready)
-        main.wait_event(q_ready)
-        for c in chunks:
-            owner, half = owners[c], c % 2
-            rows = slice(half * Lh, (half + 1) * Lh)
-            if owner == me:
-                qc = q[:, rows]
-            else:
-                stage = x.staging[x._stage_of[owner]]
-                qc = _carve(stage, off_q, self.q_shape, torch.bfloat16)[0][:, rows]
-            segs = []
-            for origin in pull_order:
-                if origin <= c // 2 and origin in kv_of:
-                    rkv, flag_ptr = kv_of[origin]
-                    segs.append((rkv[0], rkv[1], origin * L) if flag_ptr is None
-                                else (rkv[0], rkv[1], origin * L, flag_ptr, e))
-            # results go straight into the owner's inbox (its memory is mapped here): raw addresses
-            attn_fwd_segments(
-                qc, segs, softmax_scale, causal=True, q_off=c * Lh,
-                out_raw=(inbox.ptr(owner, res_o_off + half * Lh * Hq * D * 2), L * Hq * D, Hq * D, D),
-                lse_raw=(inbox.ptr(owner, res_l_off + half * Lh * 4), Hq * L, L))
-            ctx.signal(res_flag(owner, half), e, main)
-
-        # 3. my own rows: wait for whoever computed them, then hand them to the caller
-        my_o, _ = _carve(inbox.local.bytes(), res_o_off, self.q_shape, torch.bfloat16)
-        my_lse, _ = _carve(inbox.local.bytes(), res_l_off, (B, Hq, L), torch.float32)
-        ctx.wait_flag(res_flag(me, 0), e, main)
-        ctx.wait_flag(res_flag(me, 1), e, main)
+        B, Hq, D = self.batch, self.hq, self.head_dim
         if o is None:
-            o = torch.empty_like(q)
+            o = self._s_o if self.balanced else torch.empty_like(q)
         if lse is None:
-            lse = torch.empty((B, Hq, L), dtype=torch.float32, device=q.device)
-        o.copy_(my_o, non_blocking=True)
-        lse.copy_(my_lse, non_blocking=True)
+            lse = self._s_lse if self.balanced else torch.empty(self.lse_shape, dtype=torch.float32, device=q.device)
+        if tuple(lse.shape) != self.lse_shape or lse.dtype != torch.float32 or lse.stride(2) != 1:
+            raise ValueError("lse must be an fp32 [batch, hq, seq] tensor with contiguous rows")
+        if tuple(o.shape) != self.q_shape or o.dtype != torch.bfloat16 or o.stride(3) != 1:
+            raise ValueError("o must be a bf16 tensor shaped like q with a contiguous head_dim")
+
+        # ---- which query rows this rank computes, and where their results go
+        jobs: List[dict] = []
+        q_pulls: List[Tuple[int, List[Tuple[int, int]], int]] = []   # (owner, ranges, index of the arrival flag)
+        if self.balanced:
+            # The sequence is cut into 2P half-shards; rank r computes the queries of half-shards 2P-1-r and
+            # r: (2P-1-r + 1/2) + (r + 1/2) = 2P units of work on every rank.  Results go straight into the
+            # owning rank's inbox through the peer mapping (stores over NVLink from the kernel's epilogue),
+            # and the job's last CTA raises the owner's flag for that half.
+            Lh = L // 2
+            for idx, c in enumerate((2 * P - 1 - me, me)):      # heavier half-shard first
+                owner, half = c // 2, c % 2
+                rows = slice(half * Lh, (half + 1) * Lh)
+                job = {"q_off": c * Lh,
+                       "out_raw": (x.inbox_ptr(owner, self._inbox_o + half * Lh * Hq * D * 2), L * Hq * D, Hq * D, D),
+                       "lse_raw": (x.inbox_ptr(owner, self._inbox_lse + half * Lh * 4), Hq * L, L),
+                       "done": (x.res_ptr(owner, half), e, x.aux_ptr(8 + idx))}
+                if owner == me:
+                    job["q"] = q[:, rows]
+                else:
+                    job["q"] = self._stage_views(owner)[1][:, rows]
+                    job["q_flag"] = (x.aux_ptr(idx), e)
+                    q_pulls.append((owner, self._q_rows_ranges(self._off_q, half * Lh, (half + 1) * Lh), idx))
+                jobs.append(job)
+            max_shard = (2 * P - 1 - me) // 2       # K/V shards 0..max_shard are visible to some query here
+            needed = [og for og in ((me - t) % P for t in range(1, P)) if og <= max_shard]
+        else:
+            jobs.append({"q": q, "q_off": me * L,
+                         "out_raw": (o.data_ptr(), o.stride(0), o.stride(1), o.stride(2)),
+                         "lse_raw": (lse.data_ptr(), lse.stride(0), lse.stride(1))})
+            needed = [og for og in self.order[1:] if self._sees_keys_of(og)]
+
+        # ---- transfers: owners nobody here reads are released at once; query half-shards go first on
+        # their origin's stream, then the K/V shards in consumption order, piece by piece
+        q_owners = {owner for owner, _, _ in q_pulls}
+        x.release([og for og in range(P) if og != me and og not in needed and og not in q_owners])
+        for owner, ranges, idx in q_pulls:
+            x.pull(owner, ranges, raise_after=[(x.aux_ptr(idx), e)], last=owner not in needed)
+        d, c = self.ring_divide, L // self.ring_divide
+        segs: List[tuple] = [(kv[0], kv[1], me * L)]
+        for og in needed:
+            rkv = self._stage_views(og)[0]
+            for j in range(d):
+                flag = x.piece_flag_ptr(og, j)
+                ranges = self._kv_piece_ranges(j) if d > 1 else [(self._off_kv, self._kv_b)]
+                x.pull(og, ranges, raise_after=[(flag, e)], last=(j == d - 1))
+                rows = slice(j * c, (j + 1) * c)
+                segs.append((rkv[0][:, rows], rkv[1][:, rows], og * L + j * c, flag, e))
+
+        attn_fwd_multi(jobs, segs, softmax_scale, self.causal, B, Hq, self.hkv, D, q.device)
+
+        if self.balanced:
+            # my own rows: wait for whoever computed them (one launch for both halves)
+            ctx.wait_many([(x.res_ptr(me, 0), e), (x.res_ptr(me, 1), e)], main)
+            if not self._same(o, self._s_o):
+                o.copy_(self._s_o, non_blocking=True)
+            if not self._same(lse, self._s_lse):
+                lse.copy_(self._s_lse, non_blocking=True)
+        self._monitor.post(main)
+        self.last_launches = ctx.launch_count - launches0 + 1
         return o, lse
 
     # ------------------------------------------------------------------ backward
@@ -379,6 +445,7 @@ class RingAttention:
             dq = torch.empty_like(q)
         if dkv is None:
             dkv = torch.empty_like(kv)
+        self._monitor.poll()
         L = self.seq_local
         me = self.rank
         if self.world == 1:
@@ -386,60 +453,73 @@ class RingAttention:
             attn_bwd_dq(q, dout, stats, [(kv[0], kv[1], 0)], softmax_scale, causal=self.causal, q_off=0, dq=dq)
             attn_bwd_dkv(kv[0], kv[1], [(q, dout, stats, 0)], softmax_scale, causal=self.causal, k_off=0,
                          dk=dkv[0], dv=dkv[1])
+            self._monitor.post(torch.cuda.current_stream())
             return dq, dkv
+        if not self.with_backward:
+            raise ValueError("construct RingAttention with backward=True to call backward() on more than one rank")
 
-        kv_b = self._kv_bytes()
-        q_b = self.batch * L * self.hq * self.head_dim * 2
-        st_b = 2 * self.batch * self.hq * self.stat_pad * 4
-        off_kv, off_q = 0, _align(kv_b, 256)
-        off_do = off_q + _align(q_b, 256)
-        off_st = off_do + _align(q_b, 256)
-        if self._bwd_x is None:
-            assert off_st + _align(st_b, 256) == self._bwd_slot_bytes()
-            self._bwd_x = _ShardExchange(self.ctx, self._bwd_slot_bytes())
-        x = self._bwd_x
+        ctx, P = self.ctx, self.world
+        x = self._exchange()
+        launches0 = ctx.launch_count
         main = torch.cuda.current_stream()
-        comm = self.ctx.comm_stream
-
-        def views(buf):
-            v_kv, _ = _carve(buf, off_kv, self.kv_shape, torch.bfloat16)
-            v_q, _ = _carve(buf, off_q, self.q_shape, torch.bfloat16)
-            v_do, _ = _carve(buf, off_do, self.q_shape, torch.bfloat16)
-            v_st, _ = _carve(buf, off_st, self.stat_shape, torch.float32)
-            return v_kv, v_q, v_do, v_st
-
-        # statistics of my rows go straight into my slot (main stream), the tensors are copied beside them
-        slot_bytes = x.begin(main)
-        s_kv, s_q, s_do, s_st = views(slot_bytes)
+        comm = ctx.comm_stream
+        e = x.begin(main)
+        peers = range(P)
+        zero_in = self._same(kv, self._s_kv) and self._same(q, self._s_q) and self._same(dout, self._s_do)
+        # always: this call itself rewrites the row statistics inside the slot
+        x.wait_slot_free(peers)
         with torch.cuda.stream(comm):
-            stats = bwd_preprocess(dout, o, lse, workspace=s_st)
-            s_kv.copy_(kv, non_blocking=True)
-            s_q.copy_(q, non_blocking=True)
-            s_do.copy_(dout, non_blocking=True)
-        local_ready = x.publish()
+            # statistics of my rows go straight into my slot, the tensors are copied beside them
+            stats = bwd_preprocess(dout, o, lse, workspace=self._s_st)
+            if not zero_in:
+                if not self._same(kv, self._s_kv):
+                    self._s_kv.copy_(kv, non_blocking=True)
+                if not self._same(q, self._s_q):
+                    self._s_q.copy_(q, non_blocking=True)
+                if not self._same(dout, self._s_do):
+                    self._s_do.copy_(dout, non_blocking=True)
+        local_ready = x.publish(peers)
 
-        kv_segs = [{"str": s_kv[0], "str_g": s_kv[1], "off": me * L}]
-        q_segs = [{"str": s_q, "str_g": s_do, "stats": stats, "off": me * L}]
-        for t in range(1, self.world):
-            origin = self.order[t]
-            need_kv, need_q = self._sees_keys_of(origin), self._seen_by_queries_of(origin)
+        d, c = self.ring_divide, L // self.ring_divide
+        kv_segs = [{"str": kv[0], "str_g": kv[1], "off": me * L}]
+        q_segs = [{"str": q, "str_g": dout, "stats": stats, "off": me * L}]
+        x.release([og for og in range(P) if og != me and not (self._sees_keys_of(og) or self._seen_by_queries_of(og))])
+        for t in range(1, P):
+            og = self.order[t]
+            need_kv, need_q = self._sees_keys_of(og), self._seen_by_queries_of(og)
             if not (need_kv or need_q):
-                x.release(origin)
                 continue
-            ranges = ([(off_kv, kv_b)] if need_kv else []) + ([(off_q, off_st + st_b - off_q)] if need_q else [])
-            buf, flag_ptr = x.pull(origin, ranges)
-            r_kv, r_q, r_do, r_st = views(buf)
-            if need_kv:
-                kv_segs.append({"str": r_kv[0], "str_g": r_kv[1], "off": origin * L,
-                                "flag": flag_ptr, "flag_value": x.epoch})
-            if need_q:
-                q_segs.append({"str": r_q, "str_g": r_do, "stats": RowStats(r_st[0], r_st[1], L), "off": origin * L,
-                               "flag": flag_ptr, "flag_value": x.epoch})
+            r_kv, r_q, r_do, r_st = self._stage_views(og)
+            for j in range(d):
+                flag = x.piece_flag_ptr(og, j)
+                ranges: List[Tuple[int, int]] = []
+                if need_kv:
+                    ranges += self._kv_piece_ranges(j) if d > 1 else [(self._off_kv, self._kv_b)]
+                if need_q:
+                    if d > 1:
+                        ranges += self._q_rows_ranges(self._off_q, j * c, (j + 1) * c)
+                        ranges += self._q_rows_ranges(self._off_do, j * c, (j + 1) * c)
+                        if j == 0:      # the row statistics are small: all of them travel with the first piece
+                            ranges.append((self._off_st, self._st_b))
+                    else:
+                        ranges.append((self._off_q, self._off_st + self._st_b - self._off_q))
+                x.pull(og, ranges, raise_after=[(flag, e)], last=(j == d - 1))
+                rows = slice(j * c, (j + 1) * c)
+                if need_kv:
+                    kv_segs.append({"str": r_kv[0][:, rows], "str_g": r_kv[1][:, rows], "off": og * L + j * c,
+                                    "flag": flag, "flag_value": e})
+                if need_q:
+                    st = (RowStats(r_st[0][:, :, j * c:], r_st[1][:, :, j * c:], c, pad=self.stat_pad) if d > 1
+                          else RowStats(r_st[0], r_st[1], L))
+                    q_segs.append({"str": r_q[:, rows], "str_g": r_do[:, rows], "stats": st, "off": og * L + j * c,
+                                   "flag": flag, "flag_value": e})
 
-        main.wait_event(local_ready)
+        main.wait_event(local_ready)   # my own statistics were computed on the transfer stream
         attn_bwd_dq(q, dout, stats, kv_segs, softmax_scale, causal=self.causal, q_off=me * L, dq=dq, hkv=self.hkv)
         attn_bwd_dkv(kv[0], kv[1], q_segs, softmax_scale, causal=self.causal, k_off=me * L, dk=dkv[0], dv=dkv[1],
                      hq=self.hq)
+        self._monitor.post(main)
+        self.last_launches = ctx.launch_count - launches0 + 3
         return dq, dkv
 
     # ------------------------------------------------------------------ host-buffer entry
@@ -452,12 +532,26 @@ class RingAttention:
         are contiguous on the device and go in as one segment) and chunk i-2 is copied out, so the PCIe
         transfers in both directions overlap the kernels.  What stays exposed is the last chunk's
         kernel and copy-out, hence many small chunks rather than few large ones.
-        Otherwise: copy in, forward(), copy out.  Returns after the results are in host memory.
+        Several ranks: the host tensors are copied straight into this rank's symmetric q / kv (once the
+        peers have released them), the forward runs without staging copies, and o / lse are read back
+        from the symmetric result buffers.  Returns after the results are in host memory.
         """
         dev = torch.device("cuda", torch.cuda.current_device()) if self.ctx is None else self.ctx.device
         if softmax_scale is None:
             softmax_scale = self.head_dim ** -0.5
         L = self.seq_local
+        main = torch.cuda.current_stream()
+        if self.world > 1:
+            bufs = self.symmetric_buffers()
+            q, kv, o, lse = bufs["q"], bufs["kv"], bufs["o"], bufs["lse"]
+            self.inputs_writable()
+            q.copy_(q_host, non_blocking=True)
+            kv.copy_(kv_host, non_blocking=True)
+            self.forward(q, kv, o, lse, softmax_scale)
+            o_host.copy_(o, non_blocking=True)
+            lse_host.copy_(lse, non_blocking=True)
+            main.synchronize()
+            return
         if not hasattr(self, "_host_bufs"):
             self._host_bufs = (torch.empty(self.q_shape, dtype=torch.bfloat16, device=dev),
                                torch.empty(self.kv_shape, dtype=torch.bfloat16, device=dev),
@@ -465,9 +559,8 @@ class RingAttention:
                                torch.empty((self.batch, self.hq, L), dtype=torch.float32, device=dev),
                                torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
         q, kv, o, lse, s_in, s_out = self._host_bufs
-        main = torch.cuda.current_stream()
         n = max(1, min(chunks, 64))
-        pipelined = self.world == 1 and self.batch == 1 and L % n == 0 and (L // n) % 128 == 0
+        pipelined = self.batch == 1 and L % n == 0 and (L // n) % 128 == 0
         if not pipelined:
             q.copy_(q_host, non_blocking=True)
             kv.copy_(kv_host, non_blocking=True)
@@ -509,40 +602,30 @@ class RingAttention:
                     lse_host.copy_(lse, non_blocking=True)
         s_out.synchronize()
 
-    def memory_bytes(self, backward: bool = False) -> dict:
+    def _plain_outputs(self, dev):
+        if not hasattr(self, "_plain_out"):
+            self._plain_out = (torch.empty(self.q_shape, dtype=torch.bfloat16, device=dev),
+                               torch.empty(self.lse_shape, dtype=torch.float32, device=dev))
+        return self._plain_out
+
+    def memory_bytes(self, backward: Optional[bool] = None) -> dict:
         """Device memory this object allocates per rank for its transfers, by kind (the counterpart of
-        the reference's per-card buffer model, mercury/ir/calculate_memory.py:9-66, for symmetric slots
-        and staging instead of the rotating double buffer): `symmetric` is mapped by every peer (two
-        epoch slots per exchange), `staging` holds pulled shards (world - 1 slots per exchange),
-        `inbox` receives results computed elsewhere (balanced causal forward).  Flag regions included."""
+        the reference's per-card buffer model, mercury/ir/calculate_memory.py:9-66, for a symmetric slot
+        and staging instead of the rotating double buffer): `symmetric` is mapped by every peer -- the
+        slot [kv | q (| dout | row statistics with backward=True)] plus the flag region; `staging`
+        holds pulled shards (world - 1 slots); `inbox` is the symmetric o / lse that results computed
+        on other ranks are written into.  `backward` defaults to what the object was built with."""
         if self.world == 1:
             return {"symmetric": 0, "staging": 0, "inbox": 0}
-        q_b = self.batch * self.seq_local * self.hq * self.head_dim * 2
-        lse_b = self.batch * self.hq * self.seq_local * 4
-        kv_b = self._kv_bytes()
-
-        def exchange(slot_bytes):
-            slot = _align(slot_bytes, 1024)
-            return 2 * slot + _FLAG_REGION, max(self.world - 1, 1) * slot
-
-        sym = stage = inbox = 0
-        if self.balanced:
-            a, b = exchange(_align(kv_b, 256) + _align(q_b, 256))
-            sym, stage = sym + a, stage + b
-            inbox = 2 * (_align(q_b, 256) + _align(lse_b, 256)) + _FLAG_REGION
-        else:
-            a, b = exchange(kv_b)
-            sym, stage = sym + a, stage + b
-        if backward:
-            a, b = exchange(self._bwd_slot_bytes())
-            sym, stage = sym + a, stage + b
-        return {"symmetric": sym, "staging": stage, "inbox": inbox}
+        if backward is not None and bool(backward) != self.with_backward:
+            raise ValueError("the slot layout is fixed at construction: pass backward= to RingAttention")
+        slot = _align(self._slot_bytes, 1024)
+        inbox = _align(self._inbox_bytes, 1024)
+        return {"symmetric": slot + _FLAG_REGION, "staging": (self.world - 1) * slot, "inbox": inbox}
 
     def check(self) -> None:
         """Synchronise and raise if a device-side wait timed out."""
         if self.ctx is not None:
             self.ctx.check()
         else:
-            from . import _lib
-
             _lib.raise_on_status(torch.cuda.current_stream().cuda_stream)

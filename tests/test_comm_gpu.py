@@ -73,7 +73,7 @@ def test_sendrecv_single_rank_self_exchange():
 
 def test_kernel_wait_for_a_shard_that_never_arrives_gives_up():
     """The attention kernels wait inside the launch for the arrival flag of a staged shard.  If the
-    flag is never raised the waits run out of their (about one second) budget, every other wait of
+    flag is never raised the waits run out of their budget (mb_set_peer_wait_ms, shortened here), every other wait of
     the CTA returns at once, the kernel frees its tensor memory and exits, the host reads status 109,
     and the next launch works.  One tiny CTA per launch, so the whole test takes a few seconds."""
     import mercury_artifact_b200 as mb
@@ -84,6 +84,14 @@ def test_kernel_wait_for_a_shard_that_never_arrives_gives_up():
 
     st = torch.cuda.current_stream()
     assert _lib.status_fetch(st.cuda_stream) == 0
+    _lib.set_peer_wait_ms(500)   # the default (30 s) is sized for rank skew in real jobs
+    try:
+        _kernel_wait_body(mb, _lib, DeviceBuffer, block, seeded_qkv, st)
+    finally:
+        _lib.set_peer_wait_ms(_lib.PEER_WAIT_MS)
+
+
+def _kernel_wait_body(mb, _lib, DeviceBuffer, block, seeded_qkv, st):
     flag = DeviceBuffer(256, torch.device("cuda", 0))      # zero-initialised, nobody raises it
     q, k, v, do = seeded_qkv(11, 1, 256, 1, 1, 128, device="cuda")
     # forward: first segment in place, second "still in flight"
@@ -106,3 +114,94 @@ def test_kernel_wait_for_a_shard_that_never_arrives_gives_up():
     rdq, _, _ = block.block_attn_bwd(do.cpu(), q.cpu(), k.cpu(), v.cpu(), ro, rl, 128 ** -0.5, causal=False)
     assert (dq.float().cpu() - rdq).abs().max().item() <= 2e-2
     flag.free()
+
+
+def test_batched_flag_kernels_and_status_monitor():
+    """mb_flags_signal / mb_flags_wait handle up to 32 words per launch; a wait that runs out is noticed by
+    the StatusMonitor at a later poll(), without the caller synchronising after every call."""
+    from mercury_artifact_b200 import _lib
+    from mercury_artifact_b200.comm import DeviceBuffer, PeerContext
+
+    ctx = PeerContext()
+    buf = DeviceBuffer(1024, torch.device("cuda", 0))
+    st = torch.cuda.current_stream()
+    flags = [(buf.ptr + 4 * i, 10 + i) for i in range(40)]       # 40 words: two launches
+    n0 = ctx.launch_count
+    ctx.signal_many(flags, st)
+    ctx.wait_many(flags, st)
+    assert ctx.launch_count - n0 == 4
+    assert _lib.status_fetch(st.cuda_stream) == 0
+    assert buf.view(0, (40,), torch.int32).tolist() == [10 + i for i in range(40)]
+    # one of the words never reaches its value: the wait gives up, the monitor reports it afterwards
+    mon = _lib.StatusMonitor()
+    mon.poll()
+    ctx.wait_many([(buf.ptr, 10), (buf.ptr + 4, 999)], st, timeout_ns=20_000_000)
+    mon.post(st)
+    st.synchronize()
+    with pytest.raises(_lib.MercuryB200Error, match="earlier call timed out"):
+        mon.poll()
+    mon.poll()                       # reported once; the device word was cleared
+    assert _lib.status_fetch(st.cuda_stream) == 0
+    buf.free()
+
+
+def test_multi_job_forward_flags_and_completion():
+    """mb_attn_fwd_multi: two query shards in one launch write where their job says, equal the one-job
+    results bit for bit, wait for their queries' arrival flag, and each raises its completion flag once
+    all its CTAs have stored (the counter word is back at zero afterwards)."""
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200 import _lib
+    from mercury_artifact_b200.attention import attn_fwd_multi
+    from mercury_artifact_b200.comm import DeviceBuffer
+    from tests.helpers import seeded_qkv
+
+    dev = torch.device("cuda", 0)
+    st = torch.cuda.current_stream()
+    B, S, H, hkv, D = 2, 1024, 4, 2, 128
+    q, k, v, _ = seeded_qkv(21, B, S, H, hkv, D, device="cuda")
+    scale = D ** -0.5
+    words = DeviceBuffer(256, dev)         # [0] q arrival flag, [1..2] completion flags, [3..4] counters
+    segs = [(k[:, 512:], v[:, 512:], 512), (k[:, :512], v[:, :512], 0)]
+    # one-job references: rows 768.. (job A) and rows 0..255 (job B), causal on global positions
+    ra, la = mb.attn_fwd_segments(q[:, 768:], segs, scale, causal=True, q_off=768)
+    rb, lb = mb.attn_fwd_segments(q[:, :256], segs, scale, causal=True, q_off=0)
+    o = torch.zeros_like(q)
+    lse = torch.zeros(B, H, S, device=dev)
+
+    def job(rows, flag_idx, q_flag=None):
+        r0 = rows.start
+        j = {"q": q[:, rows], "q_off": r0,
+             "out_raw": (o[:, rows].data_ptr(), o.stride(0), o.stride(1), o.stride(2)),
+             "lse_raw": (lse[:, :, rows].data_ptr(), lse.stride(0), lse.stride(1)),
+             "done": (words.ptr + 4 * flag_idx, 5, words.ptr + 4 * (flag_idx + 2))}
+        if q_flag is not None:
+            j["q_flag"] = q_flag
+        return j
+
+    _lib.check(_lib.lib.mb_flag_signal(C.c_void_p(words.ptr), 3, C.c_void_p(st.cuda_stream)), "signal")
+    attn_fwd_multi([job(slice(768, 1024), 1, q_flag=(words.ptr, 3)), job(slice(0, 256), 2)], segs, scale, True,
+                   B, H, hkv, D, dev)
+    assert _lib.status_fetch(st.cuda_stream) == 0
+    assert torch.equal(o[:, 768:], ra) and torch.equal(lse[:, :, 768:], la)
+    assert torch.equal(o[:, :256], rb) and torch.equal(lse[:, :, :256], lb)
+    assert o[:, 256:768].abs().max().item() == 0          # rows of no job are untouched
+    assert words.view(0, (5,), torch.int32).tolist() == [3, 5, 5, 0, 0]
+    # queries that never arrive: status 109, the completion flag of that job still gets raised (every CTA
+    # counts, so that the counter returns to zero), the other job is complete and correct
+    _lib.set_peer_wait_ms(300)
+    try:
+        o.zero_()
+        j0 = job(slice(768, 1024), 1, q_flag=(words.ptr, 4))
+        j0["done"] = (words.ptr + 4, 6, words.ptr + 12)
+        j1 = job(slice(0, 256), 2)
+        j1["done"] = (words.ptr + 8, 6, words.ptr + 16)
+        attn_fwd_multi([j0, j1], segs, scale, True, B, H, hkv, D, dev)
+        assert _lib.status_fetch(st.cuda_stream) == 109
+        assert words.view(0, (5,), torch.int32).tolist() == [3, 6, 6, 0, 0]
+        assert torch.equal(o[:, :256], rb)
+    finally:
+        _lib.set_peer_wait_ms(_lib.PEER_WAIT_MS)
+    # and the next launch works
+    o2, l2 = mb.attn_fwd_segments(q[:, 768:], segs, scale, causal=True, q_off=768)
+    assert _lib.status_fetch(st.cuda_stream) == 0 and torch.equal(o2, ra)
+    words.free()

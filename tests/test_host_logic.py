@@ -39,7 +39,7 @@ def test_argument_validation_needs_no_gpu():
     assert _lib.lib.mb_attn_fwd(ctypes.byref(a), None) == -2  # only head_dim 128 is built
     a.head_dim, a.batch, a.hq, a.hkv, a.nseg = 128, 1, 3, 2, 1
     assert _lib.lib.mb_attn_fwd(ctypes.byref(a), None) == -1  # hq not a multiple of hkv
-    a.hq, a.nseg = 4, 9
+    a.hq, a.nseg = 4, 33
     assert _lib.lib.mb_attn_fwd(ctypes.byref(a), None) == -1  # too many segments
     assert _lib.lib.mb_merge_out_lse(None, None) == -1
     assert _lib.lib.mb_flag_signal(None, 1, None) == -1
@@ -166,7 +166,8 @@ def test_emitter_recognises_kv_rings_and_leaves_other_programs_alone():
     # shift(..., ring_divide=4): the outer sub-block loop is recognised and carried into the fused call
     assert emitter.recognise(golden_text("gpu_ring_p2_div4"))["ring_divide"] == 4
     fused = emitter.fuse_generated(golden_text("gpu_ring_p2_div4"))
-    assert "causal=bool(causal), ring_divide=4, balance_causal=False)" in fused and "for S_kv" not in fused
+    assert "causal=bool(causal), ring_divide=4)" in fused and "for S_kv" not in fused
+    assert "backward=True)" in emitter.fuse_generated(golden_text("gpu_bwd_p4"))
     compile(fused, "<fused>", "exec")
 
 
@@ -267,18 +268,24 @@ def test_ring_divide_validation_and_memory_model():
 
     op = RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx())
     kv_b, q_b, lse_b = 2 * 4096 * 32 * 128 * 2, 4096 * 32 * 128 * 2, 32 * 4096 * 4
-    m = op.memory_bytes()
-    assert m["symmetric"] == 2 * (kv_b + q_b) + 4096 and m["staging"] == 7 * (kv_b + q_b)
-    assert m["inbox"] == 2 * (q_b + lse_b) + 4096
+    st_b = 2 * 32 * 4096 * 4
+    # balanced causal forward: one symmetric slot [kv | q], seven staging slots, the o / lse inbox
+    assert op.memory_bytes() == {"symmetric": kv_b + q_b + 4096, "staging": 7 * (kv_b + q_b), "inbox": q_b + lse_b}
     plain = RingAttention((8,), 1, 4096, 32, 32, 128, causal=False, ctx=Ctx())
-    assert plain.memory_bytes() == {"symmetric": 2 * kv_b + 4096, "staging": 7 * kv_b, "inbox": 0}
-    assert plain.memory_bytes(backward=True)["staging"] > 7 * (kv_b + 2 * q_b)
+    assert plain.memory_bytes() == {"symmetric": kv_b + 4096, "staging": 7 * kv_b, "inbox": 0}
+    both = RingAttention((8,), 1, 4096, 32, 32, 128, causal=False, ctx=Ctx(), backward=True)
+    assert both.memory_bytes()["staging"] == 7 * (kv_b + 2 * q_b + st_b)
+    with pytest.raises(ValueError, match="fixed at construction"):
+        plain.memory_bytes(backward=True)
     with pytest.raises(ValueError, match="divide the local sequence"):
         RingAttention((8,), 1, 4096, 32, 32, 128, ctx=Ctx(), ring_divide=3)
     with pytest.raises(ValueError, match="segments exceed"):
-        RingAttention((8,), 1, 4096, 32, 32, 128, ctx=Ctx(), ring_divide=2)
-    with pytest.raises(ValueError, match="balance_causal=False"):
-        RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx(), ring_divide=2)
+        RingAttention((8,), 1, 4096, 32, 32, 128, ctx=Ctx(), ring_divide=8)
+    # eight ranks x four pieces = 29 segments fit one launch, also with the balanced causal forward
+    assert RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx(), ring_divide=4).balanced
+    with pytest.raises(ValueError, match="multiples of 64 rows"):
+        RingAttention((2,), 1, 960, 4, 4, 128, ctx=type("C2", (), dict(world=2, rank=0, device=None))(),
+                      ring_divide=2, backward=True)
     Ctx.world, Ctx.rank = 2, 1
     assert RingAttention((2,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx(), balance_causal=False,
                          ring_divide=7 if 4096 % 7 == 0 else 4).ring_divide == 4

@@ -32,32 +32,46 @@ def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=F
     q, k, v, do = seeded_qkv(1234, B, S, H, hkv, 128)
     qs, kvs = shard_inputs(q, k, v, world)
     op = RingAttention(mesh_shape, B, S // world, H, hkv, 128, causal=causal, balance_causal=balance,
-                       ring_divide=ring_divide)
+                       ring_divide=ring_divide, backward=with_bwd)
     lq, lkv = qs[rank].cuda(), kvs[rank].cuda()
     ldo = do.chunk(world, 1)[rank].contiguous().cuda()
     outs = []
-    for it in range(3):  # three epochs: exercises slot reuse and the done/ready flags
-        o, lse = op.forward(lq, lkv)
+    bufs = op.symmetric_buffers()
+    for it in range(4):  # four epochs: slot reuse and the done/ready flags; ordinary tensors, then zero-copy
+        if it >= 2:      # inputs produced inside the symmetric buffers, results read from them
+            op.inputs_writable()
+            bufs["q"].copy_(lq)
+            bufs["kv"].copy_(lkv)
+            if with_bwd:
+                bufs["dout"].copy_(ldo)
+            o, lse = op.forward(bufs["q"], bufs["kv"], bufs["o"], bufs["lse"])
+            if with_bwd:
+                dq, dkv = op.backward(bufs["dout"], bufs["q"], bufs["kv"], o, lse)
+        else:
+            o, lse = op.forward(lq, lkv)
+            if with_bwd:
+                dq, dkv = op.backward(ldo, lq, lkv, o, lse)
         if with_bwd:
-            dq, dkv = op.backward(ldo, lq, lkv, o, lse)
             outs.append((o.float().cpu(), lse.cpu(), dq.float().cpu(), dkv.float().cpu()))
         else:
             outs.append((o.float().cpu(), lse.cpu()))
     op.check()
     # the memory model against what was actually allocated
-    model = op.memory_bytes(backward=with_bwd)
-    xs = [x for x in (op._fwd_x, op._bal_x, op._bwd_x) if x is not None]
-    assert model["symmetric"] == sum(x.sym.local.bytes().numel() for x in xs)
-    assert model["staging"] == sum(x.staging.numel() for x in xs)
-    assert model["inbox"] == (op._bal_inbox.local.bytes().numel() if op._bal_inbox is not None else 0)
+    model = op.memory_bytes()
+    assert model["symmetric"] + model["inbox"] == op._x.sym.local.bytes().numel()
+    assert model["staging"] == op._x.staging.numel()
+    assert model["inbox"] == op._x.inbox().numel()
     ret[rank] = outs
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("causal,ring_divide", [(False, 2), (True, 4), (False, 7)])
-def test_ring_divide_pieces_two_gpus(causal, ring_divide):
-    """ring_divide > 1: the peer's shard arrives as sequence pieces, each a flagged segment of the launch."""
+@pytest.mark.parametrize("causal,ring_divide,balance,with_bwd", [(False, 2, False, False), (True, 4, False, False),
+                                                                 (False, 7, False, False), (True, 2, True, False),
+                                                                 (True, 7, True, True)])
+def test_ring_divide_pieces_two_gpus(causal, ring_divide, balance, with_bwd):
+    """ring_divide > 1: the peer's shard arrives as sequence pieces, each a flagged segment of the launch --
+    in the plain forward, in the balanced causal forward, and in both backward launches."""
     import torch.multiprocessing as mp
     from oracle import block
     from tests.helpers import seeded_qkv
@@ -66,16 +80,24 @@ def test_ring_divide_pieces_two_gpus(causal, ring_divide):
     if world < 2:
         pytest.skip("needs 2 GPUs")
     B, S, H, hkv = 2, 1792, 4, 2   # 896 rows per rank: 448-, 224- and 128-row pieces
-    q, k, v, _ = seeded_qkv(1234, B, S, H, hkv, 128)
-    fo, fl = block.full_attention(q, k, v, 128 ** -0.5, causal=causal)
+    q, k, v, do = seeded_qkv(1234, B, S, H, hkv, 128)
+    scale = 128 ** -0.5
+    fo, fl = block.full_attention(q, k, v, scale, causal=causal)
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, False, False, ring_divide),
+    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, with_bwd, balance, ring_divide),
              nprocs=world, join=True)
     L = S // world
+    if with_bwd:
+        gq, gk, gv = block.block_attn_bwd(do, q, k, v, fo, fl, scale, causal=causal, q_off=0, k_off=0)
     for r in range(world):
-        for o, lse in ret[r]:
-            assert (o - fo[:, r * L:(r + 1) * L].float()).abs().max().item() <= 2e-2
-            assert (lse - fl[:, :, r * L:(r + 1) * L]).abs().max().item() <= 1e-3
+        rows = slice(r * L, (r + 1) * L)
+        for res in ret[r]:
+            assert (res[0] - fo[:, rows].float()).abs().max().item() <= 2e-2
+            assert (res[1] - fl[:, :, rows]).abs().max().item() <= 1e-3
+            if with_bwd:
+                assert (res[2] - gq[:, rows]).abs().max().item() <= 2e-2
+                assert (res[3][0] - gk[:, rows]).abs().max().item() <= 2e-2
+                assert (res[3][1] - gv[:, rows]).abs().max().item() <= 2e-2
 
 
 @pytest.mark.parametrize("causal,balance", [(False, True), (True, False), (True, True)])
@@ -286,3 +308,70 @@ def test_generated_tree_program_two_gpus():
         for o, lse in ret[r]:
             assert (o - fo.float()).abs().max().item() <= 2e-2
             assert (lse - fl).abs().max().item() <= 1e-3
+
+
+def _size_worker(rank, world, port, name, dims, mesh_shape, ret):
+    """One rank of a benchmark-sized job: NCCL process group (the check gathers whole tensors on the GPUs),
+    inputs generated on the device inside the op's symmetric buffers, row-sampled fp32 check of this
+    rank's results (oracle/sampled.py)."""
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    from mercury_artifact_b200.comm import init_p2p
+    from mercury_artifact_b200.ring import RingAttention
+    from oracle import sampled
+
+    init_p2p(device=dev)
+    B, S, H, hkv, causal, backward = dims
+    L = S // world
+    scale = 128 ** -0.5
+    op = RingAttention(mesh_shape, B, L, H, hkv, 128, causal=causal, backward=backward)
+    bufs = op.symmetric_buffers()
+    g = torch.Generator(device=dev).manual_seed(900 + rank)
+    for key in ("q", "kv") + (("dout",) if backward else ()):
+        bufs[key].copy_((torch.randn(bufs[key].shape, generator=g, device=dev) * 0.5).to(torch.bfloat16))
+    res = {}
+    for _ in range(2):
+        o, lse = op.forward(bufs["q"], bufs["kv"], bufs["o"], bufs["lse"], scale)
+        res = sampled.check_forward_shard(bufs["q"], bufs["kv"], o, lse, rank, world, causal, scale, rows=32)
+        if backward:
+            dq, dkv = op.backward(bufs["dout"], bufs["q"], bufs["kv"], o, lse, None, None, scale)
+            res.update(sampled.check_backward_shard(bufs["q"], bufs["kv"], o, lse, bufs["dout"], dq, dkv, rank, world,
+                                                    causal, scale, rows=24))
+    op.check()
+    ret[rank] = {k: float(v) for k, v in res.items()}
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name,dims", [
+    ("131072-token causal forward", (1, 131072, 32, 32, True, False)),
+    ("GQA 32/8 heads, batch 2, 131072 tokens, causal", (2, 131072, 32, 8, True, False)),
+    ("double ring, 262144 tokens, non-causal", (1, 262144, 16, 16, False, False)),
+    ("65536-token causal forward + backward", (1, 65536, 32, 32, True, True)),
+])
+def test_benchmark_sizes_on_all_gpus(name, dims):
+    """The sequence-parallel workloads at their real sizes on as many GPUs as there are (8, 4 or 2; the
+    double ring needs 4 or 8 for its inner x outer mesh, else it runs as a single ring): every rank's
+    shard against fp32 attention over the whole sequence, as the reference's own distributed tests compare
+    each rank's chunk with the single-device result (tests/test_ring_attn_codegen.py:120-148,
+    tests/test_attn_bwd.py:267)."""
+    import torch.multiprocessing as mp
+
+    n = torch.cuda.device_count()
+    world = 8 if n >= 8 else 4 if n >= 4 else 2
+    mesh_shape = (world,)
+    if name.startswith("double ring") and world >= 4:
+        mesh_shape = (world // 2, 2)
+    ret = mp.Manager().dict()
+    mp.spawn(_size_worker, args=(world, _free_port(), name, dims, mesh_shape, ret), nprocs=world, join=True)
+    for r in range(world):
+        e = ret[r]
+        assert e["o_max_abs"] <= 2e-2 and e["lse_max_abs"] <= 1e-3, (r, e)
+        if dims[5]:
+            assert max(e["dq_max_abs"], e["dk_max_abs"], e["dv_max_abs"]) <= 2e-2, (r, e)

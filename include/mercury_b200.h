@@ -143,6 +143,10 @@ MB_API int mb_attn_bwd_preprocess(const mb_bwd_preprocess_args* args, void* cuda
 
 #define MB_BWD_MODE_DKV 1 /* owner = one K/V shard, stream = query shards: writes dK (out1) and dV (out2) */
 #define MB_BWD_MODE_DQ 0  /* owner = one query shard, stream = K/V shards: writes dQ (out1) */
+#define MB_BWD_MODE_FUSED 2 /* like DKV, and each streamed query shard's dQ contributions are ADDED (fp32,
+                             * red.global.add) into its segment's dq_accum: scores are computed once, 5 tile
+                             * products per block instead of 7.  dQ then depends on the order of fp32
+                             * additions (not bitwise reproducible); finish with mb_attn_bwd_dq_convert. */
 #define MB_OUT_BF16 0
 #define MB_OUT_F32 1
 #define MB_OUT_F32_ACCUM 2 /* out += result (each element is owned by one CTA: no atomics) */
@@ -160,6 +164,9 @@ typedef struct mb_bwd_segment {
   int32_t stat_pad;
   int32_t ready_value;
   const int32_t* ready_flag; /* optional arrival flag, as in mb_kv_segment */
+  /* MB_BWD_MODE_FUSED only: fp32 [batch, hq, stat_pad, head_dim], zero-filled by the caller (or holding a
+   * partial sum to add to): receives this query shard's UNSCALED dQ contributions. */
+  float* dq_accum;
 } mb_bwd_segment;
 
 typedef struct mb_attn_bwd_args {
@@ -191,6 +198,13 @@ typedef struct mb_attn_bwd_args {
  * and, with one segment per rank, the whole generated backward loop including its fp32
  * accumulation and the rotating dK/dV buffer (mercury/backend/pytorch/codegen.py:99-190). */
 MB_API int mb_attn_bwd(const mb_attn_bwd_args* args, void* cuda_stream);
+
+/* dq[b, s, h, :] = softmax_scale * dq_accum[b, h, s, :]: the last step of MB_BWD_MODE_FUSED.
+ * dq is bf16 (MB_OUT_BF16) or fp32 (MB_OUT_F32) with the given element strides; dq_accum has row pitch
+ * stat_pad per (batch, head). */
+MB_API int mb_attn_bwd_dq_convert(const float* dq_accum, void* dq, int64_t dq_stride_b, int64_t dq_stride_s,
+                                  int64_t dq_stride_h, int32_t batch, int32_t sq, int32_t hq, int32_t stat_pad,
+                                  int32_t out_mode, float softmax_scale, void* cuda_stream);
 
 typedef struct mb_attn_bwd_block_args {
   const void* dout; /* [batch, sq, hq, head_dim] bf16; dout and out use q's strides */

@@ -142,6 +142,7 @@ class MergeArgs(C.Structure):
 
 MB_BWD_MODE_DKV = 1
 MB_BWD_MODE_DQ = 0
+MB_BWD_MODE_FUSED = 2
 MB_OUT_BF16 = 0
 MB_OUT_F32 = 1
 MB_OUT_F32_ACCUM = 2
@@ -182,6 +183,7 @@ class BwdSegment(C.Structure):
         ("stat_pad", C.c_int32),
         ("ready_value", C.c_int32),
         ("ready_flag", C.c_void_p),
+        ("dq_accum", C.c_void_p),
     ]
 
 
@@ -271,6 +273,8 @@ _SIGNATURES = {
     "mb_attn_fwd_multi": [C.POINTER(AttnFwdMultiArgs), C.c_void_p],
     "mb_attn_bwd_preprocess": [C.POINTER(BwdPreprocessArgs), C.c_void_p],
     "mb_attn_bwd": [C.POINTER(AttnBwdArgs), C.c_void_p],
+    "mb_attn_bwd_dq_convert": [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                               C.c_int32, C.c_int32, C.c_float, C.c_void_p],
     "mb_attn_bwd_block_noalloc": [C.POINTER(AttnBwdBlockArgs), C.c_void_p],
     "mb_merge_out_lse": [C.POINTER(MergeArgs), C.c_void_p],
     "mb_tree_merge": [C.POINTER(C.c_void_p), C.c_int32, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p],

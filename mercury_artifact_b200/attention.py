@@ -213,6 +213,8 @@ _OUT_MODES = {torch.bfloat16: _lib.MB_OUT_BF16, torch.float32: _lib.MB_OUT_F32}
 
 
 def _bwd_launch(mode, own, own_g, own_off, segments, hq, hkv, scale, causal, out1, out2, accumulate, own_stats=None):
+    """One mb_attn_bwd launch.  Segment dicts: str, str_g, off, optional stats (RowStats), flag / flag_value,
+    and dq_accum (fp32 tensor, single-pass mode)."""
     _check_bshd(own, "owner")
     _check_bshd(own_g, "owner_g")
     if own.shape != own_g.shape or own.stride() != own_g.stride():
@@ -259,6 +261,11 @@ def _bwd_launch(mode, own, own_g, own_off, segments, hq, hkv, scale, causal, out
             seg.lse2, seg.delta, seg.stat_pad = st.lse2.data_ptr(), st.delta.data_ptr(), st.pad
         if sg.get("flag"):
             seg.ready_flag, seg.ready_value = sg["flag"], int(sg["flag_value"])
+        if sg.get("dq_accum") is not None:
+            acc = sg["dq_accum"]
+            if acc.dtype != torch.float32 or not acc.is_contiguous() or tuple(acc.shape) != (b, hq, seg.stat_pad, d):
+                raise ValueError(f"dq_accum must be contiguous fp32 {(b, hq, seg.stat_pad, d)}")
+            seg.dq_accum = acc.data_ptr()
     with torch.cuda.device(own.device):
         _lib.check(_lib.lib.mb_attn_bwd(C.byref(a), C.c_void_p(_stream_ptr())), "mb_attn_bwd")
 
@@ -297,3 +304,31 @@ def attn_bwd_dkv(k, v, q_segments, softmax_scale, causal=False, k_off=0, dk=None
     hq = hq if hq is not None else (segs[0]["str"].shape[2] if segs else k.shape[2])
     _bwd_launch(_lib.MB_BWD_MODE_DKV, k, v, k_off, segs, hq, k.shape[2], softmax_scale, causal, dk, dv, accumulate)
     return dk, dv
+
+
+def attn_bwd_fused(q, dout, stats: RowStats, k, v, softmax_scale, causal=False, q_off=0, k_off=0, dq=None, dk=None,
+                   dv=None, dq_accum: Optional[torch.Tensor] = None):
+    """dQ, dK, dV of one query shard against one K/V shard in a single sweep (MB_BWD_MODE_FUSED): scores
+    and probabilities are computed once; the dQ contributions of every K/V tile are added into an fp32
+    buffer (`dq_accum`, [batch, hq, pad64(sq), d], allocated and zeroed here unless given) and converted
+    at the end.  The order of those additions varies, so dq is not bitwise reproducible run to run
+    (dk and dv are); attn_bwd_dq + attn_bwd_dkv is the deterministic two-launch form."""
+    if dq is None:
+        dq = torch.empty_like(q)
+    if dk is None:
+        dk = torch.empty_like(k)
+    if dv is None:
+        dv = torch.empty_like(v)
+    b, sq, hq, d = q.shape
+    if dq_accum is None:
+        dq_accum = torch.zeros((b, hq, stats.pad, d), dtype=torch.float32, device=q.device)
+    seg = {"str": q, "str_g": dout, "stats": stats, "off": q_off, "dq_accum": dq_accum}
+    _bwd_launch(_lib.MB_BWD_MODE_FUSED, k, v, k_off, [seg], hq, k.shape[2], softmax_scale, causal, dk, dv, False)
+    if dq.dtype not in _OUT_MODES or dq.stride(3) != 1 or tuple(dq.shape) != tuple(q.shape):
+        raise ValueError("dq must be bf16 or fp32, shaped like q, with a contiguous head_dim")
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib.mb_attn_bwd_dq_convert(dq_accum.data_ptr(), dq.data_ptr(), dq.stride(0), dq.stride(1),
+                                                   dq.stride(2), b, sq, hq, stats.pad, _OUT_MODES[dq.dtype],
+                                                   float(softmax_scale), C.c_void_p(_stream_ptr())),
+                   "mb_attn_bwd_dq_convert")
+    return dq, dk, dv

@@ -74,6 +74,13 @@ int mb_attn_bwd(const mb_attn_bwd_args* args, void* cuda_stream) {
   return mb::launch_attn_bwd(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int mb_attn_bwd_dq_convert(const float* dq_accum, void* dq, int64_t dq_stride_b, int64_t dq_stride_s, int64_t dq_stride_h,
+                           int32_t batch, int32_t sq, int32_t hq, int32_t stat_pad, int32_t out_mode,
+                           float softmax_scale, void* cuda_stream) {
+  return mb::launch_dq_convert(dq_accum, dq, dq_stride_b, dq_stride_s, dq_stride_h, batch, sq, hq, stat_pad, out_mode,
+                               softmax_scale, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int mb_attn_bwd_block_noalloc(const mb_attn_bwd_block_args* args, void* cuda_stream) {
   return mb::launch_bwd_block_noalloc(args, static_cast<cudaStream_t>(cuda_stream));
 }

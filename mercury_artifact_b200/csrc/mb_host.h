@@ -27,6 +27,8 @@ int launch_tree_merge(const float* const* srcs, int n, float* out, long long row
 int launch_flash_reduce(const float* lhs, const float* rhs, float* out, long long rows, int width, cudaStream_t stream);
 int launch_bwd_preprocess(const mb_bwd_preprocess_args* args, cudaStream_t stream);
 int launch_attn_bwd(const mb_attn_bwd_args* args, cudaStream_t stream);
+int launch_dq_convert(const float* acc, void* dq, long long sb, long long ss, long long sh, int batch, int sq, int hq,
+                      int pad, int out_mode, float scale, cudaStream_t stream);
 int launch_bwd_block_noalloc(const mb_attn_bwd_block_args* args, cudaStream_t stream);
 
 }  // namespace mb

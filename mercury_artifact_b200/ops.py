@@ -16,7 +16,8 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from .attention import _stream_ptr, attn_bwd_dkv, attn_bwd_dq, attn_fwd_segments, bwd_preprocess
+from .attention import (_stream_ptr, attn_bwd_dkv, attn_bwd_dq, attn_bwd_fused, attn_fwd_segments,
+                        bwd_preprocess)
 
 
 # -- get_default_args -----------------------------------------------------------------------
@@ -107,7 +108,9 @@ def _flash_attn_backward(
     (utils/attn_bwd_dsl.py:115).  Writes dq, dk, dv IN PLACE (dk/dv may be the two halves of
     a packed [2,...] buffer) and returns softmax_d = rowsum(dout * out) as [B, Hq, pad64(Sq)].
     `out` and `softmax_lse` are the final forward results of the query rows, which need not come
-    from this K/V block alone.  Always deterministic (no atomics)."""
+    from this K/V block alone.  deterministic=False (the generated code's default) runs the
+    single-sweep kernel, whose dq depends on the order of fp32 additions; deterministic=True runs
+    the two-launch form, which has no atomics and is bitwise reproducible."""
     _reject_unsupported(dropout_p, window_size_left, window_size_right, softcap, alibi_slopes, causal)
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** -0.5
@@ -119,8 +122,12 @@ def _flash_attn_backward(
         dv = torch.empty_like(v)
     q_off = k.shape[1] - q.shape[1] if causal else 0
     stats = bwd_preprocess(dout, out, softmax_lse)
-    attn_bwd_dq(q, dout, stats, [(k, v, 0)], softmax_scale, causal=bool(causal), q_off=q_off, dq=dq)
-    attn_bwd_dkv(k, v, [(q, dout, stats, q_off)], softmax_scale, causal=bool(causal), k_off=0, dk=dk, dv=dv)
+    if deterministic or q.shape[1] == 0 or k.shape[1] == 0:
+        attn_bwd_dq(q, dout, stats, [(k, v, 0)], softmax_scale, causal=bool(causal), q_off=q_off, dq=dq)
+        attn_bwd_dkv(k, v, [(q, dout, stats, q_off)], softmax_scale, causal=bool(causal), k_off=0, dk=dk, dv=dv)
+    else:
+        attn_bwd_fused(q, dout, stats, k, v, softmax_scale, causal=bool(causal), q_off=q_off, k_off=0, dq=dq, dk=dk,
+                       dv=dv)
     return stats.delta
 
 

@@ -38,8 +38,8 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from . import _lib, mesh
-from .attention import (RowStats, _pad64, attn_bwd_dkv, attn_bwd_dq, attn_fwd_multi, attn_fwd_segments,
-                        bwd_preprocess)
+from .attention import (RowStats, _pad64, attn_bwd_dkv, attn_bwd_dq, attn_bwd_fused, attn_fwd_multi,
+                        attn_fwd_segments, bwd_preprocess)
 from .comm import PeerContext, SymmetricBuffer, _align, default_context
 
 _FLAG_REGION = 4096
@@ -240,6 +240,10 @@ class RingAttention:
             raise ValueError("with backward=True the pieces of ring_divide must be multiples of 64 rows "
                              "(the row statistics travel in 64-row blocks)")
         self.last_launches = 0   # kernels this object launched in its latest forward() / backward()
+        # World size 1 runs the backward as one sweep whose dq depends on the order of fp32 additions; set
+        # this to get the two-launch form, which is bitwise reproducible.  (On several ranks the two-launch
+        # form is always used: it needs no cross-rank reduction of dq contributions.)
+        self.deterministic_backward = False
 
     # ------------------------------------------------------------------ helpers
     def _sees_keys_of(self, origin: int) -> bool:
@@ -450,9 +454,18 @@ class RingAttention:
         me = self.rank
         if self.world == 1:
             stats = bwd_preprocess(dout, o, lse)
-            attn_bwd_dq(q, dout, stats, [(kv[0], kv[1], 0)], softmax_scale, causal=self.causal, q_off=0, dq=dq)
-            attn_bwd_dkv(kv[0], kv[1], [(q, dout, stats, 0)], softmax_scale, causal=self.causal, k_off=0,
-                         dk=dkv[0], dv=dkv[1])
+            if self.deterministic_backward:
+                attn_bwd_dq(q, dout, stats, [(kv[0], kv[1], 0)], softmax_scale, causal=self.causal, q_off=0, dq=dq)
+                attn_bwd_dkv(kv[0], kv[1], [(q, dout, stats, 0)], softmax_scale, causal=self.causal, k_off=0,
+                             dk=dkv[0], dv=dkv[1])
+            else:
+                # one sweep: scores computed once, dQ contributions added in fp32 (see attn_bwd_fused)
+                if getattr(self, "_dq_accum", None) is None:
+                    self._dq_accum = torch.empty((self.batch, self.hq, self.stat_pad, self.head_dim),
+                                                 dtype=torch.float32, device=q.device)
+                self._dq_accum.zero_()
+                attn_bwd_fused(q, dout, stats, kv[0], kv[1], softmax_scale, causal=self.causal, q_off=0, k_off=0,
+                               dq=dq, dk=dkv[0], dv=dkv[1], dq_accum=self._dq_accum)
             self._monitor.post(torch.cuda.current_stream())
             return dq, dkv
         if not self.with_backward:

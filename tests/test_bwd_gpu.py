@@ -62,6 +62,35 @@ def test_block_backward_matches_oracle(B, Sq, Sk, Hq, Hkv, causal, q_off):
         assert (got - want).abs().max().item() <= G_TOL
 
 
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,causal,q_off", CASES + [(1, 2048, 2048, 4, 4, True, 0), (2, 1000, 1536, 8, 2, False, 0)])
+def test_single_sweep_backward_matches_oracle(B, Sq, Sk, Hq, Hkv, causal, q_off):
+    """The single-sweep kernel (scores computed once, dQ contributions added in fp32) on the same cases, and
+    dK / dV bit for bit equal to the two-launch form's (same products in the same order; only dQ's summation
+    order differs)."""
+    import mercury_artifact_b200 as mb
+
+    S = max(Sq, Sk)
+    q, k, v, do = seeded_qkv(77, B, S, Hq, Hkv, 128)
+    q, do, k, v = q[:, :Sq].contiguous(), do[:, :Sq].contiguous(), k[:, :Sk].contiguous(), v[:, :Sk].contiguous()
+    scale = 128 ** -0.5
+    ro, rl, rdq, rdk, rdv = _reference(q, k, v, do, scale, causal, q_off)
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    st = mb.bwd_preprocess(dod, ro.cuda(), rl.cuda())
+    for _ in range(2):   # twice: the accumulation buffer is allocated and zeroed per call
+        dq, dk, dv = mb.attn_bwd_fused(qd, dod, st, kd, vd, scale, causal=causal, q_off=q_off, k_off=0)
+        _status_ok()
+        for got, want in ((dq, rdq), (dk, rdk), (dv, rdv)):
+            got = got.float().cpu()
+            assert not torch.isnan(got).any()
+            assert (got - want).abs().max().item() <= G_TOL
+    dk2, dv2 = mb.attn_bwd_dkv(kd, vd, [(qd, dod, st, q_off)], scale, causal=causal, k_off=0)
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    # fp32 output of dq straight from the accumulation buffer
+    dq32 = torch.empty(qd.shape, dtype=torch.float32, device="cuda")
+    mb.attn_bwd_fused(qd, dod, st, kd, vd, scale, causal=causal, q_off=q_off, k_off=0, dq=dq32)
+    assert (dq32.cpu() - rdq).abs().max().item() <= G_TOL
+
+
 def test_drop_in_backward_call_writes_in_place():
     """_flash_attn_backward(**params) as utils/attn_bwd_dsl.py:86-115 calls it: dk/dv are the two
     halves of one packed buffer, dq/dk/dv are written in place, softmax_d is returned."""

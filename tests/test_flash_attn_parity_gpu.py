@@ -49,7 +49,7 @@ def test_block_ops_equal_flash_attn(Sq, Sk, Hq, Hkv, causal):
     assert s_dmask is None and rng is None
     assert o.shape == ro.shape and o.dtype == ro.dtype
     assert tuple(lse.shape) == tuple(rl.shape) == (B, Hq, Sq) and lse.dtype == rl.dtype == torch.float32
-    assert (o.float() - ro.float()).abs().max().item() <= 2e-2
+    assert bool(((o.float() - ro.float()).abs() <= 2e-2 + 2.0 ** -7 * ro.float().abs()).all())
     assert (lse - rl).abs().max().item() <= 1e-3
 
     # backward: both write dq, dk, dv in place and return softmax_d
@@ -59,9 +59,11 @@ def test_block_ops_equal_flash_attn(Sq, Sk, Hq, Hkv, causal):
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     d = ops._flash_attn_backward(dout=do, q=q, k=k, v=v, out=ro, softmax_lse=rl, dq=dq, dk=dk, dv=dv,
                                  deterministic=False, rng_state=None, **kw)
-    assert (dq.float() - rdq.float()).abs().max().item() <= 2e-2
-    assert (dk.float() - rdk.float()).abs().max().item() <= 2e-2
-    assert (dv.float() - rdv.float()).abs().max().item() <= 2e-2
+    # both sides are bf16-rounded: beside the 2e-2 of the fp32 comparison allow one bf16 unit in the last place
+    def close(a, b):
+        return bool(((a.float() - b.float()).abs() <= 2e-2 + 2.0 ** -7 * b.float().abs()).all())
+
+    assert close(dq, rdq) and close(dk, rdk) and close(dv, rdv)
     # softmax_d = rowsum(dout * out), [B, Hq, rows padded]: compare the Sq real rows
     assert d.shape[:2] == rd.shape[:2] == (B, Hq)
     assert (d[:, :, :Sq] - rd[:, :, :Sq].float()).abs().max().item() <= 2e-2

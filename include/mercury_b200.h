@@ -328,6 +328,11 @@ MB_API int mb_status_peek_async(int32_t* pinned_host_dst, void* cuda_stream);
  * device into *out (0 = no device-side timeout so far) and clear it. */
 MB_API int mb_status_fetch(int32_t* out, void* cuda_stream);
 
+/* Text of the CUDA runtime error behind the calling thread's latest MB_E_CUDA, e.g.
+ * "launch attn_bwd_fused_kernel: cudaErrorLaunchOutOfResources (too many resources requested for launch)".
+ * Empty when there was none. */
+MB_API int mb_last_cuda_error(char* buf, int32_t len);
+
 /* Library version, major * 1000 + minor. */
 MB_API int mb_version(void);
 

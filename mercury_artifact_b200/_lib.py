@@ -293,6 +293,7 @@ _SIGNATURES = {
     "mb_set_peer_wait_ms": [C.c_uint32],
     "mb_status_peek_async": [C.c_void_p, C.c_void_p],
     "mb_status_fetch": [C.POINTER(C.c_int32), C.c_void_p],
+    "mb_last_cuda_error": [C.c_char_p, C.c_int32],
 }
 
 
@@ -341,7 +342,12 @@ lib = _load()
 
 def check(code: int, what: str) -> None:
     if code != MB_SUCCESS:
-        raise MercuryB200Error(f"{what} failed: {ERROR_NAMES.get(code, code)}")
+        detail = ""
+        if code == -3:
+            buf = C.create_string_buffer(256)
+            if lib.mb_last_cuda_error(buf, 256) == MB_SUCCESS and buf.value:
+                detail = ": " + buf.value.decode(errors="replace")
+        raise MercuryB200Error(f"{what} failed: {ERROR_NAMES.get(code, code)}{detail}")
 
 
 def status_fetch(stream_ptr: int) -> int:

@@ -497,7 +497,7 @@ int launch_attn_bwd(const mb_attn_bwd_args* x, cudaStream_t stream) {
   dim3 grid((x->own_rows + kOwnRows - 1) / kOwnRows, h_own, x->batch);
   if (fused) return launch_attn_bwd_fused(maps, a, grid, stream);
   attn_bwd_kernel<0><<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(maps, a);
-  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+  return cuda_ok(cudaGetLastError(), "launch attn_bwd_kernel") ? MB_SUCCESS : MB_E_CUDA;
 }
 
 // ---------------------------------------------------------------------------

@@ -10,31 +10,54 @@
 // plus, per step,
 //     dQ^T(step) = K^T dS^T  (rows: head-dim, columns: the 64 queries of the step)
 // which is not accumulated on chip (every step has other queries) but added into an fp32 buffer
-// [batch, hq, rows, head_dim] in global memory with red.global.add: each query row receives one
-// contribution per K/V tile that it can see.  A small kernel afterwards scales and converts the
+// [batch, hq, rows, head_dim] in global memory: the drain warps transpose it through shared memory
+// into 32 query rows x 128 floats (16 KiB, contiguous in the buffer) and one thread adds it with a
+// bulk reduction (cp.reduce.async.bulk ... add.f32).  Per-element red.global.add from registers was
+// measured first: it cost 18 % of the kernel.  Each query row receives one contribution per K/V
+// tile that it can see.  A small kernel afterwards scales and converts the
 // buffer to bf16.  The order of those fp32 additions varies from run to run, so dQ is not
 // bitwise reproducible (dK and dV are); the two-launch form stays available for callers that
 // need determinism.
 //
 // Tensor memory (512 columns): dK | dV | X0 | X1 | Y | dQ^T = 128 + 128 + 4 x 64.  X is
-// double-buffered, so the exponentials of step t+1 start while the products of step t run; Y has
-// one buffer, refilled as soon as the element-wise warps have copied it to registers (mid-step),
-// and dQ^T one, drained by four dedicated warps a step behind.  The bf16 P^T and dS^T overwrite
-// the X buffer they came from (each thread writes only columns it has itself read) and are the
-// tensor-memory A operand of the dV / dK products; dS^T is also written to shared memory
-// ([128 keys][64 queries], 128-byte swizzle) as the MN-major B operand of the dQ^T product, whose
-// A operand is the K tile read MN-major.
+// double-buffered; Y has one buffer, which the element-wise warps copy to registers together with X
+// at the start of a step and hand back at once, so Y of the next step is produced while this step
+// computes; dQ^T has one, drained by four dedicated warps a step behind.  The bf16 P^T and dS^T
+// overwrite the X buffer they came from (each thread writes only columns it has itself read) and are
+// the tensor-memory A operand of the dV / dK products; dS^T is also written to shared memory
+// ([128 keys][64 queries], 128-byte swizzle, two buffers) as the MN-major B operand of the dQ^T
+// product, whose A operand is the K tile read MN-major.
 //
-// 14 warps: 0-7 element-wise (lane quarter x column half), 8 MMA issuer and tensor-memory owner,
-// 9 TMA loader, 10-13 drain dQ^T.  Every wait is bounded, as in the other kernels.
+// Every hand-over between roles costs a few hundred cycles of latency (a timeline of the first
+// version showed the element-wise warps waiting for about 1 100 of the 2 850 cycles of a step), so a
+// step has as few as possible: the element-wise warps wait once (X, Y and the stage's statistics
+// are all there), give Y back, and arrive once when P^T and dS^T are both in place; the issuing warp
+// waits for that one event per step.  Issue order per step t: Y(t+1) | dV, dK, dQ^T of step t |
+// X(t+2); the tensor pipe runs in issue order, which is what makes X(t)'s completion imply that the
+// dQ^T product of step t-2 has finished reading the shared-memory dS^T buffer step t reuses.
+//
+// 16 warps in four warpgroups: 0-7 element-wise (lane quarter x column half), 8 MMA issuer and
+// tensor-memory owner, 9 TMA loader, 10-11 idle, 12-15 drain dQ^T.  Registers are allocated per
+// warpgroup (a CTA of 14 warps is charged for 16), so the CTA launches with 512 x 128 registers and
+// setmaxnreg moves them to where they are needed: 168 for the element-wise warpgroups, 88 for the
+// other two.  Every wait is bounded, as in the other kernels.
 #include "attn_bwd_common.cuh"
 
 namespace mb {
 
-constexpr int kFusedThreads = 448;
-constexpr int kFusedStages = 4;
+constexpr int kFusedThreads = 512;
+#define MB_FUSED_LAUNCH_REGS 128
+#define MB_FUSED_EW_REGS 168
+#define MB_FUSED_AUX_REGS 88
+#define MB_FSTR2(x) #x
+#define MB_FSTR(x) MB_FSTR2(x)
+static_assert(8 * 32 * MB_FUSED_EW_REGS + 8 * 32 * MB_FUSED_AUX_REGS <= kFusedThreads * MB_FUSED_LAUNCH_REGS,
+              "setmaxnreg budgets exceed the registers the CTA is launched with");
+constexpr int kFusedStages = 3;
 constexpr int kDsBytes = kOwnRows * kStrRows * 2;  // 16 KiB: dS^T as [128 keys][64 queries] bf16
-constexpr int kFusedSmemBytes = 2 * kOwnTileBytes + kFusedStages * kBwdStageBytes + kDsBytes + 1024 + 1024;
+constexpr int kDqStageBytes = 32 * kBD * 4;          // 16 KiB: 32 query rows x 128 floats on their way to the reduction
+constexpr int kFusedSmemBytes =
+    2 * kOwnTileBytes + kFusedStages * kBwdStageBytes + 2 * kDsBytes + kDqStageBytes + 1024 + 1024;
 static_assert(kFusedSmemBytes <= 232448, "shared memory budget of one CTA");
 
 struct FusedSmem {
@@ -46,8 +69,7 @@ struct FusedSmem {
   uint64_t x_full[2];
   uint64_t y_full[2];
   uint64_t y_free[2];   // 256 arrivals: every element-wise thread has copied its part of Y
-  uint64_t p_full[2];   // 256 arrivals: P^T of the step is in tensor memory
-  uint64_t ds_full[2];  // 256 arrivals: dS^T of the step is in tensor memory and in shared memory
+  uint64_t pd_full[2];  // 256 arrivals: P^T and dS^T of the step are in tensor memory, dS^T also in shared memory
   uint64_t dq_full[2];  // the dQ^T product of the step (and everything issued before it) is complete
   uint64_t dq_free[2];  // 128 arrivals: the drain warps have copied dQ^T out
   uint64_t acc_full;
@@ -91,15 +113,16 @@ __device__ __forceinline__ void issue_dq_group(uint32_t d_tmem, uint64_t k_desc,
       : "memory");
 }
 
-__global__ void __maxnreg__(144) attn_bwd_fused_kernel(const __grid_constant__ BwdMaps maps,
+__global__ void __maxnreg__(MB_FUSED_LAUNCH_REGS) attn_bwd_fused_kernel(const __grid_constant__ BwdMaps maps,
                                                        const __grid_constant__ BwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sOwn = smem;                   // K tile
   uint8_t* sOwnG = smem + kOwnTileBytes;  // V tile
   uint8_t* sStage = smem + 2 * kOwnTileBytes;
-  uint8_t* sDs = sStage + kFusedStages * kBwdStageBytes;  // 1024-byte aligned: every piece before it is
-  FusedSmem* ctl = reinterpret_cast<FusedSmem*>(sDs + kDsBytes);
+  uint8_t* sDs = sStage + kFusedStages * kBwdStageBytes;  // two buffers; 1024-byte aligned: every piece before it is
+  float* sDq = reinterpret_cast<float*>(sDs + 2 * kDsBytes);  // staging of the dQ reduction
+  FusedSmem* ctl = reinterpret_cast<FusedSmem*>(sDs + 2 * kDsBytes + kDqStageBytes);
   volatile int* abort_word = &ctl->abort_word;
   static_assert((kFusedStages * kBwdStageBytes) % 1024 == 0, "dS^T tile must stay 1024-byte aligned");
 
@@ -120,8 +143,7 @@ __global__ void __maxnreg__(144) attn_bwd_fused_kernel(const __grid_constant__ B
       mbar_init(&ctl->x_full[i], 1);
       mbar_init(&ctl->y_full[i], 1);
       mbar_init(&ctl->y_free[i], 256);
-      mbar_init(&ctl->p_full[i], 256);
-      mbar_init(&ctl->ds_full[i], 256);
+      mbar_init(&ctl->pd_full[i], 256);
       mbar_init(&ctl->dq_full[i], 1);
       mbar_init(&ctl->dq_free[i], 128);
     }
@@ -152,8 +174,11 @@ __global__ void __maxnreg__(144) attn_bwd_fused_kernel(const __grid_constant__ B
   int total_steps = 0;
   for (int s = 0; s < a.nseg; ++s) total_steps += (ctl->seg_last[s] - ctl->seg_first[s]) * n_sub;
 
+  // Every role changes its register budget as the first thing it does (a warpgroup-wide instruction: all
+  // four warps of a warpgroup execute the same one).
   if (warp == 9) {
     // ------------------------------------------------------------------ loader
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_FSTR(MB_FUSED_AUX_REGS) ";");
     if (lane == 0 && total_steps > 0) {
       mbar_expect_tx(&ctl->own_full, 2 * kOwnTileBytes);
       tma_load_4d(sOwn, &maps.own, &ctl->own_full, 0, h_own, own0, b);
@@ -205,6 +230,7 @@ __global__ void __maxnreg__(144) attn_bwd_fused_kernel(const __grid_constant__ B
     }
   } else if (warp == 8) {
     // -------------------------------------------------------------- MMA issuer
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_FSTR(MB_FUSED_AUX_REGS) ";");
     if (total_steps > 0) {  // whole warp, converged; one elected lane issues
       constexpr uint32_t idesc_xy = umma_idesc_bf16(kOwnRows, kStrRows, false, false);  // 128 x 64, both K-major
       constexpr uint32_t idesc_acc = umma_idesc_bf16(kOwnRows, kBD, false, true);       // 128 x 128, B MN-major
@@ -250,29 +276,27 @@ __global__ void __maxnreg__(144) attn_bwd_fused_kernel(const __grid_constant__ B
       for (int t = 0; t < T && ok; ++t) {
         const uint32_t tx = tmem + kColX + (t & 1) * 64;
         const uint32_t su = stage_units(t);
-        // dV += P^T dO as soon as the probabilities are in place
-        ok = mbar_wait_warp(&ctl->p_full[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_P, a.wait_cycles);
-        if (!ok) break;
-        tc_fence_after();
-        issue_acc_group(tmem + 128, tx, str_mn_desc0 + su + kStrGUnits, idesc_acc, t > 0 ? 1u : 0u);
-        // Y of the next step: its buffer is free once every thread holds Y(t) in registers
+        // Y of the next step: its buffer is free once every thread holds Y(t) in registers, which
+        // happens at the start of the element-wise step (its stage arrived before X(t+1) was issued)
         if (t + 1 < T) {
           ok = mbar_wait_warp(&ctl->y_free[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_S, a.wait_cycles);
           if (!ok) break;
           tc_fence_after();
-          issue_y(t + 1);  // its stage arrived before X(t+1) was issued
+          issue_y(t + 1);
         }
-        // dK += dS^T Q, dQ^T = K^T dS^T
-        ok = mbar_wait_warp(&ctl->ds_full[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_P, a.wait_cycles);
+        // dV += P^T dO, dK += dS^T Q, dQ^T = K^T dS^T
+        ok = mbar_wait_warp(&ctl->pd_full[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_P, a.wait_cycles);
         if (!ok) break;
         tc_fence_after();
+        issue_acc_group(tmem + 128, tx, str_mn_desc0 + su + kStrGUnits, idesc_acc, t > 0 ? 1u : 0u);
         issue_acc_group(tmem + 0, tx + 16, str_mn_desc0 + su, idesc_acc, t > 0 ? 1u : 0u);
         if (t > 0) {  // the drain warps must have copied dQ^T(t-1) out
-          ok = mbar_wait_warp(&ctl->dq_free[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_word, MB_ERR_TIMEOUT_O, a.wait_cycles);
+          ok = mbar_wait_warp(&ctl->dq_free[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_word, MB_ERR_TIMEOUT_O,
+                              a.wait_cycles);
           if (!ok) break;
           tc_fence_after();
         }
-        issue_dq_group(tmem + kColDq, kt_desc, ds_desc, idesc_dq);
+        issue_dq_group(tmem + kColDq, kt_desc, ds_desc + (t & 1) * (kDsBytes / 16), idesc_dq);
         umma_commit_elect(&ctl->dq_full[t & 1]);
         umma_commit_elect(&ctl->str_empty[t % kFusedStages]);
         // X of step t+2 into the buffer whose P^T / dS^T the products above read (in issue order)
@@ -293,53 +317,84 @@ __global__ void __maxnreg__(144) attn_bwd_fused_kernel(const __grid_constant__ B
         __syncwarp();
       }
     }
-  } else if (warp >= 10) {
+  } else if (warp == 10 || warp == 11) {
+    // idle: these two warps only complete the third warpgroup
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_FSTR(MB_FUSED_AUX_REGS) ";");
+  } else if (warp >= 12) {
     // ------------------------------------------------ drain dQ^T: tensor memory -> red.global.add
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_FSTR(MB_FUSED_AUX_REGS) ";");
     const int quarter = warp & 3;
     const int d = (quarter << 5) | lane;  // head-dim index == tensor-memory lane
     const uint32_t tq = tmem + kColDq + (static_cast<uint32_t>(quarter << 5) << 16);
+    const bool issuer = warp == 12 && lane == 0;
     bool ok = true;
     int t = 0;
     for (int s = 0; s < a.nseg && ok; ++s) {
       const int f = ctl->seg_first[s], l = ctl->seg_last[s];
       const int rows = a.seg_rows[s];
       for (int g = 0; g < n_sub && ok; ++g) {
-        float* acc_base = a.seg_dq[s] + ((long long)b * a.Hq + (h_str_base + g)) * a.seg_stat_pad[s] * kBD + d;
+        float* acc_base = a.seg_dq[s] + ((long long)b * a.Hq + (h_str_base + g)) * a.seg_stat_pad[s] * kBD;
         for (int st = f; st < l; ++st, ++t) {
           ok = mbar_wait_warp(&ctl->dq_full[t & 1], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_O, a.wait_cycles);
+          {
+            // The four drain warps meet at named barriers below, so they must leave the loop together:
+            // agree on the outcome of the (bounded) wait.  Every warp always reaches this point.
+            uint32_t all_ok;
+            asm volatile(
+                "{\n\t"
+                ".reg .pred pin, pout;\n\t"
+                "setp.ne.u32 pin, %1, 0;\n\t"
+                "bar.red.and.pred pout, 2, 128, pin;\n\t"
+                "selp.u32 %0, 1, 0, pout;\n\t"
+                "}"
+                : "=r"(all_ok)
+                : "r"(ok ? 1u : 0u)
+                : "memory");
+            ok = all_ok != 0;
+          }
           if (!ok) break;
           tc_fence_after();
-          uint32_t v0[32], v1[32];
-          tmem_ld32(tq, v0);
-          tmem_ld32(tq + 32, v1);
+          uint32_t v[2][32];
+          tmem_ld32(tq, v[0]);
+          tmem_ld32(tq + 32, v[1]);
           tmem_wait_ld();
           tc_fence_before();
           mbar_arrive(&ctl->dq_free[t & 1]);
           const int r0 = st * kStrRows;
-          float* dst = acc_base + (long long)r0 * kBD;
-          const int nrow = min(kStrRows, rows - r0);  // rows past the shard's end carry zeros: skipped
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            if (e < nrow)
-              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + e * kBD), "f"(__uint_as_float(v0[e])) : "memory");
-          }
+          for (int hh = 0; hh < 2; ++hh) {
+            const int nrow = min(32, rows - (r0 + hh * 32));  // rows past the shard's end carry zeros: skipped
+            // the staging tile is free once the previous bulk reduction has read it
+            if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            // transpose: lane d of the tile's column e becomes element [e][d] (conflict-free rows of 128 floats)
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            if (32 + e < nrow)
-              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (32 + e) * kBD), "f"(__uint_as_float(v1[e]))
-                           : "memory");
+            for (int e = 0; e < 32; ++e) sDq[e * kBD + d] = __uint_as_float(v[hh][e]);
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (issuer && nrow > 0) {
+              float* dst = acc_base + (long long)(r0 + hh * 32) * kBD;
+              asm volatile(
+                  "cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;\n\t"
+                  "cp.async.bulk.commit_group;"
+                  :
+                  : "l"(dst), "r"(smem_u32(sDq)), "r"(nrow * kBD * 4)
+                  : "memory");
+            }
           }
         }
       }
     }
+    // the last reduction must have left shared memory before the CTA exits (its global side completes on its own)
+    if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ------------------------------------------------ element-wise warps (0..7) + epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 " MB_FSTR(MB_FUSED_EW_REGS) ";");
     const int quarter = warp & 3, half = warp >> 2;
     const int row = (quarter << 5) | lane;  // key row == tensor-memory lane
     const uint32_t lane_field = static_cast<uint32_t>(quarter << 5) << 16;
     const int own_pos = a.own_off + own0 + row;
     // my row of the dS^T tile in shared memory: four 16-byte chunks (32 queries), 128-byte swizzle
-    uint8_t* ds_row = sDs + row * 128;
     const int swz = row & 7;
     bool ok = true;
 
@@ -352,17 +407,20 @@ __global__ void __maxnreg__(144) attn_bwd_fused_kernel(const __grid_constant__ B
           const int buf = t & 1, stage = t % kFusedStages;
           const uint32_t tx = tmem + kColX + buf * 64 + lane_field + half * 32;
           const uint32_t ty = tmem + kColY + lane_field + half * 32;
-          ok = mbar_wait_warp(&ctl->x_full[buf], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_S, a.wait_cycles);
-          if (!ok) break;
-          // the stage's statistics arrived with the stream tile (complete long ago: this only orders the
-          // reads below after the bulk copy that wrote them)
+          // One wait per step: the stage (its statistics are read below; it landed long ago, this only
+          // orders those reads after the bulk copy), X and Y.
           ok = mbar_wait_warp(&ctl->str_full[stage], (t / kFusedStages) & 1, abort_word, MB_ERR_TIMEOUT_KV_FULL,
-                              a.wait_cycles);
+                              a.wait_cycles) &&
+               mbar_wait_warp(&ctl->x_full[buf], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_S, a.wait_cycles) &&
+               mbar_wait_warp(&ctl->y_full[buf], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_S, a.wait_cycles);
           if (!ok) break;
           tc_fence_after();
-          uint32_t xr[32];
+          uint32_t xr[32], yr[32];
           tmem_ld32(tx, xr);
+          tmem_ld32(ty, yr);
           tmem_wait_ld();
+          tc_fence_before();
+          mbar_arrive(&ctl->y_free[buf]);   // Y(t+1) may overwrite the buffer from here on
 
           const int c0 = st * kStrRows + half * 32;  // first query row (local to the segment) of my columns
           int lo = 0;
@@ -372,58 +430,15 @@ __global__ void __maxnreg__(144) attn_bwd_fused_kernel(const __grid_constant__ B
           const float* nl_col = stats + half * 32;            // -lse*log2(e) of my 32 columns
           const float* d_col = stats + kStrRows + half * 32;  // delta of my 32 columns
 
-          // p = exp2(x*c + nlse2): packed pairs; kept in fp32 for the dS product, written as bf16
-          uint32_t pk[16];
-          {
-            const uint64_t c2 = pack2(a.scale_log2, a.scale_log2);
-#pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              const uint64_t nl2 = *reinterpret_cast<const uint64_t*>(nl_col + e);
-              const uint64_t t2 = fma2(pack2(__uint_as_float(xr[e]), __uint_as_float(xr[e + 1])), c2, nl2);
-              float t0, t1;
-              unpack2(t2, t0, t1);
-              float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-              if (need_mask) {
-                if (e < lo) p0 = 0.f;
-                if (e + 1 < lo) p1 = 0.f;
-              }
-              xr[e] = __float_as_uint(p0);
-              xr[e + 1] = __float_as_uint(p1);
-              pk[e >> 1] = pack_bf16x2(p0, p1);
-            }
-          }
+          // p = exp2(x*c + nlse2), ds = p * (y - delta): packed pairs, bf16 pairs out
+          uint32_t pk[16], dk[16];
+          if (need_mask) ew_compute<true, true>(xr, yr, pk, dk, a.scale_log2, nl_col, d_col, 0.f, 0.f, lo, 32);
+          else ew_compute<true, false>(xr, yr, pk, dk, a.scale_log2, nl_col, d_col, 0.f, 0.f, lo, 32);
           tmem_st16(tx, pk);
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(&ctl->p_full[buf]);
-
-          // dP^T
-          ok = mbar_wait_warp(&ctl->y_full[buf], (t >> 1) & 1, abort_word, MB_ERR_TIMEOUT_S, a.wait_cycles);
-          if (!ok) break;
-          tc_fence_after();
-          uint32_t yr[32];
-          tmem_ld32(ty, yr);
-          tmem_wait_ld();
-          tc_fence_before();
-          mbar_arrive(&ctl->y_free[buf]);
-
-          uint32_t dk[16];
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const uint64_t d2 = *reinterpret_cast<const uint64_t*>(d_col + e);
-            const uint64_t s2 = mul2(pack2(__uint_as_float(xr[e]), __uint_as_float(xr[e + 1])),
-                                     sub2(pack2(__uint_as_float(yr[e]), __uint_as_float(yr[e + 1])), d2));
-            float s0, s1;
-            unpack2(s2, s0, s1);
-            dk[e >> 1] = pack_bf16x2(s0, s1);
-          }
           tmem_st16(tx + 16, dk);
-          // the shared-memory copy of dS^T(t-1) must have been consumed by its dQ^T product
-          if (t > 0) {
-            ok = mbar_wait_warp(&ctl->dq_full[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_word, MB_ERR_TIMEOUT_O,
-                                a.wait_cycles);
-            if (!ok) break;
-          }
+          // dS^T also to shared memory.  Buffer t & 1 was last read by the dQ^T product of step t-2, which
+          // the tensor pipe finished before it produced X(t) (issue order), so no further wait is needed.
+          uint8_t* ds_row = sDs + buf * kDsBytes + row * 128;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int chunk = (half * 4 + c) ^ swz;
@@ -432,7 +447,7 @@ __global__ void __maxnreg__(144) attn_bwd_fused_kernel(const __grid_constant__ B
           fence_proxy_async_smem();
           tmem_wait_st();
           tc_fence_before();
-          mbar_arrive(&ctl->ds_full[buf]);
+          mbar_arrive(&ctl->pd_full[buf]);
         }
       }
     }
@@ -535,15 +550,16 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const DqConvertArgs a) 
 int launch_attn_bwd_fused(const BwdMaps& maps, const BwdArgs& a, dim3 grid, cudaStream_t stream) {
   static bool done[64] = {};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return MB_E_CUDA;
+  if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return MB_E_CUDA;
   if (dev >= 0 && dev < 64 && !done[dev]) {
-    if (cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBytes) !=
-        cudaSuccess)
+    if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kFusedSmemBytes),
+                 "shared-memory attribute of attn_bwd_fused_kernel"))
       return MB_E_CUDA;
     done[dev] = true;
   }
   attn_bwd_fused_kernel<<<grid, kFusedThreads, kFusedSmemBytes, stream>>>(maps, a);
-  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+  return cuda_ok(cudaGetLastError(), "launch attn_bwd_fused_kernel") ? MB_SUCCESS : MB_E_CUDA;
 }
 
 int launch_dq_convert(const float* acc, void* dq, long long sb, long long ss, long long sh, int batch, int sq, int hq,

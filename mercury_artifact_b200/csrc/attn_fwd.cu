@@ -618,7 +618,7 @@ int launch_attn_fwd_multi(const mb_attn_fwd_multi_args* x, cudaStream_t stream) 
 
   dim3 grid(x_total, x->hq, x->batch);
   attn_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(maps, a);
-  return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+  return cuda_ok(cudaGetLastError(), "launch attn_fwd_kernel") ? MB_SUCCESS : MB_E_CUDA;
 }
 
 // One query shard: the single-job form of the launch above.

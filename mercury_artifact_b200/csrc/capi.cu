@@ -1,12 +1,22 @@
 // extern "C" surface of libmercury_b200.so and the few host utilities the
 // kernels share (TMA descriptor encoding, the per-device status word).
 #include <cudaTypedefs.h>
+#include <stdio.h>
 
 #include "mb_host.h"
 
 namespace mb {
 
 __device__ int g_status_word = 0;
+
+static thread_local char g_last_cuda_error[256] = "";
+
+bool cuda_ok(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return true;
+  snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+  cudaGetLastError();  // clear the non-sticky error so that it is not reported again by a later call
+  return false;
+}
 
 int* default_status_word() {
   static int* cached[64] = {};
@@ -41,7 +51,14 @@ int encode_tiled_bf16(CUtensorMap* map, void* base, int rank, const cuuint64_t* 
 
 extern "C" {
 
-int mb_version(void) { return 1000; }
+int mb_version(void) { return 1001; }
+
+int mb_last_cuda_error(char* buf, int32_t len) {
+  if (buf == nullptr || len <= 0) return MB_E_INVALID;
+  strncpy(buf, mb::g_last_cuda_error, static_cast<size_t>(len) - 1);
+  buf[len - 1] = 0;
+  return MB_SUCCESS;
+}
 
 int mb_attn_fwd(const mb_attn_fwd_args* args, void* cuda_stream) {
   return mb::launch_attn_fwd(args, static_cast<cudaStream_t>(cuda_stream));

@@ -13,6 +13,9 @@ namespace mb {
 int encode_tiled_bf16(CUtensorMap* map, void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
                       const cuuint32_t* box, const cuuint32_t* elem_strides);
 
+// Remember a failed CUDA runtime call for mb_last_cuda_error(); returns true when `e` is cudaSuccess.
+bool cuda_ok(cudaError_t e, const char* what);
+
 // Device address of the library's status word on the current device (nullptr on failure).
 int* default_status_word();
 

@@ -35,49 +35,75 @@ __device__ __forceinline__ float4 load4(const void* base, long long idx, int is_
   return r;
 }
 
-// One warp per (b, s, h) row; each lane walks the row in float4 steps.
+// A warp takes kRowsPerWarp consecutive (b, s, h) rows per iteration: lanes 0..3 fetch the rows' two
+// log-sum-exp words and work out the weights at the same time (one round of memory latency instead of
+// one per row), then every lane issues the float4 loads of all four rows before it uses any of them.
+constexpr int kRowsPerWarp = 4;
+
 __global__ void __launch_bounds__(256) merge_kernel(const MergeArgs a) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const long long rows = static_cast<long long>(a.B) * a.S * a.H;
-  for (long long row = warp0; row < rows; row += nwarps) {
-    const int h = static_cast<int>(row % a.H);
-    const long long bs = row / a.H;
-    const int s = static_cast<int>(bs % a.S);
-    const int b = static_cast<int>(bs / a.S);
-    const float bl = a.block_lse[(static_cast<long long>(b) * a.H + h) * a.S + s];
-    const float l = a.first ? -INFINITY : a.lse[row];
-    // weight of the block and the merged LSE
-    float w, new_l;
-    if (l == -INFINITY) {  // nothing accumulated yet for this row
-      w = 1.f;
-      new_l = bl;
-    } else if (bl == -INFINITY) {  // the block saw no key for this row
-      w = 0.f;
-      new_l = l;
-    } else {
-      const float x = bl - l;
-      w = 1.f / (1.f + expf(-x));                          // sigmoid(block_lse - lse)
-      new_l = l + fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));  // lse - logsigmoid(lse - block_lse)
-    }
-    float* orow = a.out + row * a.D;
-    const long long brow = b * a.bo_sb + s * a.bo_ss + h * a.bo_sh;
-    for (int d = lane * 4; d < a.D; d += 128) {
-      const float4 bo = load4(a.block_out, brow + d, a.block_is_f32);
-      float4 o;
-      if (w == 1.f) {
-        o = bo;
+  for (long long row0 = warp0 * kRowsPerWarp; row0 < rows; row0 += nwarps * kRowsPerWarp) {
+    // weight of the block and position of its row, per row of the group (lane r serves row r)
+    float my_w = 0.f;
+    long long my_brow = 0;
+    if (lane < kRowsPerWarp && row0 + lane < rows) {
+      const long long row = row0 + lane;
+      const int h = static_cast<int>(row % a.H);
+      const long long bs = row / a.H;
+      const int s = static_cast<int>(bs % a.S);
+      const int b = static_cast<int>(bs / a.S);
+      const float bl = a.block_lse[(static_cast<long long>(b) * a.H + h) * a.S + s];
+      const float l = a.first ? -INFINITY : a.lse[row];
+      float new_l;
+      if (l == -INFINITY) {  // nothing accumulated yet for this row
+        my_w = 1.f;
+        new_l = bl;
+      } else if (bl == -INFINITY) {  // the block saw no key for this row
+        my_w = 0.f;
+        new_l = l;
       } else {
-        o = *reinterpret_cast<const float4*>(orow + d);
-        o.x -= w * (o.x - bo.x);
-        o.y -= w * (o.y - bo.y);
-        o.z -= w * (o.z - bo.z);
-        o.w -= w * (o.w - bo.w);
+        const float x = bl - l;
+        my_w = 1.f / (1.f + expf(-x));                          // sigmoid(block_lse - lse)
+        new_l = l + fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));  // lse - logsigmoid(lse - block_lse)
       }
-      *reinterpret_cast<float4*>(orow + d) = o;
+      a.lse[row] = new_l;
+      my_brow = b * a.bo_sb + s * a.bo_ss + h * a.bo_sh;
     }
-    if (lane == 0) a.lse[row] = new_l;
+    float w[kRowsPerWarp];
+    long long brow[kRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+      w[r] = __shfl_sync(0xffffffffu, my_w, r);
+      brow[r] = __shfl_sync(0xffffffffu, my_brow, r);
+    }
+    for (int d = lane * 4; d < a.D; d += 128) {
+      float4 bo[kRowsPerWarp], o[kRowsPerWarp];
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) {
+        if (row0 + r < rows) {
+          bo[r] = load4(a.block_out, brow[r] + d, a.block_is_f32);
+          // w == 1 adopts the block: the old state (uninitialised on the first step) is not read
+          if (w[r] != 1.f) o[r] = *reinterpret_cast<const float4*>(a.out + (row0 + r) * a.D + d);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) {
+        if (row0 + r < rows) {
+          float4 v = bo[r];
+          if (w[r] != 1.f) {
+            v = o[r];
+            v.x -= w[r] * (v.x - bo[r].x);
+            v.y -= w[r] * (v.y - bo[r].y);
+            v.z -= w[r] * (v.z - bo[r].z);
+            v.w -= w[r] * (v.w - bo[r].w);
+          }
+          *reinterpret_cast<float4*>(a.out + (row0 + r) * a.D + d) = v;
+        }
+      }
+    }
   }
 }
 
@@ -223,7 +249,7 @@ int launch_merge(const mb_merge_args* x, cudaStream_t stream) {
   a.block_is_f32 = x->block_dtype == MB_DTYPE_F32;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long want = (rows + 7) / 8;  // 8 warps per block
+  const long long want = (rows + 8 * kRowsPerWarp - 1) / (8 * kRowsPerWarp);  // 8 warps per block
   const long long cap = static_cast<long long>(sms) * 8;
   const int grid = static_cast<int>(want < cap ? want : cap);
   merge_kernel<<<grid, 256, 0, stream>>>(a);

@@ -276,6 +276,8 @@ class RingAttention:
     def _stage_views(self, origin: int):
         buf = self._x.stage(origin)
         kv, _ = _carve(buf, self._off_kv, self.kv_shape, torch.bfloat16)
+        if self._slot_bytes <= self._off_q:     # K/V only: nobody pulls queries in this configuration
+            return kv, None, None, None
         q, _ = _carve(buf, self._off_q, self.q_shape, torch.bfloat16)
         if not self.with_backward:
             return kv, q, None, None

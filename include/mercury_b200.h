@@ -312,6 +312,38 @@ MB_API int mb_flags_signal(int32_t* const* flags, const int32_t* values, int32_t
 MB_API int mb_flags_wait(const int32_t* const* flags, const int32_t* values, int32_t n, uint64_t timeout_ns,
                          int32_t* status, void* cuda_stream);
 
+/* One contiguous byte range of a pull: src may be a peer mapping; both addresses and the size are
+ * multiples of 16. */
+typedef struct mb_pull_range {
+  const void* src;
+  void* dst;
+  uint64_t bytes;
+} mb_pull_range;
+
+#define MB_MAX_PULL_RANGES 8
+#define MB_MAX_PULL_FLAGS 4
+
+typedef struct mb_pull_args {
+  int32_t nranges;
+  int32_t nflags;
+  mb_pull_range range[MB_MAX_PULL_RANGES];
+  const int32_t* wait_flag; /* optional: do not read before *wait_flag >= wait_value (the source's "published" word) */
+  int32_t wait_value;
+  int32_t ctas; /* CTAs to use; 0 selects one per SM */
+  int32_t* flag[MB_MAX_PULL_FLAGS]; /* raised (release, system scope) once every byte has landed; may be peer memory */
+  int32_t value[MB_MAX_PULL_FLAGS];
+  int32_t* counter; /* zero-initialised word on this GPU; counts finished CTAs and is left at zero again */
+  int32_t* status;  /* NULL selects the library's word */
+} mb_pull_args;
+
+/* SM-driven pull over NVLink: a grid of one-warp CTAs copies the ranges in 8 KiB chunks with bulk
+ * copies peer -> shared memory -> local memory (three chunks in flight per CTA), waits first (bounded)
+ * for the source's flag, and the last CTA to finish raises the completion flags -- wait, transfer and
+ * signal in ONE launch.  The CTAs are small enough (25 KiB of shared memory, 32 threads) to run beside a
+ * resident attention CTA on every SM.  The alternative to mb_flag_wait + mb_copy_async + mb_flags_signal
+ * (copy engines); both replace the transfer inside SendRecv, mercury/backend/pytorch/utils.py:22-39. */
+MB_API int mb_pull_sm(const mb_pull_args* args, void* cuda_stream);
+
 /* How long a kernel waits for a shard that another GPU has to deliver (the ready_flag of a segment or of
  * a job's queries) before it gives up with status 109.  Process-wide, applies to launches made afterwards.
  * Default 30 000 ms: ranks of a job may be seconds apart (first-call module load, data loading, a

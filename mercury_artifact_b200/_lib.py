@@ -118,6 +118,29 @@ class AttnFwdMultiArgs(C.Structure):
     ]
 
 
+MB_MAX_PULL_RANGES = 8
+MB_MAX_PULL_FLAGS = 4
+
+
+class PullRange(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("bytes", C.c_uint64)]
+
+
+class PullArgs(C.Structure):
+    _fields_ = [
+        ("nranges", C.c_int32),
+        ("nflags", C.c_int32),
+        ("range", PullRange * MB_MAX_PULL_RANGES),
+        ("wait_flag", C.c_void_p),
+        ("wait_value", C.c_int32),
+        ("ctas", C.c_int32),
+        ("flag", C.c_void_p * MB_MAX_PULL_FLAGS),
+        ("value", C.c_int32 * MB_MAX_PULL_FLAGS),
+        ("counter", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
 MB_DTYPE_BF16 = 0
 MB_DTYPE_F32 = 1
 
@@ -290,6 +313,7 @@ _SIGNATURES = {
     "mb_flag_wait": [C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p],
     "mb_flags_signal": [C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int32, C.c_void_p],
     "mb_flags_wait": [C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p],
+    "mb_pull_sm": [C.POINTER(PullArgs), C.c_void_p],
     "mb_set_peer_wait_ms": [C.c_uint32],
     "mb_status_peek_async": [C.c_void_p, C.c_void_p],
     "mb_status_fetch": [C.POINTER(C.c_int32), C.c_void_p],

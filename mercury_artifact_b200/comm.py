@@ -168,6 +168,31 @@ class PeerContext:
                                               C.c_uint64(_FLAG_TIMEOUT_NS if timeout_ns is None else timeout_ns), None,
                                               C.c_void_p(stream.cuda_stream)), "mb_flags_wait")
 
+    def pull_sm(self, ranges, wait, flags, counter_ptr: int, stream: torch.cuda.Stream, ctas: int = 0) -> None:
+        """SM-driven pull (mb_pull_sm): ranges [(dst address, src address, nbytes)], wait = (flag address,
+        value) or None, flags [(address, value)] raised when every byte has landed -- one launch for wait,
+        transfer and signal.  More than eight ranges are split over several launches; the flags go with
+        the last one."""
+        ranges = [r for r in ranges if r[2] > 0]
+        groups = [ranges[i:i + _lib.MB_MAX_PULL_RANGES] for i in range(0, len(ranges), _lib.MB_MAX_PULL_RANGES)] or [[]]
+        for gi, grp in enumerate(groups):
+            a = _lib.PullArgs()
+            a.nranges = len(grp)
+            for i, (dst, src, nbytes) in enumerate(grp):
+                a.range[i].src, a.range[i].dst, a.range[i].bytes = src, dst, nbytes
+            if wait is not None and gi == 0:
+                a.wait_flag, a.wait_value = wait[0], int(wait[1])
+            last = gi == len(groups) - 1
+            fl = list(flags) if last else []
+            if len(fl) > _lib.MB_MAX_PULL_FLAGS:
+                raise ValueError(f"at most {_lib.MB_MAX_PULL_FLAGS} completion flags per pull")
+            a.nflags = len(fl)
+            for i, (ptr, val) in enumerate(fl):
+                a.flag[i], a.value[i] = ptr, int(val)
+            a.counter, a.ctas, a.status = counter_ptr, int(ctas), None
+            self.launch_count += 1
+            _lib.check(_lib.lib.mb_pull_sm(C.byref(a), C.c_void_p(stream.cuda_stream)), "mb_pull_sm")
+
     def check(self) -> None:
         """Synchronise and raise if any device-side wait timed out since the last check."""
         with torch.cuda.device(self.device):

@@ -74,6 +74,113 @@ __global__ void flags_wait_kernel(const __grid_constant__ FlagBatch b, unsigned 
   }
 }
 
+// ---------------------------------------------------------------------------
+// SM-driven pull: peer memory -> shared memory -> local memory with bulk copies
+// ---------------------------------------------------------------------------
+constexpr int kPullChunk = 8192;
+constexpr int kPullDepth = 3;
+constexpr int kPullSmemBytes = kPullDepth * kPullChunk;
+
+struct PullArgs {
+  const uint8_t* src[MB_MAX_PULL_RANGES];
+  uint8_t* dst[MB_MAX_PULL_RANGES];
+  unsigned long long bytes[MB_MAX_PULL_RANGES];
+  int first_chunk[MB_MAX_PULL_RANGES + 1];  // prefix sums of the ranges' chunk counts
+  int nranges;
+  const int* wait_flag;
+  int wait_value;
+  int* flag[MB_MAX_PULL_FLAGS];
+  int value[MB_MAX_PULL_FLAGS];
+  int nflags;
+  int* counter;
+  long long wait_cycles;
+  int* status;
+};
+
+__global__ void __launch_bounds__(32) pull_kernel(const __grid_constant__ PullArgs a) {
+  extern __shared__ __align__(128) uint8_t pull_smem[];
+  __shared__ uint64_t bar[kPullDepth];
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int i = 0; i < kPullDepth; ++i) mbar_init(&bar[i], 1);
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    bool ok = true;
+    if (a.wait_flag != nullptr) {
+      ok = flag_wait_ge(a.wait_flag, a.wait_value, &abort_word, MB_ERR_TIMEOUT_FLAG, a.wait_cycles);
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
+    const int total = a.first_chunk[a.nranges];
+    // chunk c of this CTA's list: global chunk index blockIdx.x + c * gridDim.x
+    auto chunk_of = [&](int idx, const uint8_t** src, uint8_t** dst, unsigned* nbytes) {
+      int r = 0;
+      while (r + 1 < a.nranges && idx >= a.first_chunk[r + 1]) ++r;
+      const unsigned long long off = static_cast<unsigned long long>(idx - a.first_chunk[r]) * kPullChunk;
+      const unsigned long long left = a.bytes[r] - off;
+      *src = a.src[r] + off;
+      *dst = a.dst[r] + off;
+      *nbytes = static_cast<unsigned>(left < kPullChunk ? left : kPullChunk);
+    };
+    const int mine = ok && (int)blockIdx.x < total ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    // kPullDepth buffers: one being drained by a store, the others receiving loads.  Chunk c + kPullDepth - 1
+    // goes into the buffer chunk c - 1 was stored from; that store is the second most recent bulk group
+    // when the refill is issued (right after the store of chunk c), hence wait_group.read 1.
+    int issued = 0;
+    auto issue_load = [&](int c) {
+      const uint8_t* src;
+      uint8_t* dst;
+      unsigned nbytes;
+      chunk_of(blockIdx.x + c * gridDim.x, &src, &dst, &nbytes);
+      const int b = c % kPullDepth;
+      mbar_expect_tx(&bar[b], nbytes);
+      bulk_load(pull_smem + b * kPullChunk, src, nbytes, &bar[b]);
+      ++issued;
+    };
+    for (int c = 0; c < kPullDepth - 1 && c < mine; ++c) issue_load(c);
+    for (int c = 0; c < mine && ok; ++c) {
+      const int b = c % kPullDepth;
+      ok = mbar_wait(&bar[b], (c / kPullDepth) & 1, &abort_word, MB_ERR_TIMEOUT_MISC, a.wait_cycles);
+      if (!ok) break;
+      const uint8_t* src;
+      uint8_t* dst;
+      unsigned nbytes;
+      chunk_of(blockIdx.x + c * gridDim.x, &src, &dst, &nbytes);
+      asm volatile(
+          "cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n\t"
+          "cp.async.bulk.commit_group;" ::"l"(dst),
+          "r"(smem_u32(pull_smem + b * kPullChunk)), "r"(nbytes)
+          : "memory");
+      const int nxt = c + kPullDepth - 1;
+      if (nxt < mine) {
+        if (c >= 1) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        issue_load(nxt);
+      }
+    }
+    if (!ok) {
+      // loads still in flight must land before the CTA (and its shared memory) goes away: bounded
+      for (int m = 0; m < kPullDepth; ++m) {
+        const long long t0 = clock64();
+        while (issued > m && !mbar_try_wait(&bar[m], ((issued - 1 - m) / kPullDepth) & 1) &&
+               clock64() - t0 < kWaitCycleLimit / 16) {
+        }
+      }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every store of this CTA is complete
+    if (abort_word != 0 && a.status != nullptr) atomicCAS(a.status, 0, abort_word);
+    // count this CTA; the last one publishes (a CTA that gave up still counts, the status word tells the host)
+    __threadfence();
+    int prev;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(a.counter) : "memory");
+    if (prev == (int)gridDim.x - 1) {
+      *a.counter = 0;
+      __threadfence_system();
+      for (int i = 0; i < a.nflags; ++i)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.flag[i]), "r"(a.value[i]) : "memory");
+    }
+  }
+}
+
 // The flag kernels must be able to start while an attention kernel fills every SM.  An SM
 // only co-hosts kernels that agree on its shared-memory carve-out, and the attention
 // kernels run with the largest one, so the flag kernels ask for the same.
@@ -89,6 +196,7 @@ static void prefer_max_smem_carveout_once() {
                        cudaSharedmemCarveoutMaxShared);
   cudaFuncSetAttribute(flags_wait_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                        cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(pull_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   done[dev] = true;
 }
 
@@ -190,6 +298,50 @@ int mb_flags_wait(const int32_t* const* flags, const int32_t* values, int32_t n,
   mb::prefer_max_smem_carveout_once();
   mb::flags_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(b, timeout_ns, st);
   return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
+}
+
+int mb_pull_sm(const mb_pull_args* x, void* cuda_stream) {
+  if (x == nullptr || x->nranges < 0 || x->nranges > MB_MAX_PULL_RANGES || x->nflags < 0 ||
+      x->nflags > MB_MAX_PULL_FLAGS || x->counter == nullptr || x->ctas < 0)
+    return MB_E_INVALID;
+  mb::PullArgs a;
+  memset(&a, 0, sizeof(a));
+  int n = 0, chunks = 0;
+  for (int r = 0; r < x->nranges; ++r) {
+    const mb_pull_range& g = x->range[r];
+    if (g.bytes == 0) continue;
+    if (g.src == nullptr || g.dst == nullptr) return MB_E_INVALID;
+    if ((reinterpret_cast<uintptr_t>(g.src) | reinterpret_cast<uintptr_t>(g.dst) | g.bytes) & 15u) return MB_E_INVALID;
+    a.src[n] = static_cast<const uint8_t*>(g.src);
+    a.dst[n] = static_cast<uint8_t*>(g.dst);
+    a.bytes[n] = g.bytes;
+    a.first_chunk[n] = chunks;
+    chunks += static_cast<int>((g.bytes + mb::kPullChunk - 1) / mb::kPullChunk);
+    ++n;
+  }
+  a.first_chunk[n] = chunks;
+  a.nranges = n;
+  a.wait_flag = x->wait_flag;
+  a.wait_value = x->wait_value;
+  for (int i = 0; i < x->nflags; ++i) {
+    if (x->flag[i] == nullptr) return MB_E_INVALID;
+    a.flag[i] = x->flag[i];
+    a.value[i] = x->value[i];
+  }
+  a.nflags = x->nflags;
+  a.counter = x->counter;
+  a.wait_cycles = mb::peer_wait_cycles();
+  a.status = x->status ? x->status : mb::default_status_word();
+  if (a.status == nullptr) return MB_E_CUDA;
+  int dev = 0, sms = 148;
+  if (!mb::cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return MB_E_CUDA;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int grid = x->ctas > 0 ? x->ctas : sms;
+  if (chunks > 0 && grid > chunks) grid = chunks;
+  if (grid < 1) grid = 1;
+  mb::prefer_max_smem_carveout_once();
+  mb::pull_kernel<<<grid, 32, mb::kPullSmemBytes, static_cast<cudaStream_t>(cuda_stream)>>>(a);
+  return mb::cuda_ok(cudaGetLastError(), "launch pull_kernel") ? MB_SUCCESS : MB_E_CUDA;
 }
 
 }  // extern "C"

@@ -205,3 +205,47 @@ def test_multi_job_forward_flags_and_completion():
     o2, l2 = mb.attn_fwd_segments(q[:, 768:], segs, scale, causal=True, q_off=768)
     assert _lib.status_fetch(st.cuda_stream) == 0 and torch.equal(o2, ra)
     words.free()
+
+
+def test_sm_pull_kernel_copies_ranges_waits_and_signals():
+    """mb_pull_sm on one device (source and destination local): several ranges of odd sizes arrive bit for
+    bit, the kernel waits for the source's flag first, raises the completion flags last, leaves its counter
+    at zero, and gives up with a status code when the source's flag never comes."""
+    from mercury_artifact_b200 import _lib
+    from mercury_artifact_b200.comm import DeviceBuffer, PeerContext
+
+    dev = torch.device("cuda", 0)
+    ctx = PeerContext()
+    st = torch.cuda.current_stream()
+    words = DeviceBuffer(256, dev)    # [0] source flag, [1..2] completion flags, [3] counter
+    g = torch.Generator(device="cuda").manual_seed(3)
+    src = torch.randint(0, 255, (3 * (1 << 20) + 4096,), dtype=torch.uint8, device=dev, generator=g)
+    dst = torch.zeros_like(src)
+    # ranges: 1 MiB + 16 bytes, 48 bytes, 8 KiB exactly, 1.5 MiB -- all multiples of 16, none of the chunk size
+    spans = [(0, (1 << 20) + 16), (1 << 21, 48), ((1 << 21) + 4096, 8192), ((1 << 21) + 65536, 3 << 19)]
+    ranges = [(dst.data_ptr() + o, src.data_ptr() + o, n) for o, n in spans]
+    _lib.check(_lib.lib.mb_flag_signal(C.c_void_p(words.ptr), 9, C.c_void_p(st.cuda_stream)), "signal")
+    ctx.pull_sm(ranges, (words.ptr, 9), [(words.ptr + 4, 21), (words.ptr + 8, 22)], words.ptr + 12, st)
+    assert _lib.status_fetch(st.cuda_stream) == 0
+    for o, n in spans:
+        assert torch.equal(dst[o:o + n], src[o:o + n])
+    touched = torch.zeros_like(src, dtype=torch.bool)
+    for o, n in spans:
+        touched[o:o + n] = True
+    assert int(dst[~touched].max().item()) == 0          # nothing outside the ranges was written
+    assert words.view(0, (4,), torch.int32).tolist() == [9, 21, 22, 0]
+    # a few CTAs only, and no wait flag
+    dst.zero_()
+    ctx.pull_sm(ranges[:1], None, [(words.ptr + 4, 23)], words.ptr + 12, st, ctas=3)
+    assert _lib.status_fetch(st.cuda_stream) == 0
+    assert torch.equal(dst[:spans[0][1]], src[:spans[0][1]]) and words.view(4, (1,), torch.int32).item() == 23
+    # the source never publishes: bounded wait, status 107, completion flag still raised so that nothing
+    # downstream hangs, counter back at zero
+    _lib.set_peer_wait_ms(200)
+    try:
+        ctx.pull_sm(ranges[:1], (words.ptr, 10), [(words.ptr + 4, 24)], words.ptr + 12, st)
+        assert _lib.status_fetch(st.cuda_stream) == 107
+    finally:
+        _lib.set_peer_wait_ms(_lib.PEER_WAIT_MS)
+    assert words.view(0, (4,), torch.int32).tolist() == [9, 24, 22, 0]
+    words.free()

@@ -150,15 +150,14 @@ __global__ void __maxnreg__(MB_FUSED_LAUNCH_REGS) attn_bwd_fused_kernel(const __
     mbar_init(&ctl->acc_full, 1);
     mbar_init(&ctl->drain, 1);
     ctl->abort_word = 0;
-#pragma unroll 1
-    for (int s = 0; s < MB_MAX_SEGMENTS; ++s) {
-      int f = 0, l = 0;
-      if (s < a.nseg) step_range(a, own0, s, &f, &l);
-      ctl->seg_first[s] = f;
-      ctl->seg_last[s] = l;
-    }
     fence_barrier_init();
     fence_proxy_async_smem();
+  }
+  if (tid < MB_MAX_SEGMENTS) {  // one thread per segment: its range of 64-row steps for this owner tile
+    int f = 0, l = 0;
+    if (tid < a.nseg) step_range(a, own0, tid, &f, &l);
+    ctl->seg_first[tid] = f;
+    ctl->seg_last[tid] = l;
   }
   if (warp == 8) {
     tmem_alloc(&ctl->tmem_base, 512);

@@ -115,15 +115,16 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ Fw
     mbar_init(&ctl->s_free, 4);
     mbar_init(&ctl->drain, 2);
     ctl->abort_word = 0;
-#pragma unroll 1
-    for (int i = 0; i < 2; ++i)
-#pragma unroll 1
-      for (int s = 0; s < MB_MAX_SEGMENTS; ++s)
-        ctl->n_tiles[i][s] = (s < a.nseg && ((J.seg_mask >> s) & 1u))
-                                 ? visible_tiles(q0 + i * kBM, J.Sq, J.q_off, a.causal, a.seg_sk[s], a.seg_koff[s])
-                                 : 0;
     fence_barrier_init();
     fence_proxy_async_smem();
+  }
+  // K/V tiles of each segment that each of the two query tiles takes part in: one thread per entry
+  // (computed by one thread this was ~4 000 cycles of a CTA's prologue at 32 segments)
+  if (tid < 2 * MB_MAX_SEGMENTS) {
+    const int i = tid / MB_MAX_SEGMENTS, s = tid % MB_MAX_SEGMENTS;
+    ctl->n_tiles[i][s] = (s < a.nseg && ((J.seg_mask >> s) & 1u))
+                             ? visible_tiles(q0 + i * kBM, J.Sq, J.q_off, a.causal, a.seg_sk[s], a.seg_koff[s])
+                             : 0;
   }
   if (warp == 8) {
     tmem_alloc(&ctl->tmem_base, 512);

@@ -1,0 +1,263 @@
+"""Host logic of the fused ring on CPU, for 2, 4 and 8 ranks: what every rank would enqueue.
+
+RingAttention.forward / backward are run for each rank of a job with the GPU taken away: the peer
+context records copies and flag operations instead of launching them, symmetric memory is a CPU
+tensor whose peer addresses are made-up bases, and the attention launches are replaced by recorders.
+The records of all ranks together must form a consistent protocol: every slot is pulled or released
+by every peer exactly once, copies stay inside the slot / staging they belong to, each arrival flag
+a kernel waits for is raised behind the copy that fills it (on the same stream), each half-shard of
+the balanced causal forward is computed by exactly one rank and lands in its owner's inbox, and the
+owner waits for exactly those result flags.
+"""
+import contextlib
+from unittest import mock
+
+import pytest
+import torch
+
+from mercury_artifact_b200 import ring
+
+BASE_SHIFT = 44
+
+
+class FakeStream:
+    def __init__(self, name):
+        self.name, self.cuda_stream = name, 0
+
+    def wait_stream(self, other):
+        pass
+
+    def wait_event(self, ev):
+        pass
+
+
+class FakeEvent:
+    def record(self, stream=None):
+        pass
+
+
+class FakeMonitor:
+    def poll(self):
+        pass
+
+    def post(self, stream):
+        pass
+
+
+class FakeCtx:
+    def __init__(self, rank, world):
+        self.rank, self.world, self.device = rank, world, torch.device("cpu")
+        self.comm_streams = [FakeStream("comm0"), FakeStream("comm1")]
+        self.comm_stream = self.comm_streams[0]
+        self.monitor = FakeMonitor()
+        self.launch_count = 0
+        self.ops = []   # (kind, stream name, payload)
+
+    def copy(self, dst, src, nbytes, stream):
+        self.ops.append(("copy", stream.name, (dst, src, nbytes)))
+
+    def signal(self, ptr, value, stream):
+        self.signal_many([(ptr, value)], stream)
+
+    def wait_flag(self, ptr, value, stream, timeout_ns=None):
+        self.wait_many([(ptr, value)], stream)
+
+    def signal_many(self, flags, stream):
+        self.launch_count += 1
+        self.ops.append(("signal", stream.name, list(flags)))
+
+    def wait_many(self, flags, stream, timeout_ns=None):
+        self.launch_count += 1
+        self.ops.append(("wait", stream.name, list(flags)))
+
+
+class FakeSym:
+    """Symmetric buffer stand-in: a local CPU tensor; rank p's copy 'lives' at (p + 1) << 44."""
+
+    def __init__(self, ctx, nbytes):
+        self.ctx, self.nbytes = ctx, ring._align(nbytes)
+        self._t = torch.zeros(self.nbytes, dtype=torch.uint8)
+        self.local = self
+
+    def bytes(self):
+        return self._t
+
+    def ptr(self, rank, offset=0):
+        if rank == self.ctx.rank:
+            return self._t.data_ptr() + offset
+        return ((rank + 1) << BASE_SHIFT) + offset
+
+    def where(self, ptr):
+        """(rank, offset) of an address inside some rank's copy of this buffer, else None."""
+        lo = self._t.data_ptr()
+        if lo <= ptr < lo + self.nbytes:
+            return self.ctx.rank, ptr - lo
+        r = (ptr >> BASE_SHIFT) - 1
+        off = ptr & ((1 << BASE_SHIFT) - 1)
+        if 0 <= r < self.ctx.world and off < self.nbytes:
+            return r, off
+        return None
+
+
+@contextlib.contextmanager
+def _no_gpu(launches):
+    main = FakeStream("main")
+
+    def fwd_multi(jobs, segs, scale, causal, b, hq, hkv, d, device):
+        launches.append(("fwd", jobs, segs))
+
+    def bwd_dq(q, dout, stats, kv_segs, scale, causal=False, q_off=0, dq=None, accumulate=False, hkv=None):
+        launches.append(("dq", kv_segs, q_off))
+
+    def bwd_dkv(k, v, q_segs, scale, causal=False, k_off=0, dk=None, dv=None, accumulate=False, hq=None):
+        launches.append(("dkv", q_segs, k_off))
+
+    def pre(dout, o, lse, workspace=None):
+        return ring.RowStats(workspace[0], workspace[1], dout.shape[1])
+
+    with mock.patch.object(ring, "SymmetricBuffer", FakeSym), mock.patch.object(ring, "attn_fwd_multi", fwd_multi), \
+            mock.patch.object(ring, "attn_bwd_dq", bwd_dq), mock.patch.object(ring, "attn_bwd_dkv", bwd_dkv), \
+            mock.patch.object(ring, "bwd_preprocess", pre), mock.patch.object(torch.cuda, "synchronize", lambda *a: None), \
+            mock.patch.object(torch.cuda, "current_stream", lambda *a: main), \
+            mock.patch.object(torch.cuda, "stream", lambda s: contextlib.nullcontext()), \
+            mock.patch.object(torch.cuda, "Event", FakeEvent):
+        yield
+
+
+def _run_rank(rank, world, mesh, causal, ring_divide, backward, B=1, L=256, H=2, hkv=2):
+    launches = []
+    ctx = FakeCtx(rank, world)
+    with _no_gpu(launches):
+        op = ring.RingAttention(mesh, B, L, H, hkv, 128, causal=causal, ctx=ctx, ring_divide=ring_divide,
+                                backward=backward)
+        q = torch.zeros(op.q_shape, dtype=torch.bfloat16)
+        kv = torch.zeros(op.kv_shape, dtype=torch.bfloat16)
+        o, lse = op.forward(q, kv)
+        fwd_ops, ctx.ops = ctx.ops, []
+        bwd_ops = []
+        if backward:
+            op.backward(torch.zeros_like(q), q, kv, o, lse)
+            bwd_ops = ctx.ops
+    return op, launches, fwd_ops, bwd_ops
+
+
+def _check_transfers(op, ops, epoch, need_done_from_all=True):
+    """Per-rank invariants of one epoch's transfer ops; returns {flag address: position} of raised flags."""
+    x, me, P = op._x, op.rank, op.world
+    sym = x.sym
+    stage_lo = x.staging.data_ptr()
+    raised = {}
+    done_raised = []
+    last_copy_on = {}
+    for pos, (kind, stream, payload) in enumerate(ops):
+        if kind == "copy":
+            dst, src, n = payload
+            w = sym.where(src)
+            assert w is not None and w[0] != me, "a pull reads another rank's symmetric memory"
+            origin, off = w
+            assert off + n <= x.slot_bytes, "a pull stays inside the owner's slot"
+            s_idx = x.stage_index(origin)
+            assert stage_lo + s_idx * x.slot_bytes + off == dst, "it lands at the same offset of that origin's staging slot"
+            assert stream == x.stream_of(origin).name, "all pulls from one origin share a stream"
+            last_copy_on[stream] = pos
+        elif kind == "signal":
+            for ptr, val in payload:
+                assert val == epoch
+                raised[ptr] = (pos, stream)
+                w = sym.where(ptr)
+                if w is not None and w[0] != me and x._flag_off + ring._DONE <= w[1] < x._flag_off + ring._RES:
+                    done_raised.append(w[0])
+                    assert (w[1] - x._flag_off - ring._DONE) // 4 == me, "done[me] on the owner"
+    if need_done_from_all:
+        assert sorted(done_raised) == [p for p in range(P) if p != me], "every peer's slot is pulled or released once"
+    return raised
+
+
+@pytest.mark.parametrize("world,mesh", [(2, (2,)), (4, (4,)), (8, (8,))])
+@pytest.mark.parametrize("ring_divide", [1, 2])
+def test_balanced_causal_forward_plan(world, mesh, ring_divide):
+    L, H = 256, 2
+    Lh = L // 2
+    computed = {}
+    waited = {}
+    for r in range(world):
+        op, launches, ops, _ = _run_rank(r, world, mesh, True, ring_divide, False)
+        assert op.balanced and len(launches) == 1
+        x = op._x
+        raised = _check_transfers(op, ops, 1)
+        _, jobs, segs = launches[0]
+        assert len(jobs) == 2 and len(segs) <= 32
+        # segments: the local shard first, then remote pieces; every remote piece waits for a flag that is
+        # raised behind a copy on the same stream
+        assert segs[0][2] == r * L and len(segs[0]) == 3
+        seen_keys = set()
+        for sg in segs:
+            k, v, k_off = sg[:3]
+            seen_keys.update(range(k_off, k_off + k.shape[1]))
+            if len(sg) > 3:
+                assert sg[3] in raised and sg[4] == 1
+        chunks = (2 * world - 1 - r, r)
+        # the keys this rank holds cover everything its heavier half-shard can see
+        assert seen_keys >= set(range(0, (chunks[0] + 1) * Lh))
+        for idx, (c, job) in enumerate(zip(chunks, jobs)):
+            owner, half = c // 2, c % 2
+            assert job["q_off"] == c * Lh and job["q"].shape[1] == Lh
+            where_o = x.sym.where(job["out_raw"][0])
+            assert where_o == (owner, x.slot_bytes + op._inbox_o + half * Lh * H * 128 * 2)
+            where_l = x.sym.where(job["lse_raw"][0])
+            assert where_l == (owner, x.slot_bytes + op._inbox_lse + half * Lh * 4)
+            flag, val, counter = job["done"]
+            assert x.sym.where(flag) == (owner, x._flag_off + ring._RES + 4 * half) and val == 1
+            assert (owner, half) not in computed, "each half-shard is computed once"
+            computed[(owner, half)] = r
+            if owner != r:
+                assert job["q_flag"][0] in raised, "pulled queries announce themselves"
+            else:
+                assert "q_flag" not in job
+        # the owner waits for both of its halves on the main stream, after the launch
+        w = [p for k, s, p in ops if k == "wait" and s == "main"]
+        assert w and sorted(x.sym.where(ptr)[1] for ptr, _ in w[-1]) == [x._flag_off + ring._RES, x._flag_off + ring._RES + 4]
+        waited[r] = True
+    assert sorted(computed) == [(o, h) for o in range(world) for h in (0, 1)]
+    # the re-assignment balances the work: every rank computes 2P half-shard units
+    for r in range(world):
+        mine = [oh for oh, who in computed.items() if who == r]
+        assert sorted(2 * o + h for o, h in mine) == sorted((r, 2 * world - 1 - r))
+        assert sum((2 * o + h) + 0.5 for o, h in mine) == 2 * world
+
+
+@pytest.mark.parametrize("world,mesh,causal", [(2, (2,), False), (8, (8,), False), (8, (4, 2), False), (8, (8,), True)])
+def test_plain_forward_and_backward_plan(world, mesh, causal):
+    """balance off: one job on the caller's own tensors; the backward pulls K/V from the ranks whose keys
+    it can see and (q, dout, statistics) from the ranks whose queries can see its keys."""
+    L = 256
+    for r in range(world):
+        launches = []
+        ctx = FakeCtx(r, world)
+        with _no_gpu(launches):
+            op = ring.RingAttention(mesh, 1, L, 2, 2, 128, causal=causal, ctx=ctx, balance_causal=False, backward=True,
+                                    ring_divide=2)
+            q = torch.zeros(op.q_shape, dtype=torch.bfloat16)
+            kv = torch.zeros(op.kv_shape, dtype=torch.bfloat16)
+            o, lse = op.forward(q, kv)
+            raised = _check_transfers(op, ctx.ops, 1)
+            ctx.ops = []
+            op.backward(torch.zeros_like(q), q, kv, o, lse)
+            raised_b = _check_transfers(op, ctx.ops, 2)
+        (_, jobs, segs), (_, kv_segs, q_off), (_, q_segs, k_off) = launches
+        assert len(jobs) == 1 and "done" not in jobs[0] and jobs[0]["q_off"] == r * L
+        order = ring.mesh.kv_origin_schedule(r, mesh)
+        want = [og for og in order if (not causal) or og <= r]
+        got = []
+        for sg in segs:
+            og = sg[2] // L
+            if og not in got:
+                got.append(og)
+            if len(sg) > 3:
+                assert sg[3] in raised
+        assert got == want, "segments follow the reference's consumption order"
+        assert q_off == r * L and k_off == r * L
+        assert sorted({s["off"] // L for s in kv_segs}) == sorted(og for og in range(world) if (not causal) or og <= r)
+        assert sorted({s["off"] // L for s in q_segs}) == sorted(og for og in range(world) if (not causal) or og >= r)
+        for s in kv_segs[1:] + q_segs[1:]:
+            assert s["flag"] in raised_b and s["flag_value"] == 2

@@ -36,7 +36,7 @@ extern "C" {
 #define MB_E_TOO_LARGE (-6)   /* problem exceeds the fixed scratch of an allocation-free entry point */
 
 #define MB_MAX_SEGMENTS 32 /* K/V (or stream) shards per launch: 8 ranks x ring_divide 4, or a 32-way mesh */
-#define MB_MAX_JOBS 4      /* query shards per mb_attn_fwd_multi launch */
+#define MB_MAX_JOBS 16      /* query shards per mb_attn_fwd_multi launch */
 
 /* One sequence shard of K and V: [batch, sk, hkv, head_dim] views. */
 typedef struct mb_kv_segment {
@@ -101,6 +101,23 @@ typedef struct mb_fwd_job {
   int32_t done_value;
   int32_t* done_flag;
   int32_t* done_counter;
+  /* Optional carried state.  A job with state_out != 0 does not write o / lse (they may be NULL) but
+   * stores the online-softmax state of its rows: unnormalised output rows in state_o
+   * [batch, hq, sq, head_dim] fp32 (16-byte aligned) and (reference maximum in raw score units, running
+   * sum) pairs in state_ml [batch, hq, sq, 2] fp32.  A job with state_in != 0 starts from that state
+   * instead of the empty one (same q rows, same buffers; in place is fine).  A chain of such jobs, one
+   * per K/V shard in arrival order, gives the same bits as one job over all the shards, and lets the
+   * CTAs of a launch be ordered shard by shard, so that none holds an SM while it waits for a shard
+   * that is still in flight.  If the jobs of a chain are in ONE launch, give them chain: int32 words
+   * [batch, hq, ceil(sq / 256)] on this GPU; a job with state_out stores chain_set to its CTA's word
+   * after its state (release), a job with state_in waits (bounded, status 109) until the word is
+   * >= chain_wait.  The continuing job must come later in job[] (CTAs are dispatched in job order).
+   * With chain == NULL the jobs must be in different launches of one stream. */
+  float* state_o;
+  float* state_ml;
+  int32_t state_in, state_out;
+  int32_t* chain;
+  int32_t chain_wait, chain_set;
 } mb_fwd_job;
 
 typedef struct mb_attn_fwd_multi_args {

@@ -10,7 +10,7 @@ import ctypes as C
 from pathlib import Path
 
 MB_MAX_SEGMENTS = 32
-MB_MAX_JOBS = 4
+MB_MAX_JOBS = 16
 
 MB_SUCCESS = 0
 ERROR_NAMES = {
@@ -99,6 +99,13 @@ class FwdJob(C.Structure):
         ("done_value", C.c_int32),
         ("done_flag", C.c_void_p),
         ("done_counter", C.c_void_p),
+        ("state_o", C.c_void_p),
+        ("state_ml", C.c_void_p),
+        ("state_in", C.c_int32),
+        ("state_out", C.c_int32),
+        ("chain", C.c_void_p),
+        ("chain_wait", C.c_int32),
+        ("chain_set", C.c_int32),
     ]
 
 

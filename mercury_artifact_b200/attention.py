@@ -121,7 +121,13 @@ def attn_fwd_multi(jobs: Sequence[dict], segments: Sequence[tuple], softmax_scal
       q_flag       optional (address, value): arrival flag of the query shard
       done         optional (flag address, value, counter address): completion flag raised by the kernel
       seg_mask     optional bit mask of the segments the job attends to (default: all)
-    segments: as in attn_fwd_segments.  CTAs of job 0 are scheduled first."""
+      state        optional (state_o, state_ml): fp32 tensors [batch, hq, sq, d] and [batch, hq, sq, 2] that
+                   carry the online-softmax state between jobs over the same query rows
+      state_in / state_out   start from that state / store it instead of the result (out_raw and lse_raw
+                   may then be omitted)
+      chain        optional (address of int32 words [batch, hq, ceil(sq/256)], wait value, set value): lets
+                   the job that continues a state be part of the same launch (later in `jobs`)
+    segments: as in attn_fwd_segments.  CTAs are dispatched job by job, job 0 first."""
     if not 1 <= len(jobs) <= _lib.MB_MAX_JOBS:
         raise ValueError(f"1..{_lib.MB_MAX_JOBS} jobs per launch")
     if len(segments) > _lib.MB_MAX_SEGMENTS:
@@ -140,8 +146,23 @@ def attn_fwd_multi(jobs: Sequence[dict], segments: Sequence[tuple], softmax_scal
         j = a.job[i]
         j.q = q.data_ptr()
         j.q_stride_b, j.q_stride_s, j.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
-        j.o, j.o_stride_b, j.o_stride_s, j.o_stride_h = jb["out_raw"]
-        j.lse, j.lse_stride_b, j.lse_stride_h = jb["lse_raw"]
+        if jb.get("out_raw") is not None:
+            j.o, j.o_stride_b, j.o_stride_s, j.o_stride_h = jb["out_raw"]
+            j.lse, j.lse_stride_b, j.lse_stride_h = jb["lse_raw"]
+        elif not jb.get("state_out"):
+            raise ValueError("a job needs out_raw / lse_raw unless it stores its state")
+        if jb.get("state") is not None:
+            so, sml = jb["state"]
+            if so.dtype != torch.float32 or sml.dtype != torch.float32 or not so.is_contiguous() or \
+                    not sml.is_contiguous() or tuple(so.shape) != (batch, hq, q.shape[1], head_dim) or \
+                    tuple(sml.shape) != (batch, hq, q.shape[1], 2):
+                raise ValueError("state must be contiguous fp32 [batch, hq, sq, d] and [batch, hq, sq, 2]")
+            j.state_o, j.state_ml = so.data_ptr(), sml.data_ptr()
+            j.state_in, j.state_out = int(bool(jb.get("state_in"))), int(bool(jb.get("state_out")))
+            if jb.get("chain"):
+                j.chain, j.chain_wait, j.chain_set = jb["chain"][0], int(jb["chain"][1]), int(jb["chain"][2])
+        elif jb.get("state_in") or jb.get("state_out"):
+            raise ValueError("state_in / state_out need the state tensors")
         j.sq, j.q_off = q.shape[1], int(jb.get("q_off", 0))
         j.seg_mask = int(jb.get("seg_mask", 0))
         if jb.get("q_flag"):

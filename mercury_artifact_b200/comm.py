@@ -122,8 +122,10 @@ class PeerContext:
         # flag kernels would sit behind the pending CTAs of a running attention kernel that is itself
         # waiting for them.
         self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1)
-        # further transfer streams: copies queued on different streams can use different copy engines
-        n_extra = max(0, int(os.environ.get("MB_COPY_STREAMS", "2")) - 1)
+        # Further transfer streams (MB_COPY_STREAMS, default 1).  One stream is the measured optimum for the
+        # ring forward: transfers are queued in the order the kernel consumes them, one copy already runs at
+        # the NVLink rate, and a second stream only delays the shard that is needed first.
+        n_extra = max(0, int(os.environ.get("MB_COPY_STREAMS", "1")) - 1)
         self.comm_streams = [self.comm_stream] + [torch.cuda.Stream(device=self.device, priority=-1)
                                                   for _ in range(n_extra)]
         self._channels: Dict[Tuple[int, int], "_Channel"] = {}

@@ -35,6 +35,8 @@
 // arrival flag for its queries (they may still be in flight from another GPU) and a completion flag,
 // which the job's last CTA raises with a release store at system scope once every row of the job has
 // been stored -- the rows, and the flag, may live in another GPU's memory.
+#include <climits>
+
 #include "attn_fwd_common.cuh"
 
 namespace mb {
@@ -91,14 +93,20 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ Fw
     while (jid + 1 < a.njobs && (int)blockIdx.x >= a.job[jid + 1].x_begin) ++jid;
     ctl->jid = jid;
     ctl->job = a.job[jid];
+    // CTAs are dispatched in grid order: job by job, inside a job batch entry by batch entry and head by
+    // head (the CTAs running at one time share a few heads' K/V through L2), heavier query rows first.
+    const int local = (int)blockIdx.x - a.job[jid].x_begin;
+    const int np = a.job[jid].n_pairs;
+    const int pidx = local % np;
+    ctl->pair = a.causal ? (np - 1 - pidx) : pidx;
+    ctl->h = (local / np) % a.Hq;
+    ctl->b = (local / np) / a.Hq;
   }
   __syncthreads();
   const FwdJob& J = ctl->job;
-  const int pair = a.causal ? (J.n_pairs - 1 - ((int)blockIdx.x - J.x_begin)) : ((int)blockIdx.x - J.x_begin);
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
-  const int hkv = h / a.group;
-  const int q0 = pair * 2 * kBM;
+  // (pair, head, batch entry) stay in shared memory: the roles read them where they need them, so that
+  // they occupy no registers across the softmax loop
+  const int q0 = ctl->pair * 2 * kBM;
 
   if (tid == 0) {
     mbar_init(&ctl->q_full, 1);
@@ -161,12 +169,13 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ Fw
         mbar_expect_tx(&ctl->q_full, (act0 + act1) * kTileBytes);
         for (int i = 0; i < 2; ++i) {
           if (q0 + i * kBM < J.Sq) {
-            tma_load_4d(sQ + i * kTileBytes, qmap, &ctl->q_full, 0, h, q0 + i * kBM, b);
-            tma_load_4d(sQ + i * kTileBytes + kHalfBytes, qmap, &ctl->q_full, 64, h, q0 + i * kBM, b);
+            tma_load_4d(sQ + i * kTileBytes, qmap, &ctl->q_full, 0, ctl->h, q0 + i * kBM, ctl->b);
+            tma_load_4d(sQ + i * kTileBytes + kHalfBytes, qmap, &ctl->q_full, 64, ctl->h, q0 + i * kBM, ctl->b);
           }
         }
       }
       int n = 0;
+      const int b_ = ctl->b, hkv = ctl->h / a.group;
       // One K or V tile into the next stage of the ring.
       auto load_tile = [&](int which, const TileIter& it) {
         if (which == 0 && it.jt == 0 && a.seg_flag[it.s] != nullptr) {
@@ -186,8 +195,8 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ Fw
         const CUtensorMap* map = which ? &maps.v[it.s] : &maps.k[it.s];
         uint8_t* dst = sKV + stage * kTileBytes;
         mbar_expect_tx(&ctl->kv_full[stage], kTileBytes);
-        tma_load_4d(dst, map, &ctl->kv_full[stage], 0, hkv, it.jt * kBN, b);
-        tma_load_4d(dst + kHalfBytes, map, &ctl->kv_full[stage], 64, hkv, it.jt * kBN, b);
+        tma_load_4d(dst, map, &ctl->kv_full[stage], 0, hkv, it.jt * kBN, b_);
+        tma_load_4d(dst + kHalfBytes, map, &ctl->kv_full[stage], 64, hkv, it.jt * kBN, b_);
         ++n;
       };
       TileIter nxt = iter_first(ctl, a.nseg);
@@ -280,7 +289,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ Fw
                 ok = mbar_wait_warp(&ctl->p_full[i][0], cnt & 1, abort_word, MB_ERR_TIMEOUT_P, a.wait_cycles);
                 if (!ok) break;
                 tc_fence_after();
-                issue_pv_half(tOi, tPi, v_desc, idesc_pv, cnt == 0 ? 0u : 1u);
+                issue_pv_half(tOi, tPi, v_desc, idesc_pv, (cnt == 0 && !J.st_in) ? 0u : 1u);
                 ok = mbar_wait_warp(&ctl->p_full[i][1], cnt & 1, abort_word, MB_ERR_TIMEOUT_P, a.wait_cycles);
                 if (!ok) break;
                 tc_fence_after();
@@ -322,6 +331,42 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ Fw
     float l = 0.f;            // running sum of exp2
     int cnt = 0;
     bool ok = true;
+    if (J.st_in && q0 + i * kBM < J.Sq) {
+      const int qrow = qpos - J.q_off;  // row inside the job's Q
+      const long long st_row = ((long long)ctl->b * a.Hq + ctl->h) * J.Sq + qrow;
+      // Continue where an earlier job stopped: its unnormalised rows go back into tensor memory, its
+      // maximum and sum into registers.  With chain words that job may be part of this launch (a CTA
+      // with a lower index); its release store is acquired here.
+      if (J.chain != nullptr) {
+        if (lane == 0)
+          ok = flag_wait_ge(J.chain + ((long long)ctl->b * a.Hq + ctl->h) * J.n_pairs + ctl->pair, J.chain_wait, abort_word,
+                            MB_ERR_TIMEOUT_SEGMENT, a.peer_wait_cycles);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+      if (ok) {
+        const bool valid = qrow < J.Sq;
+        const float4* src = reinterpret_cast<const float4*>(J.st_o + st_row * kD);
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t orow[32];
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const float4 w = valid ? src[c * 8 + v] : make_float4(0.f, 0.f, 0.f, 0.f);
+            orow[v * 4 + 0] = __float_as_uint(w.x);
+            orow[v * 4 + 1] = __float_as_uint(w.y);
+            orow[v * 4 + 2] = __float_as_uint(w.z);
+            orow[v * 4 + 3] = __float_as_uint(w.w);
+          }
+          tmem_st32(tOi + c * 32, orow);
+        }
+        tmem_wait_st();
+        if (valid) {
+          const float2 ml = *reinterpret_cast<const float2*>(J.st_ml + st_row * 2);
+          m_ref = ml.x;
+          l = ml.y;
+        }
+      }
+    }
 
     for (int s = 0; s < a.nseg && ok; ++s) {
       const int nt = ctl->n_tiles[i][s];
@@ -365,14 +410,16 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ Fw
         }
         const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 
-        if (cnt == 0) {
-          m_ref = m_tile;
+        if (cnt == 0 && __all_sync(0xffffffffu, m_ref == -INFINITY)) {
+          m_ref = m_tile;  // nothing accumulated yet (a carried state of rows without keys is all zero)
         } else {
           // The previous P.V product of this query tile must be complete before its probabilities
-          // are overwritten, and before O is rescaled.
-          ok = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O, a.wait_cycles);
-          if (!ok) break;
-          tc_fence_after();
+          // are overwritten, and before O is rescaled (a carried state is already in place).
+          if (cnt > 0) {
+            ok = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O, a.wait_cycles);
+            if (!ok) break;
+            tc_fence_after();
+          }
           const float m_new = fmaxf(m_ref, m_tile);
           const bool need = (m_new - m_ref) * a.scale_log2 > kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
@@ -434,47 +481,79 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ Fw
       }
     }
 
-    // epilogue: O / l -> bf16, LSE = ln(sum exp(scale * s)).  Tiles whose rows all lie past Sq skip it.
-    const int qrow = qpos - J.q_off;
+    // epilogue.  Final job: O / l -> bf16, LSE = ln(sum exp(scale * s)).  Job that hands its state on:
+    // the unnormalised rows, the maximum and the sum, as they are.  Tiles whose rows all lie past Sq skip it.
+    const int qrow = qpos - J.q_off;  // row inside the job's Q
     if (ok && qrow - row < J.Sq) {
-      bool have = cnt > 0;
-      if (have) {
-        have = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O, a.wait_cycles);
-        ok = have;
-      }
+      const long long st_row = ((long long)ctl->b * a.Hq + ctl->h) * J.Sq + qrow;
+      const bool have_acc = cnt > 0 || J.st_in;   // tensor memory holds this tile's rows
+      if (cnt > 0) ok = mbar_wait_warp(&ctl->o_full[i], (cnt - 1) & 1, abort_word, MB_ERR_TIMEOUT_O, a.wait_cycles);
       if (ok) {
         const bool store = qrow < J.Sq;
-        const float inv_l = (have && l > 0.f) ? 1.f / l : 0.f;
-        __nv_bfloat16* optr = J.o + (long long)b * J.o_sb + (long long)qrow * J.o_ss + (long long)h * J.o_sh;
-        if (have) tc_fence_after();
+        if (have_acc) tc_fence_after();
+        if (J.st_out) {
+          float4* dst = reinterpret_cast<float4*>(J.st_o + st_row * kD);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t orow[32];
-          if (have) {
-            tmem_ld32(tOi + c * 32, orow);
-            tmem_wait_ld();
-          } else {
+          for (int c = 0; c < 4; ++c) {
+            uint32_t orow[32];
+            if (have_acc) {
+              tmem_ld32(tOi + c * 32, orow);
+              tmem_wait_ld();
+            } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) orow[e] = 0u;
-          }
-          if (store) {
-            uint4* dst = reinterpret_cast<uint4*>(optr + c * 32);
+              for (int e = 0; e < 32; ++e) orow[e] = 0u;
+            }
+            if (store) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 w;
-              w.x = pack_bf16x2(__uint_as_float(orow[v * 8 + 0]) * inv_l, __uint_as_float(orow[v * 8 + 1]) * inv_l);
-              w.y = pack_bf16x2(__uint_as_float(orow[v * 8 + 2]) * inv_l, __uint_as_float(orow[v * 8 + 3]) * inv_l);
-              w.z = pack_bf16x2(__uint_as_float(orow[v * 8 + 4]) * inv_l, __uint_as_float(orow[v * 8 + 5]) * inv_l);
-              w.w = pack_bf16x2(__uint_as_float(orow[v * 8 + 6]) * inv_l, __uint_as_float(orow[v * 8 + 7]) * inv_l);
-              dst[v] = w;
+              for (int v = 0; v < 8; ++v)
+                dst[c * 8 + v] = make_float4(__uint_as_float(orow[v * 4 + 0]), __uint_as_float(orow[v * 4 + 1]),
+                                             __uint_as_float(orow[v * 4 + 2]), __uint_as_float(orow[v * 4 + 3]));
             }
           }
-        }
-        if (store) {
-          const float lse = (have && l > 0.f) ? (m_ref * a.scale + __logf(l)) : -INFINITY;
-          J.lse[(long long)b * J.lse_sb + (long long)h * J.lse_sh + qrow] = lse;
+          if (store) *reinterpret_cast<float2*>(J.st_ml + st_row * 2) = make_float2(m_ref, l);
+        } else {
+          const float inv_l = (have_acc && l > 0.f) ? 1.f / l : 0.f;
+          __nv_bfloat16* optr = J.o + (long long)ctl->b * J.o_sb + (long long)qrow * J.o_ss + (long long)ctl->h * J.o_sh;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t orow[32];
+            if (have_acc) {
+              tmem_ld32(tOi + c * 32, orow);
+              tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) orow[e] = 0u;
+            }
+            if (store) {
+              uint4* dst = reinterpret_cast<uint4*>(optr + c * 32);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 w;
+                w.x = pack_bf16x2(__uint_as_float(orow[v * 8 + 0]) * inv_l, __uint_as_float(orow[v * 8 + 1]) * inv_l);
+                w.y = pack_bf16x2(__uint_as_float(orow[v * 8 + 2]) * inv_l, __uint_as_float(orow[v * 8 + 3]) * inv_l);
+                w.z = pack_bf16x2(__uint_as_float(orow[v * 8 + 4]) * inv_l, __uint_as_float(orow[v * 8 + 5]) * inv_l);
+                w.w = pack_bf16x2(__uint_as_float(orow[v * 8 + 6]) * inv_l, __uint_as_float(orow[v * 8 + 7]) * inv_l);
+                dst[v] = w;
+              }
+            }
+          }
+          if (store) {
+            const float lse = (have_acc && l > 0.f) ? (m_ref * a.scale + __logf(l)) : -INFINITY;
+            J.lse[(long long)ctl->b * J.lse_sb + (long long)ctl->h * J.lse_sh + qrow] = lse;
+          }
         }
       }
+    }
+    if (J.st_out && J.chain != nullptr) {
+      // Publish the state to the job that continues it: every softmax thread's stores, then one release
+      // store of the chain word.  (A CTA that gave up publishes too, so that nothing downstream waits out
+      // its budget; the status word tells the host.)
+      __threadfence();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (warp == 0 && lane == 0)
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(J.chain + ((long long)ctl->b * a.Hq + ctl->h) * J.n_pairs + ctl->pair),
+                     "r"(J.chain_set)
+                     : "memory");
     }
   }
 
@@ -572,7 +651,10 @@ int launch_attn_fwd_multi(const mb_attn_fwd_multi_args* x, cudaStream_t stream) 
       if (g.done_flag != nullptr) return MB_E_INVALID;
       continue;
     }
-    if (g.q == nullptr || g.o == nullptr || g.lse == nullptr) return MB_E_INVALID;
+    if (g.q == nullptr) return MB_E_INVALID;
+    if (!g.state_out && (g.o == nullptr || g.lse == nullptr)) return MB_E_INVALID;
+    if ((g.state_in || g.state_out) && (g.state_o == nullptr || g.state_ml == nullptr)) return MB_E_INVALID;
+    if ((reinterpret_cast<uintptr_t>(g.state_o) & 15u) || (reinterpret_cast<uintptr_t>(g.state_ml) & 7u)) return MB_E_INVALID;
     if (g.done_flag != nullptr && g.done_counter == nullptr) return MB_E_INVALID;
     if (make_tile_map(&maps.q[njobs], g.q, kD, x->hq, g.sq, x->batch, g.q_stride_b, g.q_stride_s, g.q_stride_h))
       return MB_E_TENSORMAP;
@@ -598,7 +680,15 @@ int launch_attn_fwd_multi(const mb_attn_fwd_multi_args* x, cudaStream_t stream) 
     J.done_value = g.done_value;
     J.done_counter = g.done_counter;
     J.n_ctas = J.n_pairs * x->hq * x->batch;
-    x_total += J.n_pairs;
+    J.st_o = g.state_o;
+    J.st_ml = g.state_ml;
+    J.st_in = g.state_in ? 1 : 0;
+    J.st_out = g.state_out ? 1 : 0;
+    J.chain = g.chain;
+    J.chain_wait = g.chain_wait;
+    J.chain_set = g.chain_set;
+    if (x_total > INT_MAX - J.n_ctas) return MB_E_INVALID;
+    x_total += J.n_ctas;
     ++njobs;
   }
   if (njobs == 0) return MB_SUCCESS;
@@ -612,12 +702,12 @@ int launch_attn_fwd_multi(const mb_attn_fwd_multi_args* x, cudaStream_t stream) 
   a.peer_wait_cycles = peer_wait_cycles();
   bool has_flags = false;
   for (int s = 0; s < nseg; ++s) has_flags |= a.seg_flag[s] != nullptr;
-  for (int j = 0; j < njobs; ++j) has_flags |= a.job[j].q_flag != nullptr;
+  for (int j = 0; j < njobs; ++j) has_flags |= a.job[j].q_flag != nullptr || (a.job[j].chain != nullptr && a.job[j].st_in);
   a.wait_cycles = kWaitCycleLimit + (has_flags ? a.peer_wait_cycles : 0);
   a.status = x->status ? x->status : default_status_word();
   if (a.status == nullptr) return MB_E_CUDA;
 
-  dim3 grid(x_total, x->hq, x->batch);
+  dim3 grid(x_total, 1, 1);
   attn_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(maps, a);
   return cuda_ok(cudaGetLastError(), "launch attn_fwd_kernel") ? MB_SUCCESS : MB_E_CUDA;
 }

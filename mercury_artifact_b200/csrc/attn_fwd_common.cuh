@@ -34,13 +34,20 @@ struct FwdJob {
   long long lse_sb, lse_sh;    // element strides of lse
   int Sq, q_off;
   unsigned seg_mask;           // segments this job attends to
-  int x_begin, n_pairs;        // its range of blockIdx.x
+  int x_begin, n_pairs;        // first CTA of the job in the (one-dimensional) grid; query tile pairs
   const int* q_flag;           // arrival flag of the query shard (nullptr: in place)
   int q_flag_value;
   int done_value;              // stored to *done_flag by the job's last CTA
   int* done_flag;
   int* done_counter;
   int n_ctas;
+  // Carried online-softmax state (see mb_fwd_job): unnormalised rows [B, Hq, Sq, D] and (maximum, sum)
+  // pairs [B, Hq, Sq, 2], both fp32; chain words [B, Hq, n_pairs].
+  float* st_o;
+  float* st_ml;
+  int* chain;
+  int chain_wait, chain_set;
+  int st_in, st_out;
 };
 
 struct FwdArgs {
@@ -72,6 +79,7 @@ struct FwdSmem {
   uint32_t tmem_base;
   int abort_word;
   int jid;
+  int pair, h, b;  // this CTA's query tile pair, head and batch entry
   int n_tiles[2][MB_MAX_SEGMENTS];  // K/V tiles of each segment that query tile i takes part in
   FwdJob job;                       // this CTA's job (a copy: read with fixed offsets, no registers held)
 };

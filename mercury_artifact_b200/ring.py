@@ -209,6 +209,7 @@ class RingAttention:
         self.launches_per_forward = 1
         self.launches_per_backward = 3
         self._x: Optional[_Exchange] = None
+        self._state: Optional[List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]] = None
         self._monitor = getattr(self.ctx, "monitor", None) or _lib.StatusMonitor()
         # Causal attention over contiguous shards gives rank r (r + 1/2) blocks of forward work.  With
         # balancing, the forward re-assigns query half-shards so that every rank computes the same
@@ -339,6 +340,64 @@ class RingAttention:
         row_b = self.hq * self.head_dim * 2
         return [(base_off + (b * self.seq_local + r0) * row_b, (r1 - r0) * row_b) for b in range(self.batch)]
 
+    def _shard_major_jobs(self, chunks: List[dict], order: Sequence[int], shard_bits: dict, epoch: int) -> List[dict]:
+        """Cut every query chunk's work into one job per K/V shard, in the order the shards arrive, and list
+        the jobs shard by shard: CTAs are dispatched in job order, so the SMs first do everything that
+        needs only the local shard, then everything that needs the first pulled shard, and so on -- no CTA
+        holds an SM while it waits for a shard that is still in flight (a CTA that walks through all the
+        shards itself does: the first wave consumes shards faster than NVLink delivers them).  The jobs
+        of a chunk hand the online-softmax state on through fp32 scratch and chain words; the last one
+        writes the result.  More shards than job slots: consecutive shards share a job."""
+        L = self.seq_local
+        per_chunk = max(1, _lib.MB_MAX_JOBS // len(chunks))
+        group = -(-len(order) // per_chunk)
+        steps = [list(order[i:i + group]) for i in range(0, len(order), group)]
+        plan: List[Tuple[int, int, int]] = []             # (step, chunk index, segment mask)
+        for t, shards in enumerate(steps):
+            for ci, ch in enumerate(chunks):
+                rows = ch["q"].shape[1]
+                mask = 0
+                for og in shards:
+                    if (not self.causal) or og * L <= ch["q_off"] + rows - 1:     # its first key is visible
+                        mask |= shard_bits[og]
+                if mask:
+                    plan.append((t, ci, mask))
+        count = [sum(1 for _, ci, _ in plan if ci == i) for i in range(len(chunks))]
+        if self._state is None:
+            dev = chunks[0]["q"].device
+            self._state = []
+            for ch in chunks:
+                rows = ch["q"].shape[1]
+                self._state.append((torch.empty((self.batch, self.hq, rows, self.head_dim), dtype=torch.float32, device=dev),
+                                    torch.empty((self.batch, self.hq, rows, 2), dtype=torch.float32, device=dev),
+                                    torch.zeros((self.batch, self.hq, (rows + 255) // 256), dtype=torch.int32, device=dev)))
+        base = (epoch % (1 << 24)) * 64                   # chain values only grow; restart with cleared words
+        if base == 0:
+            for _, _, chain in self._state:
+                chain.zero_()
+        seen = [0] * len(chunks)
+        out: List[dict] = []
+        for t, ci, mask in plan:
+            ch = chunks[ci]
+            p, n = seen[ci], count[ci]
+            seen[ci] += 1
+            jb = {"q": ch["q"], "q_off": ch["q_off"], "seg_mask": mask}
+            if "q_flag" in ch:
+                jb["q_flag"] = ch["q_flag"]
+            if n > 1:
+                so, sml, chain = self._state[ci]
+                jb.update(state=(so, sml), state_in=p > 0, state_out=p < n - 1,
+                          chain=(chain.data_ptr(), base + p, base + p + 1))
+            if p == n - 1:
+                jb["out_raw"], jb["lse_raw"] = ch["out_raw"], ch["lse_raw"]
+                if "done" in ch:
+                    jb["done"] = ch["done"]
+            out.append(jb)
+        for ci, ch in enumerate(chunks):
+            if count[ci] == 0:                            # sees no key at all: one job that writes zeros / -inf
+                out.append({k: v for k, v in ch.items()} | {"seg_mask": 0})
+        return out
+
     # ------------------------------------------------------------------ forward
     def forward(self, q: torch.Tensor, kv: torch.Tensor, o: Optional[torch.Tensor] = None,
                 lse: Optional[torch.Tensor] = None, softmax_scale: Optional[float] = None
@@ -406,31 +465,49 @@ class RingAttention:
                     q_pulls.append((owner, self._q_rows_ranges(self._off_q, half * Lh, (half + 1) * Lh), idx))
                 jobs.append(job)
             max_shard = (2 * P - 1 - me) // 2       # K/V shards 0..max_shard are visible to some query here
-            needed = [og for og in ((me - t) % P for t in range(1, P)) if og <= max_shard]
+            # Pull order (me+1, me+2, ...): every rank starts at another origin, and the ranks near P-1 --
+            # which see nothing of their own shard and whose work is almost all on the low shards -- get
+            # shards 0, 1, ... first (MB_PULL_ORDER=down selects the ring order me-1, me-2, ...).
+            sign = -1 if os.environ.get("MB_PULL_ORDER", "up") == "down" else 1
+            needed = [og for og in ((me + sign * t) % P for t in range(1, P)) if og <= max_shard]
         else:
             jobs.append({"q": q, "q_off": me * L,
                          "out_raw": (o.data_ptr(), o.stride(0), o.stride(1), o.stride(2)),
                          "lse_raw": (lse.data_ptr(), lse.stride(0), lse.stride(1))})
             needed = [og for og in self.order[1:] if self._sees_keys_of(og)]
 
-        # ---- transfers: owners nobody here reads are released at once; query half-shards go first on
-        # their origin's stream, then the K/V shards in consumption order, piece by piece
+        # ---- transfers: owners nobody here reads are released at once.  Order: the first job's queries, the
+        # first K/V shard, the other queries (their job comes after a few waves of the first one), then the
+        # remaining K/V shards in consumption order, piece by piece.  The last pull from an owner also tells
+        # it that this rank is done with its slot.
         q_owners = {owner for owner, _, _ in q_pulls}
         x.release([og for og in range(P) if og != me and og not in needed and og not in q_owners])
-        for owner, ranges, idx in q_pulls:
-            x.pull(owner, ranges, raise_after=[(x.aux_ptr(idx), e)], last=owner not in needed)
         d, c = self.ring_divide, L // self.ring_divide
         segs: List[tuple] = [(kv[0], kv[1], me * L)]
+        shard_bits = {me: 1}                                  # origin -> bit mask of its segments
+        kv_pulls: List[List[tuple]] = []                      # per needed shard: its pieces' pull arguments
         for og in needed:
             rkv = self._stage_views(og)[0]
+            first = len(segs)
+            pieces = []
             for j in range(d):
                 flag = x.piece_flag_ptr(og, j)
-                ranges = self._kv_piece_ranges(j) if d > 1 else [(self._off_kv, self._kv_b)]
-                x.pull(og, ranges, raise_after=[(flag, e)], last=(j == d - 1))
+                pieces.append((og, self._kv_piece_ranges(j) if d > 1 else [(self._off_kv, self._kv_b)], [(flag, e)]))
                 rows = slice(j * c, (j + 1) * c)
                 segs.append((rkv[0][:, rows], rkv[1][:, rows], og * L + j * c, flag, e))
+            kv_pulls.append(pieces)
+            shard_bits[og] = ((1 << d) - 1) << first
+        q_ops = [(owner, ranges, [(x.aux_ptr(idx), e)]) for owner, ranges, idx in q_pulls]
+        first_q = [op_ for op_, (_, _, idx) in zip(q_ops, q_pulls) if idx == 0]
+        ops = first_q + (kv_pulls[0] if kv_pulls else []) + [op_ for op_ in q_ops if op_ not in first_q]
+        for pieces in kv_pulls[1:]:
+            ops += pieces
+        last_of = {origin: n for n, (origin, _, _) in enumerate(ops)}
+        for n, (origin, ranges, flags) in enumerate(ops):
+            x.pull(origin, ranges, raise_after=flags, last=last_of[origin] == n)
 
-        attn_fwd_multi(jobs, segs, softmax_scale, self.causal, B, Hq, self.hkv, D, q.device)
+        attn_fwd_multi(self._shard_major_jobs(jobs, [me] + needed, shard_bits, e), segs, softmax_scale, self.causal,
+                       B, Hq, self.hkv, D, q.device)
 
         if self.balanced:
             # my own rows: wait for whoever computed them (one launch for both halves)
@@ -635,14 +712,17 @@ class RingAttention:
         and staging instead of the rotating double buffer): `symmetric` is mapped by every peer -- the
         slot [kv | q (| dout | row statistics with backward=True)] plus the flag region; `staging`
         holds pulled shards (world - 1 slots); `inbox` is the symmetric o / lse that results computed
-        on other ranks are written into.  `backward` defaults to what the object was built with."""
+        on other ranks are written into; `state` is the fp32 online-softmax state (and chain words) that
+        the forward's per-shard jobs hand on.  `backward` defaults to what the object was built with."""
         if self.world == 1:
-            return {"symmetric": 0, "staging": 0, "inbox": 0}
+            return {"symmetric": 0, "staging": 0, "inbox": 0, "state": 0}
         if backward is not None and bool(backward) != self.with_backward:
             raise ValueError("the slot layout is fixed at construction: pass backward= to RingAttention")
         slot = _align(self._slot_bytes, 1024)
         inbox = _align(self._inbox_bytes, 1024)
-        return {"symmetric": slot + _FLAG_REGION, "staging": (self.world - 1) * slot, "inbox": inbox}
+        chunk_rows = [self.seq_local // 2] * 2 if self.balanced else [self.seq_local]
+        state = sum(self.batch * self.hq * (r * (self.head_dim + 2) + (r + 255) // 256) * 4 for r in chunk_rows)
+        return {"symmetric": slot + _FLAG_REGION, "staging": (self.world - 1) * slot, "inbox": inbox, "state": state}
 
     def check(self) -> None:
         """Synchronise and raise if a device-side wait timed out."""

@@ -223,3 +223,103 @@ def test_full_size_properties_config2():
     assert (out - o1[:, h:].float()).abs().max().item() <= O_TOL
     assert (lse.squeeze(-1).transpose(1, 2) - l1[:, :, h:]).abs().max().item() <= LSE_TOL
     assert torch.equal(pa[:, :h], o1[:, :h])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("one_launch", [False, True])
+def test_carried_state_chain_equals_one_job_bitwise(causal, one_launch):
+    """A query shard processed as a chain of jobs, one per K/V shard, each continuing the online-softmax
+    state the previous one stored (mb_fwd_job.state_*), gives the bits of one job over all the shards:
+    as separate launches of one stream, and as ONE launch whose jobs hand over through chain words.
+    Ragged sizes, GQA, a shard that the early query rows cannot see (their state passes through), and a
+    first shard that late-positioned keys make invisible to every row of some tiles."""
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200 import _lib
+    from mercury_artifact_b200.attention import attn_fwd_multi
+    from tests.helpers import seeded_qkv
+
+    dev = torch.device("cuda", 0)
+    B, Sq, Sk, H, hkv, D = 2, 1000, 1400, 4, 2, 128
+    q, _, _, _ = seeded_qkv(5, B, Sq, H, hkv, D, device="cuda")
+    _, k, v, _ = seeded_qkv(6, B, Sk, H, hkv, D, device="cuda")
+    scale = D ** -0.5
+    q_off = 300
+    # K/V shards in "arrival" order: the middle one first (keys 500..899 are invisible to rows < 200 when
+    # causal), then the head, then the tail (1 000..1 399: invisible to most rows, ragged)
+    cuts = [(500, 900), (0, 500), (900, 1400)]
+    segs = [(k[:, a:b], v[:, a:b], a) for a, b in cuts]
+    ref_o, ref_l = mb.attn_fwd_segments(q, segs, scale, causal=causal, q_off=q_off)
+
+    o = torch.full_like(q, 7.0)
+    lse = torch.full((B, H, Sq), 7.0, device=dev)
+    st_o = torch.full((B, H, Sq, D), float("nan"), device=dev)
+    st_ml = torch.full((B, H, Sq, 2), float("nan"), device=dev)
+    n_pairs = (Sq + 255) // 256
+    chain = torch.zeros(B, H, n_pairs, dtype=torch.int32, device=dev)
+    jobs = []
+    for t in range(len(segs)):
+        j = {"q": q, "q_off": q_off, "seg_mask": 1 << t, "state": (st_o, st_ml),
+             "state_in": t > 0, "state_out": t < len(segs) - 1}
+        if t == len(segs) - 1:
+            j["out_raw"] = (o.data_ptr(), o.stride(0), o.stride(1), o.stride(2))
+            j["lse_raw"] = (lse.data_ptr(), lse.stride(0), lse.stride(1))
+        if one_launch:
+            j["chain"] = (chain.data_ptr(), t, t + 1)
+        jobs.append(j)
+    if one_launch:
+        attn_fwd_multi(jobs, segs, scale, causal, B, H, hkv, D, dev)
+    else:
+        for j in jobs:
+            attn_fwd_multi([j], segs, scale, causal, B, H, hkv, D, dev)
+    assert _lib.status_fetch(torch.cuda.current_stream().cuda_stream) == 0
+    assert torch.equal(o, ref_o)
+    assert torch.equal(lse, ref_l)
+    if one_launch:
+        assert chain.unique().tolist() == [len(segs) - 1]
+
+
+@pytest.mark.gpu
+def test_carried_state_is_the_unnormalised_accumulator():
+    """What a state_out job stores: rows o * l with l the sum of exp(scale * (s - m)) and m the stored
+    maximum, so that o = state_o / l and lse = scale * m + ln(l) reproduce the one-job result; rows without
+    a visible key store (0, -inf, 0).  Two chains in one launch (two query shards) do not disturb each other."""
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200 import _lib
+    from mercury_artifact_b200.attention import attn_fwd_multi
+    from tests.helpers import seeded_qkv
+
+    dev = torch.device("cuda", 0)
+    B, S, H, D = 1, 512, 2, 128
+    q, k, v, _ = seeded_qkv(9, B, S, H, H, D, device="cuda")
+    scale = D ** -0.5
+    segs = [(k[:, 256:], v[:, 256:], 256), (k[:, :256], v[:, :256], 0)]
+    ref_o, ref_l = mb.attn_fwd_segments(q, segs, scale, causal=True, q_off=0)
+    halves = [slice(0, 256), slice(256, 512)]
+    o = torch.zeros_like(q)
+    lse = torch.zeros(B, H, S, device=dev)
+    states = [(torch.zeros(B, H, 256, D, device=dev), torch.zeros(B, H, 256, 2, device=dev)) for _ in halves]
+    chain = torch.zeros(2, B, H, 1, dtype=torch.int32, device=dev)
+    jobs = []
+    for t in range(2):                      # shard-major order: both chains' first jobs, then their second ones
+        for c, rows in enumerate(halves):
+            j = {"q": q[:, rows], "q_off": rows.start, "seg_mask": 1 << t, "state": states[c],
+                 "state_in": t == 1, "state_out": t == 0, "chain": (chain[c].data_ptr(), t, t + 1)}
+            if t == 1:
+                j["out_raw"] = (o[:, rows].data_ptr(), o.stride(0), o.stride(1), o.stride(2))
+                j["lse_raw"] = (lse[:, :, rows].data_ptr(), lse.stride(0), lse.stride(1))
+            jobs.append(j)
+    attn_fwd_multi(jobs[:2], segs, scale, True, B, H, H, D, dev)      # first jobs alone: look at the state
+    torch.cuda.synchronize()
+    so, sml = states[0]                    # rows 0..255 see nothing of keys 256..511
+    assert so.abs().max().item() == 0 and torch.isneginf(sml[..., 0]).all() and (sml[..., 1] == 0).all()
+    so, sml = states[1]                    # rows 256..511 against keys 256..511, causal
+    po, pl = mb.attn_fwd_segments(q[:, 256:], segs[:1], scale, causal=True, q_off=256)
+    m, l = sml[..., 0], sml[..., 1]
+    assert (l > 0).all()
+    assert ((so / l[..., None]).transpose(1, 2) - po.float()).abs().max().item() <= 2e-2
+    assert (m * scale + l.log() - pl).abs().max().item() <= 1e-3
+    chain.zero_()
+    attn_fwd_multi(jobs, segs, scale, True, B, H, H, D, dev)
+    assert _lib.status_fetch(torch.cuda.current_stream().cuda_stream) == 0
+    assert torch.equal(o, ref_o) and torch.equal(lse, ref_l)

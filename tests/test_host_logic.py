@@ -270,9 +270,12 @@ def test_ring_divide_validation_and_memory_model():
     kv_b, q_b, lse_b = 2 * 4096 * 32 * 128 * 2, 4096 * 32 * 128 * 2, 32 * 4096 * 4
     st_b = 2 * 32 * 4096 * 4
     # balanced causal forward: one symmetric slot [kv | q], seven staging slots, the o / lse inbox
-    assert op.memory_bytes() == {"symmetric": kv_b + q_b + 4096, "staging": 7 * (kv_b + q_b), "inbox": q_b + lse_b}
+    state_b = 2 * 32 * (2048 * 130 + 8) * 4          # two half-shards: fp32 rows + (max, sum) + chain words
+    assert op.memory_bytes() == {"symmetric": kv_b + q_b + 4096, "staging": 7 * (kv_b + q_b), "inbox": q_b + lse_b,
+                                 "state": state_b}
     plain = RingAttention((8,), 1, 4096, 32, 32, 128, causal=False, ctx=Ctx())
-    assert plain.memory_bytes() == {"symmetric": kv_b + 4096, "staging": 7 * kv_b, "inbox": 0}
+    assert plain.memory_bytes() == {"symmetric": kv_b + 4096, "staging": 7 * kv_b, "inbox": 0,
+                                    "state": 32 * (4096 * 130 + 16) * 4}
     both = RingAttention((8,), 1, 4096, 32, 32, 128, causal=False, ctx=Ctx(), backward=True)
     assert both.memory_bytes()["staging"] == 7 * (kv_b + 2 * q_b + st_b)
     with pytest.raises(ValueError, match="fixed at construction"):
@@ -289,4 +292,4 @@ def test_ring_divide_validation_and_memory_model():
     Ctx.world, Ctx.rank = 2, 1
     assert RingAttention((2,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx(), balance_causal=False,
                          ring_divide=7 if 4096 % 7 == 0 else 4).ring_divide == 4
-    assert RingAttention((1,), 1, 4096, 32, 32, 128).memory_bytes() == {"symmetric": 0, "staging": 0, "inbox": 0}
+    assert RingAttention((1,), 1, 4096, 32, 32, 128).memory_bytes() == {"symmetric": 0, "staging": 0, "inbox": 0, "state": 0}

@@ -61,6 +61,7 @@ def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=F
     assert model["symmetric"] + model["inbox"] == op._x.sym.local.bytes().numel()
     assert model["staging"] == op._x.staging.numel()
     assert model["inbox"] == op._x.inbox().numel()
+    assert model["state"] == sum(t.numel() * t.element_size() for st in op._state for t in st)
     ret[rank] = outs
     dist.barrier()
     dist.destroy_process_group()

@@ -186,22 +186,48 @@ def test_balanced_causal_forward_plan(world, mesh, ring_divide):
         x = op._x
         raised = _check_transfers(op, ops, 1)
         _, jobs, segs = launches[0]
-        assert len(jobs) == 2 and len(segs) <= 32
+        assert len(jobs) <= 16 and len(segs) <= 32
         # segments: the local shard first, then remote pieces; every remote piece waits for a flag that is
         # raised behind a copy on the same stream
         assert segs[0][2] == r * L and len(segs[0]) == 3
-        seen_keys = set()
         for sg in segs:
-            k, v, k_off = sg[:3]
-            seen_keys.update(range(k_off, k_off + k.shape[1]))
             if len(sg) > 3:
                 assert sg[3] in raised and sg[4] == 1
+        shard_of = [sg[2] // L for sg in segs]
         chunks = (2 * world - 1 - r, r)
-        # the keys this rank holds cover everything its heavier half-shard can see
-        assert seen_keys >= set(range(0, (chunks[0] + 1) * Lh))
-        for idx, (c, job) in enumerate(zip(chunks, jobs)):
+        # jobs are listed shard by shard in arrival order (local first), each job takes the segments of ONE shard
+        arrival = []
+        for jb in jobs:
+            shards = {shard_of[i] for i in range(len(segs)) if (jb["seg_mask"] >> i) & 1}
+            assert len(shards) == 1
+            arrival.append(shard_of.index(shards.pop()))
+        assert arrival == sorted(arrival)
+        for idx, c in enumerate(chunks):
             owner, half = c // 2, c % 2
-            assert job["q_off"] == c * Lh and job["q"].shape[1] == Lh
+            mine = [jb for jb in jobs if jb["q_off"] == c * Lh]
+            # a chain: the first job starts from nothing, every other continues the state the previous one
+            # stored, the last one writes the result into the owner's inbox and raises the owner's flag
+            seen_keys = set()
+            for p, jb in enumerate(mine):
+                assert jb["q"].shape[1] == Lh
+                for i in range(len(segs)):
+                    if (jb["seg_mask"] >> i) & 1:
+                        assert not (seen_keys & set(range(segs[i][2], segs[i][2] + segs[i][0].shape[1])))
+                        seen_keys.update(range(segs[i][2], segs[i][2] + segs[i][0].shape[1]))
+                last = p == len(mine) - 1
+                if len(mine) > 1:
+                    assert bool(jb["state_in"]) == (p > 0) and bool(jb["state_out"]) == (not last)
+                    assert jb["chain"][1:] == (64 + p, 64 + p + 1) and jb["chain"][0] == mine[0]["chain"][0]
+                    assert jb["state"][0].shape == (1, H, Lh, 128) and jb["state"][0] is mine[0]["state"][0]
+                else:
+                    assert "state" not in jb
+                assert ("out_raw" in jb) == last and ("done" in jb) == last
+                if owner != r:
+                    assert jb["q_flag"][0] in raised, "pulled queries announce themselves"
+                else:
+                    assert "q_flag" not in jb
+            assert seen_keys >= set(range(0, (c + 1) * Lh)), "the chain covers every key the chunk can see"
+            job = mine[-1]
             where_o = x.sym.where(job["out_raw"][0])
             assert where_o == (owner, x.slot_bytes + op._inbox_o + half * Lh * H * 128 * 2)
             where_l = x.sym.where(job["lse_raw"][0])
@@ -210,10 +236,6 @@ def test_balanced_causal_forward_plan(world, mesh, ring_divide):
             assert x.sym.where(flag) == (owner, x._flag_off + ring._RES + 4 * half) and val == 1
             assert (owner, half) not in computed, "each half-shard is computed once"
             computed[(owner, half)] = r
-            if owner != r:
-                assert job["q_flag"][0] in raised, "pulled queries announce themselves"
-            else:
-                assert "q_flag" not in job
         # the owner waits for both of its halves on the main stream, after the launch
         w = [p for k, s, p in ops if k == "wait" and s == "main"]
         assert w and sorted(x.sym.where(ptr)[1] for ptr, _ in w[-1]) == [x._flag_off + ring._RES, x._flag_off + ring._RES + 4]
@@ -245,7 +267,8 @@ def test_plain_forward_and_backward_plan(world, mesh, causal):
             op.backward(torch.zeros_like(q), q, kv, o, lse)
             raised_b = _check_transfers(op, ctx.ops, 2)
         (_, jobs, segs), (_, kv_segs, q_off), (_, q_segs, k_off) = launches
-        assert len(jobs) == 1 and "done" not in jobs[0] and jobs[0]["q_off"] == r * L
+        assert all("done" not in jb and jb["q_off"] == r * L for jb in jobs) and "out_raw" in jobs[-1]
+        assert [bool(jb.get("state_in")) for jb in jobs] == [False] + [True] * (len(jobs) - 1)
         order = ring.mesh.kv_origin_schedule(r, mesh)
         want = [og for og in order if (not causal) or og <= r]
         got = []

@@ -477,7 +477,7 @@ def run_ours(args):
 
     if world > 1:
         mb.comm.init_p2p()
-    op = RingAttention(mesh, B, L, H, hkv, D, causal=causal, backward=True)
+    op = RingAttention(mesh, B, L, H, hkv, D, causal=causal, backward=True, schedule=args.schedule)
     # resident inputs live in the op's symmetric buffers (its documented zero-copy mode): peers pull
     # q / kv straight from there and results arrive in o / lse without staging copies
     q, kv, dout, o, lse = job.inputs_in(op, B, L, H, hkv, D, with_dout=True)
@@ -582,7 +582,13 @@ def run_ours(args):
                 "workload": workload_name(args.workload, world),
                 "l2": ("inputs larger than L2: q+k+v %.0f MiB per rank; every step streams all %d shards' K/V "
                        "(%.0f MiB) through this GPU" % (3 * B * L * H * D * 2 / 2 ** 20, world,
-                                                       2 * B * S * hkv * D * 2 / 2 ** 20)),
+                                                       2 * B * S * hkv * D * 2 / 2 ** 20))
+                if getattr(op, "schedule", "ring") == "ring" else
+                ("q+k+v %.0f MiB per rank; every step pulls this rank's head group of every peer's q, k, v over "
+                 "NVLink again (%.0f MiB arrive per step, written by the copy engines), so no step finds its "
+                 "inputs in L2 from the one before" % (3 * B * L * H * D * 2 / 2 ** 20,
+                                                       (world - 1) * B * L * (H + 2 * hkv) // world * D * 2 / 2 ** 20)),
+                "schedule": getattr(op, "schedule", "ring") if world > 1 else "one rank",
                 "per_gpu_tflops": per_gpu,
                 "buffers": "q / kv / o / lse in the op's symmetric buffers (zero-copy mode)" if world > 1 else "ordinary tensors",
                 "ms_per_step_with_ordinary_tensors": ms_plain,
@@ -642,6 +648,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--schedule", default=None, choices=["ring", "heads"],
+                    help="forward schedule on several GPUs (default: the library's choice for the shape)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg")
     ap.add_argument("--quick", action="store_true",
                     help="headline, e2e, fwd+bwd and parity only (profiling runs): no sustained loop, no extra "

@@ -36,7 +36,7 @@ extern "C" {
 #define MB_E_TOO_LARGE (-6)   /* problem exceeds the fixed scratch of an allocation-free entry point */
 
 #define MB_MAX_SEGMENTS 32 /* K/V (or stream) shards per launch: 8 ranks x ring_divide 4, or a 32-way mesh */
-#define MB_MAX_JOBS 16      /* query shards per mb_attn_fwd_multi launch */
+#define MB_MAX_JOBS 40      /* query shards per mb_attn_fwd_multi launch */
 
 /* One sequence shard of K and V: [batch, sk, hkv, head_dim] views. */
 typedef struct mb_kv_segment {
@@ -317,6 +317,10 @@ MB_API int mb_ipc_import(const unsigned char* handle64, void** ptr);
 MB_API int mb_ipc_release(void* ptr);
 /* Stream-ordered copy; either side may be a peer mapping (copy engines over NVLink). */
 MB_API int mb_copy_async(void* dst, const void* src, uint64_t bytes, void* cuda_stream);
+/* The same for `height` rows of `width` bytes with row pitches dpitch / spitch (one head group of a
+ * [batch, seq, heads, head_dim] tensor is such a rectangle); all four 16-byte aligned. */
+MB_API int mb_copy2d_async(void* dst, uint64_t dpitch, const void* src, uint64_t spitch, uint64_t width,
+                           uint64_t height, void* cuda_stream);
 /* Stream-ordered release-store of `value` to a flag word (local or peer mapping). */
 MB_API int mb_flag_signal(int32_t* flag, int32_t value, void* cuda_stream);
 /* Stream-ordered wait until *flag >= value.  After timeout_ns the wait gives up, writes a

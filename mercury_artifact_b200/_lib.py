@@ -10,7 +10,7 @@ import ctypes as C
 from pathlib import Path
 
 MB_MAX_SEGMENTS = 32
-MB_MAX_JOBS = 16
+MB_MAX_JOBS = 40
 
 MB_SUCCESS = 0
 ERROR_NAMES = {
@@ -321,6 +321,7 @@ _SIGNATURES = {
     "mb_flags_signal": [C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int32, C.c_void_p],
     "mb_flags_wait": [C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p],
     "mb_pull_sm": [C.POINTER(PullArgs), C.c_void_p],
+    "mb_copy2d_async": [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p],
     "mb_set_peer_wait_ms": [C.c_uint32],
     "mb_status_peek_async": [C.c_void_p, C.c_void_p],
     "mb_status_fetch": [C.POINTER(C.c_int32), C.c_void_p],

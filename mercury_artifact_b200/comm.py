@@ -137,6 +137,13 @@ class PeerContext:
         _lib.check(_lib.lib.mb_copy_async(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), C.c_uint64(nbytes),
                                           C.c_void_p(stream.cuda_stream)), "mb_copy_async")
 
+    def copy2d(self, dst_ptr: int, dpitch: int, src_ptr: int, spitch: int, width: int, height: int,
+               stream: torch.cuda.Stream) -> None:
+        """`height` rows of `width` bytes; row pitches in bytes (mb_copy2d_async)."""
+        _lib.check(_lib.lib.mb_copy2d_async(C.c_void_p(dst_ptr), C.c_uint64(dpitch), C.c_void_p(src_ptr),
+                                            C.c_uint64(spitch), C.c_uint64(width), C.c_uint64(height),
+                                            C.c_void_p(stream.cuda_stream)), "mb_copy2d_async")
+
     def signal(self, flag_ptr: int, value: int, stream: torch.cuda.Stream) -> None:
         self.launch_count += 1
         _lib.check(_lib.lib.mb_flag_signal(C.c_void_p(flag_ptr), C.c_int32(value), C.c_void_p(stream.cuda_stream)),

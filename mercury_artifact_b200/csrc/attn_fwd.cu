@@ -156,7 +156,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const __grid_constant__ Fw
     asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_STR(MB_FWD_AUX_REGS) ";");
     if (lane == 0 && any_work) {
       bool ok = true;
-      const CUtensorMap* qmap = &maps.q[ctl->jid];
+      const CUtensorMap* qmap = &maps.q[J.qmap];
       tma_prefetch_desc(qmap);
       if (J.q_flag != nullptr) {
         // The queries are being staged from another GPU: wait (bounded) for their arrival flag.  On a
@@ -642,7 +642,8 @@ int launch_attn_fwd_multi(const mb_attn_fwd_multi_args* x, cudaStream_t stream) 
     seg_new[s] = nseg++;
   }
   a.nseg = nseg;
-  int njobs = 0, x_total = 0;
+  int njobs = 0, x_total = 0, nqmaps = 0;
+  const mb_fwd_job* qmap_of[kMaxQMaps];
   for (int j = 0; j < x->njobs; ++j) {
     const mb_fwd_job& g = x->job[j];
     if (g.sq < 0) return MB_E_INVALID;
@@ -656,9 +657,23 @@ int launch_attn_fwd_multi(const mb_attn_fwd_multi_args* x, cudaStream_t stream) 
     if ((g.state_in || g.state_out) && (g.state_o == nullptr || g.state_ml == nullptr)) return MB_E_INVALID;
     if ((reinterpret_cast<uintptr_t>(g.state_o) & 15u) || (reinterpret_cast<uintptr_t>(g.state_ml) & 7u)) return MB_E_INVALID;
     if (g.done_flag != nullptr && g.done_counter == nullptr) return MB_E_INVALID;
-    if (make_tile_map(&maps.q[njobs], g.q, kD, x->hq, g.sq, x->batch, g.q_stride_b, g.q_stride_s, g.q_stride_h))
-      return MB_E_TENSORMAP;
+    // jobs over the same query rows (the links of a state chain) share one tensor map
+    int qmap = -1;
+    for (int m = 0; m < nqmaps && qmap < 0; ++m) {
+      const mb_fwd_job& o = *qmap_of[m];
+      if (o.q == g.q && o.sq == g.sq && o.q_stride_b == g.q_stride_b && o.q_stride_s == g.q_stride_s &&
+          o.q_stride_h == g.q_stride_h)
+        qmap = m;
+    }
+    if (qmap < 0) {
+      if (nqmaps == kMaxQMaps) return MB_E_INVALID;
+      if (make_tile_map(&maps.q[nqmaps], g.q, kD, x->hq, g.sq, x->batch, g.q_stride_b, g.q_stride_s, g.q_stride_h))
+        return MB_E_TENSORMAP;
+      qmap_of[nqmaps] = &g;
+      qmap = nqmaps++;
+    }
     FwdJob& J = a.job[njobs];
+    J.qmap = qmap;
     J.o = reinterpret_cast<__nv_bfloat16*>(g.o);
     J.o_sb = g.o_stride_b;
     J.o_ss = g.o_stride_s;

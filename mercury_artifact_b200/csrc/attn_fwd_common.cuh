@@ -19,9 +19,10 @@ constexpr int kFwdStages = MB_FWD_STAGES;  // 32 KiB K or V tiles in flight (3, 
 constexpr int kFwdThreads = 384;  // 8 softmax warps + one auxiliary warpgroup (2 MMA issuers, loader, 1 idle)
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: tolerate p up to 2^8
 constexpr int kMaxJobs = MB_MAX_JOBS;
+constexpr int kMaxQMaps = 16;  // distinct query tensors per launch (jobs over the same rows share a map)
 
 struct FwdMaps {
-  CUtensorMap q[kMaxJobs];
+  CUtensorMap q[kMaxQMaps];
   CUtensorMap k[MB_MAX_SEGMENTS];
   CUtensorMap v[MB_MAX_SEGMENTS];
 };
@@ -48,6 +49,7 @@ struct FwdJob {
   int* chain;
   int chain_wait, chain_set;
   int st_in, st_out;
+  int qmap;  // index of the job's query tensor map
 };
 
 struct FwdArgs {

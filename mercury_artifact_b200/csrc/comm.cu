@@ -253,6 +253,19 @@ int mb_copy_async(void* dst, const void* src, uint64_t bytes, void* cuda_stream)
              : MB_E_CUDA;
 }
 
+int mb_copy2d_async(void* dst, uint64_t dpitch, const void* src, uint64_t spitch, uint64_t width, uint64_t height,
+                    void* cuda_stream) {
+  if (width == 0 || height == 0) return MB_SUCCESS;
+  if (dst == nullptr || src == nullptr || dpitch < width || spitch < width) return MB_E_INVALID;
+  if ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src) | dpitch | spitch | width) & 15u)
+    return MB_E_INVALID;
+  return mb::cuda_ok(cudaMemcpy2DAsync(dst, dpitch, src, spitch, width, height, cudaMemcpyDefault,
+                                       static_cast<cudaStream_t>(cuda_stream)),
+                     "cudaMemcpy2DAsync")
+             ? MB_SUCCESS
+             : MB_E_CUDA;
+}
+
 int mb_flag_signal(int32_t* flag, int32_t value, void* cuda_stream) {
   if (flag == nullptr) return MB_E_INVALID;
   mb::prefer_max_smem_carveout_once();

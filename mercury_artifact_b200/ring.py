@@ -165,6 +165,24 @@ class _Exchange:
             ctx.signal_many(flags, st)
         return dst
 
+    def pull_rects(self, origin: int, rects: Sequence[Tuple[int, int, int, int, int]],
+                   raise_after: Sequence[Tuple[int, int]] = (), last: bool = False) -> torch.Tensor:
+        """Like pull, for rectangles (staging offset, slot offset, slot row pitch, width, height) in bytes:
+        `height` rows of `width` bytes of `origin`'s slot land densely packed in its staging slot."""
+        ctx, st = self.ctx, self.stream_of(origin)
+        dst = self.stage(origin)
+        if origin not in self._waited:
+            self._waited.add(origin)
+            ctx.wait_flag(self.ready_ptr(self.rank, origin), self.epoch, st)
+        for dst_off, src_off, spitch, width, height in rects:
+            ctx.copy2d(dst.data_ptr() + dst_off, width, self.sym.ptr(origin, src_off), spitch, width, height, st)
+        flags = list(raise_after)
+        if last:
+            flags.append((self.done_ptr(origin, self.rank), self.epoch))
+        if flags:
+            ctx.signal_many(flags, st)
+        return dst
+
     def release(self, origins: Sequence[int]) -> None:
         """Tell these owners that this rank will not read their slots of this epoch (one launch)."""
         flags = [(self.done_ptr(o, self.rank), self.epoch) for o in origins if o != self.rank]
@@ -184,7 +202,8 @@ class RingAttention:
 
     def __init__(self, mesh_shape: Sequence[int], batch: int, seq_local: int, hq: int, hkv: int,
                  head_dim: int = 128, causal: bool = False, ctx: Optional[PeerContext] = None,
-                 balance_causal: bool = True, ring_divide: int = 1, backward: bool = False):
+                 balance_causal: bool = True, ring_divide: int = 1, backward: bool = False,
+                 schedule: Optional[str] = None):
         self.mesh_shape = tuple(int(n) for n in mesh_shape)
         self.world = 1
         for n in self.mesh_shape:
@@ -217,6 +236,30 @@ class RingAttention:
         # needs no such re-assignment: rank r does (r + 1/2) blocks of dQ work and (P - r - 1/2) blocks
         # of dK/dV work, P blocks on every rank.
         self.balanced = bool(balance_causal) and self.causal and self.world > 1 and seq_local % 2 == 0
+        # Forward schedule.  "ring": every rank keeps its query rows (or, balanced causal, two half-shards) and
+        # pulls whole K/V shards.  "heads": every rank computes ALL query rows for hq / world of the heads; it
+        # pulls that head group's slice of q, k and v from every peer (an all-to-all through NVSwitch, 1/world
+        # of the bytes of the ring per shard) and its kernel stores the rows of other ranks straight into their
+        # o / lse.  Causal work is then the same on every rank by construction.  It is the head-parallel split
+        # of the reference's search space (mercury/search) applied inside the call: inputs and outputs keep
+        # the sequence-sharded layout.  Default (None, or MB_SCHEDULE): "heads" on a one-dimensional mesh of up
+        # to 8 ranks when both head counts divide by the world size and balance_causal is on, else "ring".
+        # The backward always uses the ring schedule.
+        schedule = schedule or os.environ.get("MB_SCHEDULE") or None
+        can_heads = (self.world > 1 and len(self.mesh_shape) == 1 and self.world <= 8 and hq % self.world == 0
+                     and hkv % self.world == 0 and self.world <= _lib.MB_MAX_SEGMENTS)
+        if schedule is None:
+            schedule = "heads" if can_heads and balance_causal and int(ring_divide) == 1 else "ring"
+        if schedule not in ("ring", "heads"):
+            raise ValueError("schedule must be 'ring' or 'heads'")
+        if schedule == "heads" and not can_heads:
+            raise ValueError("the heads schedule needs a one-dimensional mesh of 2..8 ranks and head counts "
+                             "that divide by the world size")
+        self.schedule = schedule if self.world > 1 else "ring"
+        self.heads = self.schedule == "heads"
+        if self.heads:
+            self.balanced = False
+        self._inbox_layout = self.balanced or self.heads   # peers pull q, results arrive in a symmetric o / lse
         # ring_divide (the rounds parameter of the reference's shift primitive, ir/primitives.py:33-45,
         # 101-102): every K/V shard travels as `ring_divide` sequence pieces, each with its own arrival
         # flag and its own segment of the launch, so work on a shard starts when its first piece is in.
@@ -240,9 +283,9 @@ class RingAttention:
         if self.with_backward:
             self._slot_bytes = self._off_st + _align(self._st_b, 256)
         else:
-            self._slot_bytes = self._off_do if self.balanced else self._off_q
+            self._slot_bytes = self._off_do if self._inbox_layout else self._off_q
         self._inbox_o, self._inbox_lse = 0, _align(self._q_b, 256)
-        self._inbox_bytes = (self._inbox_lse + _align(self._lse_b, 256)) if self.balanced else 0
+        self._inbox_bytes = (self._inbox_lse + _align(self._lse_b, 256)) if self._inbox_layout else 0
         if self.with_backward and self.ring_divide > 1 and (seq_local // self.ring_divide) % 64 != 0:
             raise ValueError("with backward=True the pieces of ring_divide must be multiples of 64 rows "
                              "(the row statistics travel in 64-row blocks)")
@@ -273,7 +316,7 @@ class RingAttention:
             if self.with_backward:
                 self._s_do, _ = _carve(slot, self._off_do, self.q_shape, torch.bfloat16)
                 self._s_st, _ = _carve(slot, self._off_st, self.stat_shape, torch.float32)
-            if self.balanced:
+            if self._inbox_layout:
                 self._s_o, _ = _carve(inbox, self._inbox_o, self.q_shape, torch.bfloat16)
                 self._s_lse, _ = _carve(inbox, self._inbox_lse, self.lse_shape, torch.float32)
             else:   # results are written by this rank's own kernel: ordinary tensors
@@ -340,37 +383,49 @@ class RingAttention:
         row_b = self.hq * self.head_dim * 2
         return [(base_off + (b * self.seq_local + r0) * row_b, (r1 - r0) * row_b) for b in range(self.batch)]
 
-    def _shard_major_jobs(self, chunks: List[dict], order: Sequence[int], shard_bits: dict, epoch: int) -> List[dict]:
+    def _shard_major_jobs(self, chunks: List[dict], order: Sequence[int], shard_bits: dict, epoch: int,
+                          chunk_step: Optional[Sequence[int]] = None, hq: Optional[int] = None) -> List[dict]:
         """Cut every query chunk's work into one job per K/V shard, in the order the shards arrive, and list
         the jobs shard by shard: CTAs are dispatched in job order, so the SMs first do everything that
         needs only the local shard, then everything that needs the first pulled shard, and so on -- no CTA
         holds an SM while it waits for a shard that is still in flight (a CTA that walks through all the
         shards itself does: the first wave consumes shards faster than NVLink delivers them).  The jobs
         of a chunk hand the online-softmax state on through fp32 scratch and chain words; the last one
-        writes the result.  More shards than job slots: consecutive shards share a job."""
+        writes the result.  chunk_step[i] is the step at which chunk i's queries arrive (default 0: with
+        the first shard); its first job then takes every shard that has arrived by then.  More shards than
+        job slots: consecutive shards share a job."""
         L = self.seq_local
-        per_chunk = max(1, _lib.MB_MAX_JOBS // len(chunks))
-        group = -(-len(order) // per_chunk)
-        steps = [list(order[i:i + group]) for i in range(0, len(order), group)]
-        plan: List[Tuple[int, int, int]] = []             # (step, chunk index, segment mask)
-        for t, shards in enumerate(steps):
-            for ci, ch in enumerate(chunks):
-                rows = ch["q"].shape[1]
-                mask = 0
-                for og in shards:
-                    if (not self.causal) or og * L <= ch["q_off"] + rows - 1:     # its first key is visible
-                        mask |= shard_bits[og]
-                if mask:
-                    plan.append((t, ci, mask))
+        hq = self.hq if hq is None else hq
+        chunk_step = list(chunk_step) if chunk_step is not None else [0] * len(chunks)
+        group = 1
+        while True:
+            steps = [list(order[i:i + group]) for i in range(0, len(order), group)]
+            plan: List[Tuple[int, int, int]] = []             # (step, chunk index, segment mask)
+            for t, shards in enumerate(steps):
+                for ci, ch in enumerate(chunks):
+                    first_t = chunk_step[ci] // group
+                    if t < first_t:
+                        continue
+                    rows = ch["q"].shape[1]
+                    mask = 0
+                    for tt in (range(t + 1) if t == first_t else (t,)):
+                        for og in steps[tt]:
+                            if (not self.causal) or og * L <= ch["q_off"] + rows - 1:     # its first key is visible
+                                mask |= shard_bits[og]
+                    if mask:
+                        plan.append((t, ci, mask))
+            if len(plan) <= _lib.MB_MAX_JOBS or group >= len(order):
+                break
+            group += 1
         count = [sum(1 for _, ci, _ in plan if ci == i) for i in range(len(chunks))]
         if self._state is None:
             dev = chunks[0]["q"].device
             self._state = []
             for ch in chunks:
                 rows = ch["q"].shape[1]
-                self._state.append((torch.empty((self.batch, self.hq, rows, self.head_dim), dtype=torch.float32, device=dev),
-                                    torch.empty((self.batch, self.hq, rows, 2), dtype=torch.float32, device=dev),
-                                    torch.zeros((self.batch, self.hq, (rows + 255) // 256), dtype=torch.int32, device=dev)))
+                self._state.append((torch.empty((self.batch, hq, rows, self.head_dim), dtype=torch.float32, device=dev),
+                                    torch.empty((self.batch, hq, rows, 2), dtype=torch.float32, device=dev),
+                                    torch.zeros((self.batch, hq, (rows + 255) // 256), dtype=torch.int32, device=dev)))
         base = (epoch % (1 << 24)) * 64                   # chain values only grow; restart with cleared words
         if base == 0:
             for _, _, chain in self._state:
@@ -398,6 +453,46 @@ class RingAttention:
                 out.append({k: v for k, v in ch.items()} | {"seg_mask": 0})
         return out
 
+    def _launch_heads(self, q: torch.Tensor, kv: torch.Tensor, x: _Exchange, e: int, softmax_scale: float) -> None:
+        """Forward of the heads schedule: this rank computes ALL query rows for heads
+        [rank * hq / P, (rank + 1) * hq / P).  From every peer it pulls that head group's rectangle of q and
+        of k | v (rows of hq/P * D resp. hkv/P * D elements out of rows of hq * D resp. hkv * D) into the
+        peer's staging slot, densely packed, and raises one arrival flag per peer.  One launch: a chain of
+        jobs per peer's query rows, ordered by arrival; the last job of a chain stores o / lse for this head
+        group straight into the owner's memory and raises the owner's flag for this rank."""
+        P, me, L, B, D = self.world, self.rank, self.seq_local, self.batch, self.head_dim
+        Hl, hkl = self.hq // P, self.hkv // P
+        q_w, kv_w = Hl * D * 2, hkl * D * 2                       # bytes per row of a head group
+        q_rect_b, kv_rect_b = B * L * q_w, 2 * B * L * kv_w
+        order = [me] + [(me - t) % P for t in range(1, P)]        # every rank starts at another origin
+        segs: List[tuple] = []
+        chunks: List[dict] = []
+        shard_bits = {}
+        for n, og in enumerate(order):
+            if og == me:
+                qv = q[:, :, me * Hl:(me + 1) * Hl]
+                kvv = kv[:, :, :, me * hkl:(me + 1) * hkl]
+                flag = None
+            else:
+                buf = x.stage(og)
+                flag = x.piece_flag_ptr(og, 0)
+                x.pull_rects(og, [(0, self._off_q + me * q_w, self.hq * D * 2, q_w, B * L),
+                                  (_align(q_rect_b, 256), self._off_kv + me * kv_w, self.hkv * D * 2, kv_w, 2 * B * L)],
+                             raise_after=[(flag, e)], last=True)
+                qv, _ = _carve(buf, 0, (B, L, Hl, D), torch.bfloat16)
+                kvv, _ = _carve(buf, _align(q_rect_b, 256), (2, B, L, hkl, D), torch.bfloat16)
+            segs.append((kvv[0], kvv[1], og * L) + ((flag, e) if flag is not None else ()))
+            shard_bits[og] = 1 << n
+            ch = {"q": qv, "q_off": og * L,
+                  "out_raw": (x.inbox_ptr(og, self._inbox_o + me * q_w), L * self.hq * D, self.hq * D, D),
+                  "lse_raw": (x.inbox_ptr(og, self._inbox_lse + me * Hl * L * 4), self.hq * L, L),
+                  "done": (x.res_ptr(og, me), e, x.aux_ptr(8 + n))}
+            if flag is not None:
+                ch["q_flag"] = (flag, e)
+            chunks.append(ch)
+        jobs = self._shard_major_jobs(chunks, order, shard_bits, e, chunk_step=list(range(P)), hq=Hl)
+        attn_fwd_multi(jobs, segs, softmax_scale, self.causal, B, Hl, hkl, D, q.device)
+
     # ------------------------------------------------------------------ forward
     def forward(self, q: torch.Tensor, kv: torch.Tensor, o: Optional[torch.Tensor] = None,
                 lse: Optional[torch.Tensor] = None, softmax_scale: Optional[float] = None
@@ -422,24 +517,37 @@ class RingAttention:
         comm = ctx.comm_stream
         e = x.begin(main)
         peers = range(P)
-        zero_in = self._same(kv, self._s_kv) and (not self.balanced or self._same(q, self._s_q))
+        zero_in = self._same(kv, self._s_kv) and (not self._inbox_layout or self._same(q, self._s_q))
         if not zero_in:
             x.wait_slot_free(peers)
             with torch.cuda.stream(comm):
                 self._s_kv.copy_(kv, non_blocking=True)
-                if self.balanced:
+                if self._inbox_layout:
                     self._s_q.copy_(q, non_blocking=True)
         x.publish(peers)
 
         B, Hq, D = self.batch, self.hq, self.head_dim
         if o is None:
-            o = self._s_o if self.balanced else torch.empty_like(q)
+            o = self._s_o if self._inbox_layout else torch.empty_like(q)
         if lse is None:
-            lse = self._s_lse if self.balanced else torch.empty(self.lse_shape, dtype=torch.float32, device=q.device)
+            lse = self._s_lse if self._inbox_layout else torch.empty(self.lse_shape, dtype=torch.float32,
+                                                                    device=q.device)
         if tuple(lse.shape) != self.lse_shape or lse.dtype != torch.float32 or lse.stride(2) != 1:
             raise ValueError("lse must be an fp32 [batch, hq, seq] tensor with contiguous rows")
         if tuple(o.shape) != self.q_shape or o.dtype != torch.bfloat16 or o.stride(3) != 1:
             raise ValueError("o must be a bf16 tensor shaped like q with a contiguous head_dim")
+
+        if self.heads:
+            self._launch_heads(q, kv, x, e, softmax_scale)    # the local head group is read from the caller's tensors
+            # my rows: every rank (this one included) delivers its head group
+            ctx.wait_many([(x.res_ptr(me, p), e) for p in range(P)], main)
+            if not self._same(o, self._s_o):
+                o.copy_(self._s_o, non_blocking=True)
+            if not self._same(lse, self._s_lse):
+                lse.copy_(self._s_lse, non_blocking=True)
+            self._monitor.post(main)
+            self.last_launches = ctx.launch_count - launches0 + 1
+            return o, lse
 
         # ---- which query rows this rank computes, and where their results go
         jobs: List[dict] = []
@@ -720,8 +828,11 @@ class RingAttention:
             raise ValueError("the slot layout is fixed at construction: pass backward= to RingAttention")
         slot = _align(self._slot_bytes, 1024)
         inbox = _align(self._inbox_bytes, 1024)
-        chunk_rows = [self.seq_local // 2] * 2 if self.balanced else [self.seq_local]
-        state = sum(self.batch * self.hq * (r * (self.head_dim + 2) + (r + 255) // 256) * 4 for r in chunk_rows)
+        if self.heads:      # one chain per rank's query rows, for this rank's head group
+            chunk_rows, heads = [self.seq_local] * self.world, self.hq // self.world
+        else:
+            chunk_rows, heads = ([self.seq_local // 2] * 2 if self.balanced else [self.seq_local]), self.hq
+        state = sum(self.batch * heads * (r * (self.head_dim + 2) + (r + 255) // 256) * 4 for r in chunk_rows)
         return {"symmetric": slot + _FLAG_REGION, "staging": (self.world - 1) * slot, "inbox": inbox, "state": state}
 
     def check(self) -> None:

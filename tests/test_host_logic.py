@@ -266,17 +266,27 @@ def test_ring_divide_validation_and_memory_model():
     class Ctx:
         world, rank, device = 8, 3, None
 
-    op = RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx())
+    op = RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx(), schedule="ring")
     kv_b, q_b, lse_b = 2 * 4096 * 32 * 128 * 2, 4096 * 32 * 128 * 2, 32 * 4096 * 4
     st_b = 2 * 32 * 4096 * 4
     # balanced causal forward: one symmetric slot [kv | q], seven staging slots, the o / lse inbox
     state_b = 2 * 32 * (2048 * 130 + 8) * 4          # two half-shards: fp32 rows + (max, sum) + chain words
     assert op.memory_bytes() == {"symmetric": kv_b + q_b + 4096, "staging": 7 * (kv_b + q_b), "inbox": q_b + lse_b,
                                  "state": state_b}
-    plain = RingAttention((8,), 1, 4096, 32, 32, 128, causal=False, ctx=Ctx())
+    plain = RingAttention((8,), 1, 4096, 32, 32, 128, causal=False, ctx=Ctx(), schedule="ring")
     assert plain.memory_bytes() == {"symmetric": kv_b + 4096, "staging": 7 * kv_b, "inbox": 0,
                                     "state": 32 * (4096 * 130 + 16) * 4}
-    both = RingAttention((8,), 1, 4096, 32, 32, 128, causal=False, ctx=Ctx(), backward=True)
+    both = RingAttention((8,), 1, 4096, 32, 32, 128, causal=False, ctx=Ctx(), backward=True, schedule="ring")
+    # the heads schedule (the default here: 32 heads divide by 8 ranks): slot [kv | q], inbox, and one state
+    # chain per rank's query rows for this rank's four heads
+    heads = RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx())
+    assert heads.schedule == "heads" and not heads.balanced
+    assert heads.memory_bytes() == {"symmetric": kv_b + q_b + 4096, "staging": 7 * (kv_b + q_b), "inbox": q_b + lse_b,
+                                    "state": 8 * 4 * (4096 * 130 + 16) * 4}
+    assert RingAttention((8,), 1, 4096, 4, 2, 128, causal=True, ctx=Ctx()).schedule == "ring"
+    assert RingAttention((4, 2), 1, 4096, 32, 32, 128, ctx=Ctx()).schedule == "ring"
+    with pytest.raises(ValueError, match="divide by the world size"):
+        RingAttention((8,), 1, 4096, 4, 2, 128, ctx=Ctx(), schedule="heads")
     assert both.memory_bytes()["staging"] == 7 * (kv_b + 2 * q_b + st_b)
     with pytest.raises(ValueError, match="fixed at construction"):
         plain.memory_bytes(backward=True)
@@ -285,7 +295,7 @@ def test_ring_divide_validation_and_memory_model():
     with pytest.raises(ValueError, match="segments exceed"):
         RingAttention((8,), 1, 4096, 32, 32, 128, ctx=Ctx(), ring_divide=8)
     # eight ranks x four pieces = 29 segments fit one launch, also with the balanced causal forward
-    assert RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx(), ring_divide=4).balanced
+    assert RingAttention((8,), 1, 4096, 32, 32, 128, causal=True, ctx=Ctx(), ring_divide=4).balanced   # pieces: ring
     with pytest.raises(ValueError, match="multiples of 64 rows"):
         RingAttention((2,), 1, 960, 4, 4, 128, ctx=type("C2", (), dict(world=2, rank=0, device=None))(),
                       ring_divide=2, backward=True)

@@ -16,7 +16,8 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=False, balance=True, ring_divide=1):
+def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=False, balance=True, ring_divide=1,
+            schedule=None):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
@@ -32,7 +33,7 @@ def _worker(rank, world, port, mesh_shape, B, S, H, hkv, causal, ret, with_bwd=F
     q, k, v, do = seeded_qkv(1234, B, S, H, hkv, 128)
     qs, kvs = shard_inputs(q, k, v, world)
     op = RingAttention(mesh_shape, B, S // world, H, hkv, 128, causal=causal, balance_causal=balance,
-                       ring_divide=ring_divide, backward=with_bwd)
+                       ring_divide=ring_divide, backward=with_bwd, schedule=schedule)
     lq, lkv = qs[rank].cuda(), kvs[rank].cuda()
     ldo = do.chunk(world, 1)[rank].contiguous().cuda()
     outs = []
@@ -101,10 +102,13 @@ def test_ring_divide_pieces_two_gpus(causal, ring_divide, balance, with_bwd):
                 assert (res[3][1] - gv[:, rows]).abs().max().item() <= 2e-2
 
 
-@pytest.mark.parametrize("causal,balance", [(False, True), (True, False), (True, True)])
-def test_ring_forward_two_gpus(causal, balance):
-    """balance=True with causal: query half-shards are re-assigned across ranks and results are
-    written into the owner's memory over NVLink; B=2 exercises the strided half-shard pulls."""
+@pytest.mark.parametrize("causal,balance,schedule", [(False, True, "ring"), (True, False, "ring"), (True, True, "ring"),
+                                                     (False, True, "heads"), (True, True, "heads")])
+def test_ring_forward_two_gpus(causal, balance, schedule):
+    """Schedule "ring", balance=True with causal: query half-shards are re-assigned across ranks and results
+    are written into the owner's memory over NVLink; B=2 exercises the strided half-shard pulls.  Schedule
+    "heads": every rank computes all rows of its head group (GQA: 2 + 1 heads per rank) and stores other
+    ranks' rows into their memory."""
     import torch.multiprocessing as mp
     from oracle import block
     from tests.helpers import seeded_qkv
@@ -113,8 +117,8 @@ def test_ring_forward_two_gpus(causal, balance):
     B, S, H, hkv = 2, 2048, 4, 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, False, balance), nprocs=world,
-             join=True)
+    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, False, balance, 1, schedule),
+             nprocs=world, join=True)
     q, k, v, _ = seeded_qkv(1234, B, S, H, hkv, 128)
     fo, fl = block.full_attention(q, k, v, 128 ** -0.5, causal=causal)
     for r in range(world):
@@ -141,9 +145,10 @@ def test_double_ring_forward_four_gpus():
             assert (lse - fl.chunk(world, 2)[r]).abs().max().item() <= 1e-3
 
 
-@pytest.mark.parametrize("causal", [False, True])
-def test_ring_backward_two_gpus(causal):
-    """Forward + backward of the fused ring on two GPUs against single-device fp32 gradients."""
+@pytest.mark.parametrize("causal,schedule", [(False, "ring"), (True, "ring"), (True, "heads")])
+def test_ring_backward_two_gpus(causal, schedule):
+    """Forward + backward of the fused ring on two GPUs against single-device fp32 gradients (the backward
+    is the ring schedule whichever schedule the forward used)."""
     import torch.multiprocessing as mp
     from oracle import block
     from tests.helpers import seeded_qkv
@@ -152,7 +157,7 @@ def test_ring_backward_two_gpus(causal):
     B, S, H, hkv = 1, 2048, 4, 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, True, True, 1),
+    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, True, True, 1, schedule),
              nprocs=world, join=True)
     q, k, v, do = seeded_qkv(1234, B, S, H, hkv, 128)
     scale = 128 ** -0.5
@@ -235,16 +240,40 @@ def test_generated_programs_with_peer_transport_two_gpus(fused, fwd_text):
             assert (dkv[1] - gv.chunk(world, 1)[r]).abs().max().item() <= 2e-2
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
-@pytest.mark.parametrize("mesh_shape,causal,with_bwd", [((4, 2), False, False), ((8,), True, True)])
-def test_eight_gpus(mesh_shape, causal, with_bwd):
-    """8 ranks: the double ring of BASELINE config 4 (inner ring of 4, two groups) and the causal
-    single ring with balanced forward plus backward."""
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+@pytest.mark.parametrize("causal", [False, True])
+def test_heads_schedule_four_gpus(causal):
+    """Schedule "heads" on four ranks (GQA 8/4 heads: two query heads and one K/V head per rank), twice in a
+    row (epochs), with ordinary and with symmetric tensors."""
     import torch.multiprocessing as mp
     from oracle import block
     from tests.helpers import seeded_qkv
 
-    world, B, S, H, hkv = 8, 1, 4096, 4, 2
+    world, B, S, H, hkv = 4, 2, 4096, 8, 4
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), (world,), B, S, H, hkv, causal, ret, False, True, 1, "heads"),
+             nprocs=world, join=True)
+    q, k, v, _ = seeded_qkv(1234, B, S, H, hkv, 128)
+    fo, fl = block.full_attention(q, k, v, 128 ** -0.5, causal=causal)
+    for r in range(world):
+        for o, lse in ret[r]:
+            assert (o - fo.chunk(world, 1)[r].float()).abs().max().item() <= 2e-2
+            assert (lse - fl.chunk(world, 2)[r]).abs().max().item() <= 1e-3
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+@pytest.mark.parametrize("mesh_shape,causal,with_bwd,heads", [((4, 2), False, False, (4, 2)), ((8,), True, True, (4, 2)),
+                                                             ((8,), True, True, (16, 8))])
+def test_eight_gpus(mesh_shape, causal, with_bwd, heads):
+    """8 ranks: the double ring (inner ring of 4, two groups), the causal single ring with balanced forward
+    plus backward (4/2 heads do not divide by 8: ring schedule), and the heads schedule (16/8 heads) with
+    the ring backward."""
+    import torch.multiprocessing as mp
+    from oracle import block
+    from tests.helpers import seeded_qkv
+
+    world, B, S = 8, 1, 4096
+    H, hkv = heads
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), mesh_shape, B, S, H, hkv, causal, ret, with_bwd), nprocs=world,

@@ -56,6 +56,9 @@ class FakeCtx:
     def copy(self, dst, src, nbytes, stream):
         self.ops.append(("copy", stream.name, (dst, src, nbytes)))
 
+    def copy2d(self, dst, dpitch, src, spitch, width, height, stream):
+        self.ops.append(("copy2d", stream.name, (dst, dpitch, src, spitch, width, height)))
+
     def signal(self, ptr, value, stream):
         self.signal_many([(ptr, value)], stream)
 
@@ -124,12 +127,12 @@ def _no_gpu(launches):
         yield
 
 
-def _run_rank(rank, world, mesh, causal, ring_divide, backward, B=1, L=256, H=2, hkv=2):
+def _run_rank(rank, world, mesh, causal, ring_divide, backward, B=1, L=256, H=2, hkv=2, schedule="ring"):
     launches = []
     ctx = FakeCtx(rank, world)
     with _no_gpu(launches):
         op = ring.RingAttention(mesh, B, L, H, hkv, 128, causal=causal, ctx=ctx, ring_divide=ring_divide,
-                                backward=backward)
+                                backward=backward, schedule=schedule)
         q = torch.zeros(op.q_shape, dtype=torch.bfloat16)
         kv = torch.zeros(op.kv_shape, dtype=torch.bfloat16)
         o, lse = op.forward(q, kv)
@@ -284,3 +287,82 @@ def test_plain_forward_and_backward_plan(world, mesh, causal):
         assert sorted({s["off"] // L for s in q_segs}) == sorted(og for og in range(world) if (not causal) or og >= r)
         for s in kv_segs[1:] + q_segs[1:]:
             assert s["flag"] in raised_b and s["flag_value"] == 2
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("causal", [False, True])
+def test_heads_schedule_plan(world, causal):
+    """Schedule "heads": rank r pulls head group r's rectangle of q and of k | v from every peer exactly once,
+    computes every rank's query rows for that head group as one state chain per owner (first job when the
+    owner's rows arrive, then one job per later shard), and the last job of each chain stores into the
+    owner's o / lse at head group r and raises the owner's flag number r; the owner waits for all P flags."""
+    B, L, H, hkv, D = 2, 256, 16, 8, 128
+    Hl, hkl = H // world, hkv // world
+    q_w, kv_w = Hl * D * 2, hkl * D * 2
+    delivered = set()
+    for r in range(world):
+        op, launches, ops, _ = _run_rank(r, world, (world,), causal, 1, False, B=B, H=H, hkv=hkv, schedule="heads")
+        assert op.heads and len(launches) == 1
+        x = op._x
+        sym = x.sym
+        # transfers
+        pulled, raised, done_to = {}, {}, []
+        for pos, (kind, stream, payload) in enumerate(ops):
+            if kind == "copy2d":
+                dst, dpitch, src, spitch, width, height = payload
+                origin, off = sym.where(src)
+                assert origin != r and dpitch == width
+                stage_lo = x.staging.data_ptr() + x.stage_index(origin) * x.slot_bytes
+                assert stage_lo <= dst and dst + width * height <= stage_lo + x.slot_bytes
+                if width == q_w and spitch == H * D * 2 and off == op._off_q + r * q_w:
+                    assert height == B * L
+                    pulled.setdefault(origin, []).append("q")
+                else:
+                    assert (width, spitch, off, height) == (kv_w, hkv * D * 2, op._off_kv + r * kv_w, 2 * B * L)
+                    pulled.setdefault(origin, []).append("kv")
+            elif kind == "signal":
+                for ptr, val in payload:
+                    assert val == 1
+                    raised[ptr] = pos
+                    w = sym.where(ptr)
+                    if w is not None and w[0] != r and x._flag_off + ring._DONE <= w[1] < x._flag_off + ring._RES:
+                        assert w[1] == x._flag_off + ring._DONE + 4 * r
+                        done_to.append(w[0])
+        assert pulled == {p: ["q", "kv"] for p in range(world) if p != r}
+        assert sorted(done_to) == [p for p in range(world) if p != r]
+        _, jobs, segs = launches[0]
+        assert len(jobs) <= 40 and len(segs) == world
+        order = [sg[2] // L for sg in segs]
+        assert order[0] == r and sorted(order) == list(range(world))
+        for sg in segs[1:]:
+            assert sg[3] in raised and sg[4] == 1
+        steps = []
+        for owner in range(world):
+            mine = [(n, jb) for n, jb in enumerate(jobs) if jb["q_off"] == owner * L]
+            seen = []
+            for p, (n, jb) in enumerate(mine):
+                assert jb["q"].shape == (B, L, Hl, D)
+                shards = [order[i] for i in range(world) if (jb["seg_mask"] >> i) & 1]
+                if p == 0:      # the owner's rows arrive with its shard: everything that is there by then
+                    assert set(shards) == {s_ for s_ in order[:order.index(owner) + 1] if (not causal) or s_ <= owner}
+                else:
+                    assert len(shards) == 1 and order.index(shards[0]) > order.index(owner)
+                steps.append((n, max(order.index(s_) for s_ in shards)))
+                seen += shards
+                last = p == len(mine) - 1
+                if len(mine) > 1:
+                    assert bool(jb["state_in"]) == (p > 0) and bool(jb["state_out"]) == (not last)
+                    assert jb["state"][0].shape == (B, Hl, L, D)
+                assert ("done" in jb) == last
+                assert ("q_flag" in jb) == (owner != r)
+            assert sorted(seen) == [s_ for s_ in range(world) if (not causal) or s_ <= owner]
+            final = mine[-1][1]
+            assert sym.where(final["out_raw"][0]) == (owner, x.slot_bytes + op._inbox_o + r * q_w)
+            assert final["out_raw"][1:] == (L * H * D, H * D, D)
+            assert sym.where(final["lse_raw"][0]) == (owner, x.slot_bytes + op._inbox_lse + r * Hl * L * 4)
+            assert sym.where(final["done"][0]) == (owner, x._flag_off + ring._RES + 4 * r)
+            delivered.add((owner, r))
+        assert [t for _, t in sorted(steps)] == sorted(t for _, t in steps), "jobs are listed in arrival order"
+        w = [p for k, s_, p in ops if k == "wait" and s_ == "main"]
+        assert sorted(sym.where(ptr)[1] for ptr, _ in w[-1]) == [x._flag_off + ring._RES + 4 * p for p in range(world)]
+    assert delivered == {(o_, r_) for o_ in range(world) for r_ in range(world)}

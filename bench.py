@@ -342,10 +342,12 @@ def run_extra(job, name, peak, sustained, steps=3, warmup=2):
     q, kv, dout, o, lse = job.inputs_in(op, B, L, H, hkv, D, with_dout=backward, seed=4321)
     fl = flops_fwd(B, S, H, D, causal)
     res = {"workload": workload_name(name, world).replace("forward", "backward" if backward else "forward"),
-           "mesh": list(mesh), "steps": steps, "warmup": warmup}
+           "mesh": list(mesh), "schedule": getattr(op, "schedule", "ring") if world > 1 else "one rank",
+           "steps": steps, "warmup": warmup}
     if backward:
         op.forward(q, kv, o, lse, scale)
-        dq, dkv = torch.empty_like(q), torch.empty_like(kv)
+        bufs = op.symmetric_buffers() if world > 1 else {}
+        dq, dkv = bufs.get("dq", torch.empty_like(q)), bufs.get("dkv", torch.empty_like(kv))
         ms, _, _ = job.timed(lambda: op.backward(dout, q, kv, o, lse, dq, dkv, scale), steps, warmup)
         fl *= 2.5
         res["note"] = "backward only; FLOPs counted as 2.5 x the forward's"
@@ -529,7 +531,8 @@ def run_ours(args):
                         and parity["e2e_lse_max_abs_vs_resident"] <= LSE_TOL)
 
     # forward + backward (the metric's second figure): bwd counted as 2.5x the forward FLOPs
-    dq, dkv = torch.empty_like(q), torch.empty_like(kv)
+    gbufs = op.symmetric_buffers() if world > 1 else {}
+    dq, dkv = gbufs.get("dq", torch.empty_like(q)), gbufs.get("dkv", torch.empty_like(kv))
     ms_fb, _, _ = job.timed(step_fwd_bwd, max(3, args.steps // 2), 3)
     status |= _lib.status_fetch(stream.cuda_stream)
     parity.update({k: v for k, v in parity_backward(job, q, kv, o, lse, dout, dq, dkv, causal, scale).items()

@@ -327,6 +327,18 @@ def attn_bwd_dkv(k, v, q_segments, softmax_scale, causal=False, k_off=0, dk=None
     return dk, dv
 
 
+def dq_convert_raw(dq_accum: torch.Tensor, dq_ptr: int, strides: Sequence[int], batch: int, sq: int, hq: int, pad: int,
+                   softmax_scale: float, out_dtype=torch.bfloat16) -> None:
+    """Finish a single-sweep backward: scale the fp32 dq accumulation [batch, hq, pad, d] and store it as
+    [batch, sq, hq, d] rows at a raw address with element strides (batch, row, head) -- the address may
+    be another rank's memory mapped into this process (mb_attn_bwd_dq_convert)."""
+    with torch.cuda.device(dq_accum.device):
+        _lib.check(_lib.lib.mb_attn_bwd_dq_convert(dq_accum.data_ptr(), dq_ptr, strides[0], strides[1], strides[2],
+                                                   batch, sq, hq, pad, _OUT_MODES[out_dtype], float(softmax_scale),
+                                                   C.c_void_p(_stream_ptr())),
+                   "mb_attn_bwd_dq_convert")
+
+
 def attn_bwd_fused(q, dout, stats: RowStats, k, v, softmax_scale, causal=False, q_off=0, k_off=0, dq=None, dk=None,
                    dv=None, dq_accum: Optional[torch.Tensor] = None):
     """dQ, dK, dV of one query shard against one K/V shard in a single sweep (MB_BWD_MODE_FUSED): scores

@@ -39,8 +39,8 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from . import _lib, mesh
-from .attention import (RowStats, _pad64, attn_bwd_dkv, attn_bwd_dq, attn_bwd_fused, attn_fwd_multi,
-                        attn_fwd_segments, bwd_preprocess)
+from .attention import (RowStats, _bwd_launch, _pad64, attn_bwd_dkv, attn_bwd_dq, attn_bwd_fused, attn_fwd_multi,
+                        attn_fwd_segments, bwd_preprocess, dq_convert_raw)
 from .comm import PeerContext, SymmetricBuffer, _align, default_context
 
 _FLAG_REGION = 4096
@@ -166,22 +166,21 @@ class _Exchange:
         return dst
 
     def pull_rects(self, origin: int, rects: Sequence[Tuple[int, int, int, int, int]],
-                   raise_after: Sequence[Tuple[int, int]] = (), last: bool = False) -> torch.Tensor:
-        """Like pull, for rectangles (staging offset, slot offset, slot row pitch, width, height) in bytes:
-        `height` rows of `width` bytes of `origin`'s slot land densely packed in its staging slot."""
+                   raise_after: Sequence[Tuple[int, int]] = (), last: bool = False) -> None:
+        """Like pull, for rectangles (destination address, slot offset, slot row pitch, width, height) in
+        bytes: `height` rows of `width` bytes of `origin`'s slot land densely packed at the destination (the
+        origin's staging slot or any other local buffer)."""
         ctx, st = self.ctx, self.stream_of(origin)
-        dst = self.stage(origin)
         if origin not in self._waited:
             self._waited.add(origin)
             ctx.wait_flag(self.ready_ptr(self.rank, origin), self.epoch, st)
-        for dst_off, src_off, spitch, width, height in rects:
-            ctx.copy2d(dst.data_ptr() + dst_off, width, self.sym.ptr(origin, src_off), spitch, width, height, st)
+        for dst_ptr, src_off, spitch, width, height in rects:
+            ctx.copy2d(dst_ptr, width, self.sym.ptr(origin, src_off), spitch, width, height, st)
         flags = list(raise_after)
         if last:
             flags.append((self.done_ptr(origin, self.rank), self.epoch))
         if flags:
             ctx.signal_many(flags, st)
-        return dst
 
     def release(self, origins: Sequence[int]) -> None:
         """Tell these owners that this rank will not read their slots of this epoch (one launch)."""
@@ -286,6 +285,11 @@ class RingAttention:
             self._slot_bytes = self._off_do if self._inbox_layout else self._off_q
         self._inbox_o, self._inbox_lse = 0, _align(self._q_b, 256)
         self._inbox_bytes = (self._inbox_lse + _align(self._lse_b, 256)) if self._inbox_layout else 0
+        # heads schedule with backward: the gradients of this rank's rows arrive head group by head group
+        self._inbox_dq = self._inbox_bytes
+        self._inbox_dkv = self._inbox_dq + _align(self._q_b, 256)
+        if self.heads and self.with_backward:
+            self._inbox_bytes = self._inbox_dkv + _align(self._kv_b, 256)
         if self.with_backward and self.ring_divide > 1 and (seq_local // self.ring_divide) % 64 != 0:
             raise ValueError("with backward=True the pieces of ring_divide must be multiples of 64 rows "
                              "(the row statistics travel in 64-row blocks)")
@@ -316,6 +320,9 @@ class RingAttention:
             if self.with_backward:
                 self._s_do, _ = _carve(slot, self._off_do, self.q_shape, torch.bfloat16)
                 self._s_st, _ = _carve(slot, self._off_st, self.stat_shape, torch.float32)
+            if self.heads and self.with_backward:
+                self._s_dq, _ = _carve(inbox, self._inbox_dq, self.q_shape, torch.bfloat16)
+                self._s_dkv, _ = _carve(inbox, self._inbox_dkv, self.kv_shape, torch.bfloat16)
             if self._inbox_layout:
                 self._s_o, _ = _carve(inbox, self._inbox_o, self.q_shape, torch.bfloat16)
                 self._s_lse, _ = _carve(inbox, self._inbox_lse, self.lse_shape, torch.float32)
@@ -357,6 +364,8 @@ class RingAttention:
         out = {"q": self._s_q, "kv": self._s_kv, "o": self._s_o, "lse": self._s_lse}
         if self.with_backward:
             out["dout"] = self._s_do
+            if self.heads:      # gradients arrive here; passing these to backward() skips the copy-out
+                out["dq"], out["dkv"] = self._s_dq, self._s_dkv
         return out
 
     def inputs_writable(self) -> None:
@@ -476,8 +485,9 @@ class RingAttention:
             else:
                 buf = x.stage(og)
                 flag = x.piece_flag_ptr(og, 0)
-                x.pull_rects(og, [(0, self._off_q + me * q_w, self.hq * D * 2, q_w, B * L),
-                                  (_align(q_rect_b, 256), self._off_kv + me * kv_w, self.hkv * D * 2, kv_w, 2 * B * L)],
+                x.pull_rects(og, [(buf.data_ptr(), self._off_q + me * q_w, self.hq * D * 2, q_w, B * L),
+                                  (buf.data_ptr() + _align(q_rect_b, 256), self._off_kv + me * kv_w, self.hkv * D * 2,
+                                   kv_w, 2 * B * L)],
                              raise_after=[(flag, e)], last=True)
                 qv, _ = _carve(buf, 0, (B, L, Hl, D), torch.bfloat16)
                 kvv, _ = _carve(buf, _align(q_rect_b, 256), (2, B, L, hkl, D), torch.bfloat16)
@@ -666,6 +676,8 @@ class RingAttention:
 
         ctx, P = self.ctx, self.world
         x = self._exchange()
+        if self.heads:
+            return self._backward_heads(dout, q, kv, o, lse, dq, dkv, softmax_scale)
         launches0 = ctx.launch_count
         main = torch.cuda.current_stream()
         comm = ctx.comm_stream
@@ -726,6 +738,108 @@ class RingAttention:
                      hq=self.hq)
         self._monitor.post(main)
         self.last_launches = ctx.launch_count - launches0 + 3
+        return dq, dkv
+
+    def _backward_heads(self, dout, q, kv, o, lse, dq, dkv, softmax_scale):
+        """Backward of the heads schedule: this rank computes dq, dk, dv of ALL rows for its head group in one
+        sweep (scores once, dq contributions added in fp32: see attn_bwd_fused) -- causal work is the same
+        on every rank, and no gradient needs a cross-rank reduction.  It pulls its head group's rectangles of
+        k | v (into one [2, B, S, hkv/P, D] buffer: the owner tiles of the launch), q, dout and the row
+        statistics (per origin: the stream segments of the launch) from every peer and waits for them; dq is converted
+        straight into the owners' memory, dk | dv are pushed there by the copy engines, and one flag per
+        owner says that this rank's head group is in."""
+        ctx, x, P, me = self.ctx, self._x, self.world, self.rank
+        B, L, D, S = self.batch, self.seq_local, self.head_dim, self.seq_local * self.world
+        Hl, hkl, pad = self.hq // P, self.hkv // P, self.stat_pad
+        q_w, kv_w, st_w = Hl * D * 2, hkl * D * 2, Hl * pad * 4
+        dev = q.device
+        launches0 = ctx.launch_count
+        main = torch.cuda.current_stream()
+        comm = ctx.comm_stream
+        e = x.begin(main)
+        peers = range(P)
+        if getattr(self, "_bh", None) is None:
+            self._bh = {"kv": torch.empty((2, B, S, hkl, D), dtype=torch.bfloat16, device=dev),
+                        "dkv": torch.empty((2, B, S, hkl, D), dtype=torch.bfloat16, device=dev),
+                        "acc": torch.empty((P, B, Hl, pad, D), dtype=torch.float32, device=dev),
+                        "st": torch.empty((2, B, Hl, pad), dtype=torch.float32, device=dev)}
+        bh = self._bh
+        x.wait_slot_free(peers)      # this call rewrites the row statistics inside the slot
+        with torch.cuda.stream(comm):
+            bwd_preprocess(dout, o, lse, workspace=self._s_st)
+            bh["st"].copy_(self._s_st[:, :, me * Hl:(me + 1) * Hl], non_blocking=True)
+            if not self._same(kv, self._s_kv):
+                self._s_kv.copy_(kv, non_blocking=True)
+            if not self._same(q, self._s_q):
+                self._s_q.copy_(q, non_blocking=True)
+            if not self._same(dout, self._s_do):
+                self._s_do.copy_(dout, non_blocking=True)
+        local_ready = x.publish(peers)
+
+        order = [me] + [(me - t) % P for t in range(1, P)]
+        row_kv = hkl * D * 2
+        # K/V of every origin first (the launch needs all owner tiles), then q | dout | statistics per origin
+        for og in order[1:]:
+            rects = [(bh["kv"][w, b, og * L].data_ptr(), self._off_kv + (w * B + b) * L * self.hkv * D * 2 + me * kv_w,
+                      self.hkv * D * 2, kv_w, L) for w in range(2) for b in range(B)]
+            x.pull_rects(og, rects, raise_after=[(x.piece_flag_ptr(og, 0), e)])
+        q_rect_b = B * L * q_w
+        segs = []
+        for og in order:
+            if og == me:
+                continue
+            buf = x.stage(og)
+            o_q, o_do, o_st = 0, _align(q_rect_b, 256), 2 * _align(q_rect_b, 256)
+            x.pull_rects(og, [(buf.data_ptr() + o_q, self._off_q + me * q_w, self.hq * D * 2, q_w, B * L),
+                              (buf.data_ptr() + o_do, self._off_do + me * q_w, self.hq * D * 2, q_w, B * L),
+                              (buf.data_ptr() + o_st, self._off_st + me * st_w, self.hq * pad * 4, st_w, 2 * B)],
+                         raise_after=[(x.piece_flag_ptr(og, 1), e)], last=True)
+        # the local rows: K/V of my head group into the owner buffer; q, dout as strided views; statistics copied
+        for w in range(2):
+            for b in range(B):
+                ctx.copy2d(bh["kv"][w, b, me * L].data_ptr(), kv_w, kv[w, b, 0, me * hkl].data_ptr(), self.hkv * D * 2,
+                           kv_w, L, main)
+        bh["acc"].zero_()
+        for n, og in enumerate(order):
+            acc = bh["acc"][n]
+            if og == me:
+                sg = {"str": q[:, :, me * Hl:(me + 1) * Hl], "str_g": dout[:, :, me * Hl:(me + 1) * Hl],
+                      "stats": RowStats(bh["st"][0], bh["st"][1], L), "off": me * L, "dq_accum": acc}
+            else:
+                buf = x.stage(og)
+                rq, _ = _carve(buf, 0, (B, L, Hl, D), torch.bfloat16)
+                rdo, _ = _carve(buf, _align(q_rect_b, 256), (B, L, Hl, D), torch.bfloat16)
+                rst, _ = _carve(buf, 2 * _align(q_rect_b, 256), (2, B, Hl, pad), torch.float32)
+                sg = {"str": rq, "str_g": rdo, "stats": RowStats(rst[0], rst[1], L), "off": og * L, "dq_accum": acc}
+            segs.append(sg)
+        main.wait_event(local_ready)     # my statistics were computed on the transfer stream
+        # Everything must be in before the launch: the single-sweep kernel takes every register of the SMs it
+        # runs on, so the one-warp kernels that would raise arrival flags during it could not start.
+        ctx.wait_many([(x.piece_flag_ptr(og, pc), e) for og in order[1:] for pc in (0, 1)], main)
+        _bwd_launch(_lib.MB_BWD_MODE_FUSED, bh["kv"][0], bh["kv"][1], 0, segs, Hl, hkl, softmax_scale, self.causal,
+                    bh["dkv"][0], bh["dkv"][1], False)
+        for n, og in enumerate(order):     # dq of owner og's rows, my head group: scaled, converted, stored there
+            dq_convert_raw(bh["acc"][n], x.inbox_ptr(og, self._inbox_dq + me * q_w), (L * self.hq * D, self.hq * D, D),
+                           B, L, Hl, pad, softmax_scale)
+        # dk | dv rows of every owner: pushed by the copy engines once the kernel is done, then the owner's flag
+        comm.wait_stream(main)
+        for og in order:
+            for w in range(2):
+                for b in range(B):
+                    ctx.copy2d(x.inbox_ptr(og, self._inbox_dkv + (w * B + b) * L * self.hkv * D * 2 + me * kv_w),
+                               self.hkv * D * 2, bh["dkv"][w, b, og * L].data_ptr(), row_kv, kv_w, L, comm)
+            ctx.signal_many([(x.res_ptr(og, 16 + me), e)], comm)
+        ctx.wait_many([(x.res_ptr(me, 16 + p), e) for p in range(P)], main)
+        if dq is None:
+            dq = self._s_dq
+        elif not self._same(dq, self._s_dq):
+            dq.copy_(self._s_dq, non_blocking=True)
+        if dkv is None:
+            dkv = self._s_dkv
+        elif not self._same(dkv, self._s_dkv):
+            dkv.copy_(self._s_dkv, non_blocking=True)
+        self._monitor.post(main)
+        self.last_launches = ctx.launch_count - launches0 + 2 + P
         return dq, dkv
 
     # ------------------------------------------------------------------ host-buffer entry

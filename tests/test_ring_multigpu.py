@@ -145,10 +145,10 @@ def test_double_ring_forward_four_gpus():
             assert (lse - fl.chunk(world, 2)[r]).abs().max().item() <= 1e-3
 
 
-@pytest.mark.parametrize("causal,schedule", [(False, "ring"), (True, "ring"), (True, "heads")])
+@pytest.mark.parametrize("causal,schedule", [(False, "ring"), (True, "ring"), (True, "heads"), (False, "heads")])
 def test_ring_backward_two_gpus(causal, schedule):
-    """Forward + backward of the fused ring on two GPUs against single-device fp32 gradients (the backward
-    is the ring schedule whichever schedule the forward used)."""
+    """Forward + backward of the fused ring on two GPUs against single-device fp32 gradients (schedule
+    "heads": the backward too is computed head group by head group, in one sweep per rank)."""
     import torch.multiprocessing as mp
     from oracle import block
     from tests.helpers import seeded_qkv

@@ -118,9 +118,16 @@ def _no_gpu(launches):
     def pre(dout, o, lse, workspace=None):
         return ring.RowStats(workspace[0], workspace[1], dout.shape[1])
 
+    def bwd_launch(mode, own, own_g, own_off, segments, hq, hkv, scale, causal, out1, out2, accumulate, own_stats=None):
+        launches.append(("fused", mode, own, own_off, segments, hq, hkv, out1))
+
+    def convert(acc, ptr, strides, b, sq, hq, pad, scale, out_dtype=torch.bfloat16):
+        launches.append(("convert", acc, ptr, strides, (b, sq, hq, pad)))
+
     with mock.patch.object(ring, "SymmetricBuffer", FakeSym), mock.patch.object(ring, "attn_fwd_multi", fwd_multi), \
             mock.patch.object(ring, "attn_bwd_dq", bwd_dq), mock.patch.object(ring, "attn_bwd_dkv", bwd_dkv), \
             mock.patch.object(ring, "bwd_preprocess", pre), mock.patch.object(torch.cuda, "synchronize", lambda *a: None), \
+            mock.patch.object(ring, "_bwd_launch", bwd_launch), mock.patch.object(ring, "dq_convert_raw", convert), \
             mock.patch.object(torch.cuda, "current_stream", lambda *a: main), \
             mock.patch.object(torch.cuda, "stream", lambda s: contextlib.nullcontext()), \
             mock.patch.object(torch.cuda, "Event", FakeEvent):
@@ -366,3 +373,62 @@ def test_heads_schedule_plan(world, causal):
         w = [p for k, s_, p in ops if k == "wait" and s_ == "main"]
         assert sorted(sym.where(ptr)[1] for ptr, _ in w[-1]) == [x._flag_off + ring._RES + 4 * p for p in range(world)]
     assert delivered == {(o_, r_) for o_ in range(world) for r_ in range(world)}
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_heads_backward_plan(world):
+    """Heads schedule, backward: rank r pulls its head group's k | v rows of every peer into ONE owner buffer
+    (row block of the origin), q | dout | statistics per origin into staging, waits for all K/V before the
+    launch (q | dout | statistics too), runs one sweep with one stream segment per origin, converts dq of origin j's rows into j's
+    memory at head group r, pushes dk | dv rows to their owners and raises flag 16 + r there; every owner
+    waits for P such flags."""
+    B, L, H, hkv, D = 2, 256, 16, 8, 128
+    Hl, hkl = H // world, hkv // world
+    q_w, kv_w = Hl * D * 2, hkl * D * 2
+    got = set()
+    for r in range(world):
+        op, launches, fwd_ops, ops = _run_rank(r, world, (world,), True, 1, True, B=B, H=H, hkv=hkv, schedule="heads")
+        x, sym = op._x, op._x.sym
+        fused = [l for l in launches if l[0] == "fused"]
+        conv = [l for l in launches if l[0] == "convert"]
+        assert len(fused) == 1 and len(conv) == world
+        _, mode, own, own_off, segs, hq_, hkv_, out1 = fused[0]
+        assert mode == 2 and own.shape == (B, world * L, hkl, D) and own_off == 0 and (hq_, hkv_) == (Hl, hkl)
+        assert out1.shape == own.shape
+        kv_lo = op._bh["kv"].data_ptr()
+        kv_rows, pushes, flags_to, waits = set(), {}, [], []
+        for kind, stream, payload in ops:
+            if kind == "copy2d":
+                dst, dpitch, src, spitch, width, height = payload
+                ws, wd = sym.where(src), sym.where(dst)
+                if wd is not None and x.slot_bytes + op._inbox_dkv <= wd[1]:      # a push of dk | dv rows
+                    assert (dpitch, width, height) == (hkv * D * 2, kv_w, L)
+                    rel = wd[1] - x.slot_bytes - op._inbox_dkv
+                    assert rel % (hkv * D * 2) == r * kv_w
+                    pushes[wd[0]] = pushes.get(wd[0], 0) + 1
+                elif kv_lo <= dst < kv_lo + op._bh["kv"].numel() * 2 and width == kv_w and height == L:
+                    row = (dst - kv_lo) // kv_w
+                    origin = ws[0] if ws is not None else r
+                    assert (row % (world * L)) == origin * L
+                    kv_rows.add((origin, row // (world * L)))
+            elif kind == "signal":
+                for ptr, val in payload:
+                    w = sym.where(ptr)
+                    if w is not None and w[1] == x._flag_off + ring._RES + 4 * (16 + r):
+                        flags_to.append(w[0])
+            elif kind == "wait" and stream == "main":
+                waits.append(payload)
+        assert kv_rows == {(og, wb) for og in range(world) for wb in range(2 * B)}
+        assert pushes == {og: 2 * B for og in range(world)} and sorted(flags_to) == list(range(world))
+        assert sorted(sg["off"] // L for sg in segs) == list(range(world)) and segs[0]["off"] == r * L
+        assert all("flag" not in sg and sg["dq_accum"].shape == (B, Hl, op.stat_pad, D) for sg in segs)
+        # every arrival flag is waited for before the launch (nothing can be signalled during it); the gradient
+        # flags after it
+        assert len(waits[-2]) == 2 * (world - 1) and len(waits[-1]) == world
+        assert sorted(sym.where(p_)[1] for p_, _ in waits[-1]) == [x._flag_off + ring._RES + 4 * (16 + p_) for p_ in range(world)]
+        for (_, acc, ptr, strides, dims), sg in zip(conv, segs):
+            owner = sg["off"] // L
+            assert sym.where(ptr) == (owner, x.slot_bytes + op._inbox_dq + r * q_w)
+            assert strides == (L * H * D, H * D, D) and dims == (B, L, Hl, op.stat_pad) and acc.data_ptr() == sg["dq_accum"].data_ptr()
+            got.add((owner, r))
+    assert got == {(o_, r_) for o_ in range(world) for r_ in range(world)}

@@ -192,7 +192,7 @@ def test_generated_backward_program_four_ranks():
 
 
 def test_backward_full_size_property_config5_shard():
-    """One rank's share of BASELINE config 5 (bf16 B1 H32 D128 causal, 8192-row shards): the diagonal block.
+    """One rank's share of the 65 536-token causal backward on 8 ranks (bf16 B1 H32 D128, 8192-row shards): the diagonal block.
     Size-independent checks: row 0 of dV from a causal block receives only query 0... every query
     attends key 0, so instead: sum_k dV == sum_q dO (softmax rows sum to one) and dQ, dK of a run with
     dO = 0 are exactly zero."""

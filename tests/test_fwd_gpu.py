@@ -197,7 +197,7 @@ def test_host_buffer_forward_matches_oracle(causal, chunks):
 
 
 def test_full_size_properties_config2():
-    """BASELINE config 2 shapes (bf16 B1 S32768 H32 D128 causal): size-independent properties.
+    """The headline benchmark shape (bf16 B1 S32768 H32 D128 causal): size-independent properties.
 
     * splitting K/V into segments at tile boundaries does not change a single bit;
     * query row 0 of a causal run attends to key 0 only: o[0] == v[0], lse[0] == scale * q0.k0;

@@ -122,7 +122,7 @@ def test_causal_ring_equals_full_causal_attention():
 
 
 def test_config1_ring_fp32_matches_full_attention():
-    """BASELINE config 1: fp32, B1 S4096 H8 D64, non-causal, 2 contiguous shards."""
+    """The reference's CPU-runnable case: fp32, B1 S4096 H8 D64, non-causal, 2 contiguous shards."""
     g = torch.Generator().manual_seed(1234)
     B, S, H, D = 1, 4096, 8, 64
     q, k, v = (torch.randn(B, S, H, D, generator=g) for _ in range(3))

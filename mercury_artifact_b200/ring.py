@@ -854,13 +854,56 @@ class RingAttention:
         kernel and copy-out, hence many small chunks rather than few large ones.
         Several ranks: the host tensors are copied straight into this rank's symmetric q / kv (once the
         peers have released them), the forward runs without staging copies, and o / lse are read back
-        from the symmetric result buffers.  Returns after the results are in host memory.
+        from the symmetric result buffers; with the heads schedule this is done for four (or two) chunks of
+        the heads in a pipeline.  Returns after the results are in host memory.
         """
         dev = torch.device("cuda", torch.cuda.current_device()) if self.ctx is None else self.ctx.device
         if softmax_scale is None:
             softmax_scale = self.head_dim ** -0.5
         L = self.seq_local
         main = torch.cuda.current_stream()
+        if self.world > 1 and self.heads:
+            # Head-group chunks, pipelined: chunk c is one forward over hq / nc of the heads (its own op with its
+            # own symmetric buffers); while it runs, chunk c+1 is copied in and chunk c-1 is copied out, so the
+            # PCIe transfers in both directions overlap the kernels and the NVLink all-to-all.
+            P, B, D = self.world, self.batch, self.head_dim
+            want = int(os.environ.get("MB_HOST_CHUNKS", "1"))
+            nc = next((n for n in (4, 2) if n <= want and self.hq % (n * P) == 0 and self.hkv % (n * P) == 0), 1)
+            if nc > 1:
+                if not hasattr(self, "_host_ops"):
+                    self._host_ops = ([RingAttention(self.mesh_shape, B, L, self.hq // nc, self.hkv // nc, D,
+                                                     causal=self.causal, ctx=self.ctx, schedule="heads") for _ in range(nc)],
+                                      torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
+                ops, s_in, s_out = self._host_ops
+                hc, hkc = self.hq // nc, self.hkv // nc
+                ctx = self.ctx
+                s_in.wait_stream(main)
+                arrived = []
+                for c, op in enumerate(ops):
+                    b = op.symmetric_buffers()
+                    with torch.cuda.stream(s_in):
+                        op.inputs_writable()
+                        ctx.copy2d(b["q"].data_ptr(), hc * D * 2, q_host[0, 0, c * hc].data_ptr(), self.hq * D * 2,
+                                   hc * D * 2, B * L, s_in)
+                        ctx.copy2d(b["kv"].data_ptr(), hkc * D * 2, kv_host[0, 0, 0, c * hkc].data_ptr(), self.hkv * D * 2,
+                                   hkc * D * 2, 2 * B * L, s_in)
+                        ev = torch.cuda.Event()
+                        ev.record(s_in)
+                    arrived.append(ev)
+                for c, op in enumerate(ops):
+                    b = op.symmetric_buffers()
+                    main.wait_event(arrived[c])
+                    op.forward(b["q"], b["kv"], b["o"], b["lse"], softmax_scale)
+                    ev = torch.cuda.Event()
+                    ev.record(main)
+                    s_out.wait_event(ev)
+                    ctx.copy2d(o_host[0, 0, c * hc].data_ptr(), self.hq * D * 2, b["o"].data_ptr(), hc * D * 2,
+                               hc * D * 2, B * L, s_out)
+                    ctx.copy2d(lse_host[0, c * hc].data_ptr(), self.hq * L * 4, b["lse"].data_ptr(), hc * L * 4,
+                               hc * L * 4, B, s_out)
+                s_out.synchronize()
+                main.synchronize()
+                return
         if self.world > 1:
             bufs = self.symmetric_buffers()
             q, kv, o, lse = bufs["q"], bufs["kv"], bufs["o"], bufs["lse"]

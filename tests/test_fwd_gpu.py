@@ -323,3 +323,58 @@ def test_carried_state_is_the_unnormalised_accumulator():
     attn_fwd_multi(jobs, segs, scale, True, B, H, H, D, dev)
     assert _lib.status_fetch(torch.cuda.current_stream().cuda_stream) == 0
     assert torch.equal(o, ref_o) and torch.equal(lse, ref_l)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [False, True])
+def test_eight_chains_of_one_launch_like_one_rank_of_eight(causal):
+    """The launch one rank of an 8-rank heads schedule issues, with all data local: 8 query chunks x 8 K/V shards
+    in an arrival order that starts in the middle, 36 jobs (causal: 24) that share 8 query tensor maps, one
+    state chain per chunk -- the first job of a chunk takes every shard that arrived before its queries did.
+    Bit-identical to one job per chunk over the same shard order."""
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200 import _lib
+    from mercury_artifact_b200.attention import attn_fwd_multi
+    from tests.helpers import seeded_qkv
+
+    dev = torch.device("cuda", 0)
+    P, B, L, H, hkv, D = 8, 1, 512, 2, 1, 128
+    S = P * L
+    q, k, v, _ = seeded_qkv(77, B, S, H, hkv, D, device="cuda")
+    scale = D ** -0.5
+    me = 5
+    order = [me] + [(me - t) % P for t in range(1, P)]
+    segs = [(k[:, s * L:(s + 1) * L], v[:, s * L:(s + 1) * L], s * L) for s in order]
+    o = torch.zeros_like(q)
+    lse = torch.zeros(B, H, S, device=dev)
+    states = [(torch.empty(B, H, L, D, device=dev), torch.empty(B, H, L, 2, device=dev),
+               torch.zeros(B, H, L // 256, dtype=torch.int32, device=dev)) for _ in range(P)]
+    plan = []
+    for t in range(P):
+        for n in range(t + 1):
+            j = order[n]
+            shards = range(t + 1) if n == t else (t,)
+            mask = sum(1 << i for i in shards if (not causal) or order[i] <= j)
+            if mask:
+                plan.append((n, mask))
+    count = [sum(1 for n, _ in plan if n == c) for c in range(P)]
+    seen = [0] * P
+    jobs = []
+    for n, mask in plan:
+        j = order[n]
+        p, last = seen[n], seen[n] == count[n] - 1
+        seen[n] += 1
+        jb = {"q": q[:, j * L:(j + 1) * L], "q_off": j * L, "seg_mask": mask}
+        if count[n] > 1:
+            jb.update(state=states[n][:2], state_in=p > 0, state_out=not last, chain=(states[n][2].data_ptr(), p, p + 1))
+        if last:
+            jb["out_raw"] = (o[:, j * L:].data_ptr(), o.stride(0), o.stride(1), o.stride(2))
+            jb["lse_raw"] = (lse[:, :, j * L:].data_ptr(), lse.stride(0), lse.stride(1))
+        jobs.append(jb)
+    assert len(jobs) == (24 if causal else 36)      # more than one launch used to take
+    attn_fwd_multi(jobs, segs, scale, causal, B, H, hkv, D, dev)
+    assert _lib.status_fetch(torch.cuda.current_stream().cuda_stream) == 0
+    for j in range(P):
+        ro, rl = mb.attn_fwd_segments(q[:, j * L:(j + 1) * L], segs, scale, causal=causal, q_off=j * L)
+        assert torch.equal(o[:, j * L:(j + 1) * L], ro), j
+        assert torch.equal(lse[:, :, j * L:(j + 1) * L], rl), j

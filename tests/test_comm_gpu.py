@@ -249,3 +249,30 @@ def test_sm_pull_kernel_copies_ranges_waits_and_signals():
         _lib.set_peer_wait_ms(_lib.PEER_WAIT_MS)
     assert words.view(0, (4,), torch.int32).tolist() == [9, 24, 22, 0]
     words.free()
+
+
+def test_copy2d_moves_a_head_group_rectangle():
+    """mb_copy2d_async: the rows of one head group of a [batch, seq, heads, d] tensor land densely packed, and
+    back again into another tensor's head group; misaligned arguments are refused."""
+    from mercury_artifact_b200 import _lib
+    from mercury_artifact_b200.comm import PeerContext
+
+    ctx = PeerContext()
+    st = torch.cuda.current_stream()
+    B, L, H, D, g0, g1 = 2, 96, 8, 128, 2, 5
+    g = torch.Generator(device="cuda").manual_seed(11)
+    src = torch.randn(B, L, H, D, device="cuda", generator=g).to(torch.bfloat16)
+    packed = torch.zeros(B, L, g1 - g0, D, dtype=torch.bfloat16, device="cuda")
+    w = (g1 - g0) * D * 2
+    ctx.copy2d(packed.data_ptr(), w, src[0, 0, g0].data_ptr(), H * D * 2, w, B * L, st)
+    st.synchronize()
+    assert torch.equal(packed, src[:, :, g0:g1])
+    back = torch.zeros_like(src)
+    ctx.copy2d(back[0, 0, g0].data_ptr(), H * D * 2, packed.data_ptr(), w, w, B * L, st)
+    st.synchronize()
+    assert torch.equal(back[:, :, g0:g1], src[:, :, g0:g1]) and back[:, :, :g0].abs().max().item() == 0
+    assert back[:, :, g1:].abs().max().item() == 0
+    with pytest.raises(_lib.MercuryB200Error):
+        ctx.copy2d(packed.data_ptr() + 2, w, src.data_ptr(), H * D * 2, w, 4, st)      # 16-byte alignment
+    with pytest.raises(_lib.MercuryB200Error):
+        ctx.copy2d(packed.data_ptr(), w // 2, src.data_ptr(), H * D * 2, w, 4, st)     # pitch below the width

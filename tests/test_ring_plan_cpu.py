@@ -432,3 +432,27 @@ def test_heads_backward_plan(world):
             assert strides == (L * H * D, H * D, D) and dims == (B, L, Hl, op.stat_pad) and acc.data_ptr() == sg["dq_accum"].data_ptr()
             got.add((owner, r))
     assert got == {(o_, r_) for o_ in range(world) for r_ in range(world)}
+
+
+def test_more_shards_than_job_slots_share_jobs():
+    """32 ranks, balanced causal ring: two chains of up to 32 shards would need 48 jobs; consecutive shards
+    then share a job, the launch stays within its 40 job slots and every chain still covers every key its
+    chunk can see, each key once, in arrival order."""
+    world, L, Lh = 32, 256, 128
+    for r in (0, 13, 31):
+        op, launches, ops, _ = _run_rank(r, world, (world,), True, 1, False)
+        _, jobs, segs = launches[0]
+        assert len(jobs) <= 40 and len(segs) <= 32
+        for c in (2 * world - 1 - r, r):
+            mine = [jb for jb in jobs if jb["q_off"] == c * Lh]
+            keys, last_seg = set(), -1
+            for p, jb in enumerate(mine):
+                idx = [i for i in range(len(segs)) if (jb["seg_mask"] >> i) & 1]
+                assert idx and min(idx) > last_seg
+                last_seg = max(idx)
+                for i in idx:
+                    rng = set(range(segs[i][2], segs[i][2] + segs[i][0].shape[1]))
+                    assert not (keys & rng)
+                    keys |= rng
+                assert bool(jb.get("state_in")) == (p > 0) and ("out_raw" in jb) == (p == len(mine) - 1)
+            assert keys >= set(range(0, (c + 1) * Lh))

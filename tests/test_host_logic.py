@@ -141,8 +141,8 @@ def test_generated_programs_run_on_virtual_ranks_with_oracle_ops():
 
         res = run_ranks(g["world"], body)
         for r in range(g["world"]):
-            assert torch.allclose(res[r][0], g["t"][f"o_rank{r}"], atol=2e-6)
-            assert torch.allclose(res[r][1], g["t"][f"lse_rank{r}"], atol=2e-6)
+            assert torch.allclose(res[r][0], g["t"][f"o_rank{r}"], atol=1e-4)
+            assert torch.allclose(res[r][1], g["t"][f"lse_rank{r}"], atol=1e-4)
 
 
 def test_emitter_recognises_kv_rings_and_leaves_other_programs_alone():

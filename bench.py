@@ -483,6 +483,25 @@ def run_ours(args):
     # resident inputs live in the op's symmetric buffers (its documented zero-copy mode): peers pull
     # q / kv straight from there and results arrive in o / lse without staging copies
     q, kv, dout, o, lse = job.inputs_in(op, B, L, H, hkv, D, with_dout=True)
+    schedule_note = None
+    if world > 1 and args.schedule is None and op.schedule != "ring":
+        # One probing step of the library's default schedule; if a device-side wait runs out on any rank
+        # (a status code, never a hang), every rank falls back to the ring schedule and the line says so.
+        bad = 0
+        try:
+            op.forward(q, kv, o, lse, scale)
+            op.check()
+        except _lib.MercuryB200Error as exc:
+            bad = 1
+            print(f"[bench] rank {rank}: {op.schedule} schedule failed its probing step: {exc}", file=sys.stderr)
+        if job.max_over_ranks(bad) > 0:
+            schedule_note = f"the {op.schedule} schedule failed its probing step on some rank; ring schedule used"
+            try:
+                _lib.status_fetch(job.stream.cuda_stream)      # clears the device word
+            except Exception:
+                pass
+            op = RingAttention(mesh, B, L, H, hkv, D, causal=causal, backward=True, schedule="ring")
+            q, kv, dout, o, lse = job.inputs_in(op, B, L, H, hkv, D, with_dout=True)
     q_host, kv_host = q.cpu().pin_memory(), kv.cpu().pin_memory()
     o_host = torch.empty(B, L, H, D, dtype=torch.bfloat16).pin_memory()
     lse_host = torch.empty(B, H, L, dtype=torch.float32).pin_memory()
@@ -592,6 +611,7 @@ def run_ours(args):
                  "inputs in L2 from the one before" % (3 * B * L * H * D * 2 / 2 ** 20,
                                                        (world - 1) * B * L * (H + 2 * hkv) // world * D * 2 / 2 ** 20)),
                 "schedule": getattr(op, "schedule", "ring") if world > 1 else "one rank",
+                "schedule_note": schedule_note,
                 "per_gpu_tflops": per_gpu,
                 "buffers": "q / kv / o / lse in the op's symmetric buffers (zero-copy mode)" if world > 1 else "ordinary tensors",
                 "ms_per_step_with_ordinary_tensors": ms_plain,

@@ -472,7 +472,7 @@ class RingAttention:
         P, me, L, B, D = self.world, self.rank, self.seq_local, self.batch, self.head_dim
         Hl, hkl = self.hq // P, self.hkv // P
         q_w, kv_w = Hl * D * 2, hkl * D * 2                       # bytes per row of a head group
-        q_rect_b, kv_rect_b = B * L * q_w, 2 * B * L * kv_w
+        q_rect_b = B * L * q_w
         order = [me] + [(me - t) % P for t in range(1, P)]        # every rank starts at another origin
         segs: List[tuple] = []
         chunks: List[dict] = []

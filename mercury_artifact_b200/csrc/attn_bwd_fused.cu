@@ -40,19 +40,29 @@
 // tensor-memory owner, 9 TMA loader, 10-11 idle, 12-15 drain dQ^T.  Registers are allocated per
 // warpgroup (a CTA of 14 warps is charged for 16), so the CTA launches with 512 x 128 registers and
 // setmaxnreg moves them to where they are needed: 168 for the element-wise warpgroups, 88 for the
-// other two.  Every wait is bounded, as in the other kernels.
+// other two.  That is every register of the SM.  A launch whose stream segments carry arrival flags
+// uses a second instantiation with 120 / 160 / 80 (1 % slower): the one-warp kernels that raise those
+// flags from the transfer stream must be able to start beside a resident CTA.
+// Every wait is bounded, as in the other kernels.
 #include "attn_bwd_common.cuh"
 
 namespace mb {
 
 constexpr int kFusedThreads = 512;
-#define MB_FUSED_LAUNCH_REGS 128
-#define MB_FUSED_EW_REGS 168
-#define MB_FUSED_AUX_REGS 88
-#define MB_FSTR2(x) #x
-#define MB_FSTR(x) MB_FSTR2(x)
-static_assert(8 * 32 * MB_FUSED_EW_REGS + 8 * 32 * MB_FUSED_AUX_REGS <= kFusedThreads * MB_FUSED_LAUNCH_REGS,
+static_assert(8 * 32 * 168 + 8 * 32 * 88 <= kFusedThreads * 128 && 8 * 32 * 160 + 8 * 32 * 80 <= kFusedThreads * 120,
               "setmaxnreg budgets exceed the registers the CTA is launched with");
+
+// Register budgets of the roles, by the launch budget of the instantiation.
+template <int kLaunchRegs>
+__device__ __forceinline__ void fused_regs_aux() {
+  if constexpr (kLaunchRegs == 128) asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+  else asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+}
+template <int kLaunchRegs>
+__device__ __forceinline__ void fused_regs_ew() {
+  if constexpr (kLaunchRegs == 128) asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+  else asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
+}
 constexpr int kFusedStages = 3;
 constexpr int kDsBytes = kOwnRows * kStrRows * 2;  // 16 KiB: dS^T as [128 keys][64 queries] bf16
 constexpr int kDqStageBytes = 32 * kBD * 4;          // 16 KiB: 32 query rows x 128 floats on their way to the reduction
@@ -113,7 +123,8 @@ __device__ __forceinline__ void issue_dq_group(uint32_t d_tmem, uint64_t k_desc,
       : "memory");
 }
 
-__global__ void __maxnreg__(MB_FUSED_LAUNCH_REGS) attn_bwd_fused_kernel(const __grid_constant__ BwdMaps maps,
+template <int kLaunchRegs>
+__global__ void __maxnreg__(kLaunchRegs) attn_bwd_fused_kernel(const __grid_constant__ BwdMaps maps,
                                                        const __grid_constant__ BwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -177,7 +188,7 @@ __global__ void __maxnreg__(MB_FUSED_LAUNCH_REGS) attn_bwd_fused_kernel(const __
   // four warps of a warpgroup execute the same one).
   if (warp == 9) {
     // ------------------------------------------------------------------ loader
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_FSTR(MB_FUSED_AUX_REGS) ";");
+    fused_regs_aux<kLaunchRegs>();
     if (lane == 0 && total_steps > 0) {
       mbar_expect_tx(&ctl->own_full, 2 * kOwnTileBytes);
       tma_load_4d(sOwn, &maps.own, &ctl->own_full, 0, h_own, own0, b);
@@ -229,7 +240,7 @@ __global__ void __maxnreg__(MB_FUSED_LAUNCH_REGS) attn_bwd_fused_kernel(const __
     }
   } else if (warp == 8) {
     // -------------------------------------------------------------- MMA issuer
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_FSTR(MB_FUSED_AUX_REGS) ";");
+    fused_regs_aux<kLaunchRegs>();
     if (total_steps > 0) {  // whole warp, converged; one elected lane issues
       constexpr uint32_t idesc_xy = umma_idesc_bf16(kOwnRows, kStrRows, false, false);  // 128 x 64, both K-major
       constexpr uint32_t idesc_acc = umma_idesc_bf16(kOwnRows, kBD, false, true);       // 128 x 128, B MN-major
@@ -318,10 +329,10 @@ __global__ void __maxnreg__(MB_FUSED_LAUNCH_REGS) attn_bwd_fused_kernel(const __
     }
   } else if (warp == 10 || warp == 11) {
     // idle: these two warps only complete the third warpgroup
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_FSTR(MB_FUSED_AUX_REGS) ";");
+    fused_regs_aux<kLaunchRegs>();
   } else if (warp >= 12) {
     // ------------------------------------------------ drain dQ^T: tensor memory -> red.global.add
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MB_FSTR(MB_FUSED_AUX_REGS) ";");
+    fused_regs_aux<kLaunchRegs>();
     const int quarter = warp & 3;
     const int d = (quarter << 5) | lane;  // head-dim index == tensor-memory lane
     const uint32_t tq = tmem + kColDq + (static_cast<uint32_t>(quarter << 5) << 16);
@@ -388,7 +399,7 @@ __global__ void __maxnreg__(MB_FUSED_LAUNCH_REGS) attn_bwd_fused_kernel(const __
     if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ------------------------------------------------ element-wise warps (0..7) + epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 " MB_FSTR(MB_FUSED_EW_REGS) ";");
+    fused_regs_ew<kLaunchRegs>();
     const int quarter = warp & 3, half = warp >> 2;
     const int row = (quarter << 5) | lane;  // key row == tensor-memory lane
     const uint32_t lane_field = static_cast<uint32_t>(quarter << 5) << 16;
@@ -551,13 +562,20 @@ int launch_attn_bwd_fused(const BwdMaps& maps, const BwdArgs& a, dim3 grid, cuda
   int dev = 0;
   if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return MB_E_CUDA;
   if (dev >= 0 && dev < 64 && !done[dev]) {
-    if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_fused_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kFusedSmemBytes),
+                 "shared-memory attribute of attn_bwd_fused_kernel") ||
+        !cuda_ok(cudaFuncSetAttribute(attn_bwd_fused_kernel<120>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kFusedSmemBytes),
                  "shared-memory attribute of attn_bwd_fused_kernel"))
       return MB_E_CUDA;
     done[dev] = true;
   }
-  attn_bwd_fused_kernel<<<grid, kFusedThreads, kFusedSmemBytes, stream>>>(maps, a);
+  // arrival flags are raised by one-warp kernels of the transfer stream: leave them room on every SM
+  bool has_flags = false;
+  for (int s = 0; s < a.nseg; ++s) has_flags |= a.seg_flag[s] != nullptr;
+  if (has_flags) attn_bwd_fused_kernel<120><<<grid, kFusedThreads, kFusedSmemBytes, stream>>>(maps, a);
+  else attn_bwd_fused_kernel<128><<<grid, kFusedThreads, kFusedSmemBytes, stream>>>(maps, a);
   return cuda_ok(cudaGetLastError(), "launch attn_bwd_fused_kernel") ? MB_SUCCESS : MB_E_CUDA;
 }
 

@@ -748,7 +748,7 @@ class RingAttention:
         sweep (scores once, dq contributions added in fp32: see attn_bwd_fused) -- causal work is the same
         on every rank, and no gradient needs a cross-rank reduction.  It pulls its head group's rectangles of
         k | v (into one [2, B, S, hkv/P, D] buffer: the owner tiles of the launch), q, dout and the row
-        statistics (per origin: the stream segments of the launch) from every peer and waits for them; dq is converted
+        statistics (per origin, flagged: the stream segments of the launch) from every peer; dq is converted
         straight into the owners' memory, dk | dv are pushed there by the copy engines, and one flag per
         owner says that this rank's head group is in."""
         ctx, x, P, me = self.ctx, self._x, self.world, self.rank
@@ -813,12 +813,14 @@ class RingAttention:
                 rq, _ = _carve(buf, 0, (B, L, Hl, D), torch.bfloat16)
                 rdo, _ = _carve(buf, _align(q_rect_b, 256), (B, L, Hl, D), torch.bfloat16)
                 rst, _ = _carve(buf, 2 * _align(q_rect_b, 256), (2, B, Hl, pad), torch.float32)
-                sg = {"str": rq, "str_g": rdo, "stats": RowStats(rst[0], rst[1], L), "off": og * L, "dq_accum": acc}
+                sg = {"str": rq, "str_g": rdo, "stats": RowStats(rst[0], rst[1], L), "off": og * L, "dq_accum": acc,
+                      "flag": x.piece_flag_ptr(og, 1), "flag_value": e}
             segs.append(sg)
         main.wait_event(local_ready)     # my statistics were computed on the transfer stream
-        # Everything must be in before the launch: the single-sweep kernel takes every register of the SMs it
-        # runs on, so the one-warp kernels that would raise arrival flags during it could not start.
-        ctx.wait_many([(x.piece_flag_ptr(og, pc), e) for og in order[1:] for pc in (0, 1)], main)
+        # The owner tiles (K/V of every rank) must be in before the launch; q | dout | statistics are waited for
+        # in the kernel, origin by origin.  (With flagged segments the launch uses the kernel instantiation that
+        # leaves a few registers free on every SM: the one-warp kernels that raise the flags start beside it.)
+        ctx.wait_many([(x.piece_flag_ptr(og, 0), e) for og in order[1:]], main)
         _bwd_launch(_lib.MB_BWD_MODE_FUSED, bh["kv"][0], bh["kv"][1], 0, segs, Hl, hkl, softmax_scale, self.causal,
                     bh["dkv"][0], bh["dkv"][1], False)
         for n, og in enumerate(order):     # dq of owner og's rows, my head group: scaled, converted, stored there

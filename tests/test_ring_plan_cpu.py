@@ -379,7 +379,7 @@ def test_heads_schedule_plan(world, causal):
 def test_heads_backward_plan(world):
     """Heads schedule, backward: rank r pulls its head group's k | v rows of every peer into ONE owner buffer
     (row block of the origin), q | dout | statistics per origin into staging, waits for all K/V before the
-    launch (q | dout | statistics too), runs one sweep with one stream segment per origin, converts dq of origin j's rows into j's
+    launch, runs one sweep with one flagged stream segment per origin, converts dq of origin j's rows into j's
     memory at head group r, pushes dk | dv rows to their owners and raises flag 16 + r there; every owner
     waits for P such flags."""
     B, L, H, hkv, D = 2, 256, 16, 8, 128
@@ -421,10 +421,10 @@ def test_heads_backward_plan(world):
         assert kv_rows == {(og, wb) for og in range(world) for wb in range(2 * B)}
         assert pushes == {og: 2 * B for og in range(world)} and sorted(flags_to) == list(range(world))
         assert sorted(sg["off"] // L for sg in segs) == list(range(world)) and segs[0]["off"] == r * L
-        assert all("flag" not in sg and sg["dq_accum"].shape == (B, Hl, op.stat_pad, D) for sg in segs)
-        # every arrival flag is waited for before the launch (nothing can be signalled during it); the gradient
-        # flags after it
-        assert len(waits[-2]) == 2 * (world - 1) and len(waits[-1]) == world
+        assert all(("flag" in sg) == (sg["off"] != r * L) and sg["dq_accum"].shape == (B, Hl, op.stat_pad, D) for sg in segs)
+        # the K/V arrival flags of all origins are waited for before the launch (they are its owner tiles), the
+        # gradient flags after it
+        assert len(waits[-2]) == world - 1 and len(waits[-1]) == world
         assert sorted(sym.where(p_)[1] for p_, _ in waits[-1]) == [x._flag_off + ring._RES + 4 * (16 + p_) for p_ in range(world)]
         for (_, acc, ptr, strides, dims), sg in zip(conv, segs):
             owner = sg["off"] // L

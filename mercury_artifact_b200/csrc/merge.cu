@@ -24,54 +24,87 @@ struct MergeArgs {
   int block_is_f32;  // dtype of block_out
 };
 
-__device__ __forceinline__ float4 load4(const void* base, long long idx, int is_f32) {
-  if (is_f32) return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx);
-  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + idx);
-  float4 r;
-  r.x = __uint_as_float(raw.x << 16);
-  r.y = __uint_as_float(raw.x & 0xffff0000u);
-  r.z = __uint_as_float(raw.y << 16);
-  r.w = __uint_as_float(raw.y & 0xffff0000u);
-  return r;
-}
-
 // A warp takes kRowsPerWarp consecutive (b, s, h) rows per iteration: lanes 0..3 fetch the rows' two
-// log-sum-exp words and work out the weights at the same time (one round of memory latency instead of
-// one per row), then every lane issues the float4 loads of all four rows before it uses any of them.
+// log-sum-exp words and work out the weights at the same time, and every lane issues the float4 loads of all
+// four rows before it uses any of them.  The weights of the NEXT group of rows are fetched and computed while
+// the loads of the current group are in flight, so an iteration waits for memory once, not twice (with 68
+// registers per thread only 24 warps fit an SM; two dependent round trips per iteration left the kernel at
+// half the HBM rate).
 constexpr int kRowsPerWarp = 4;
 
-__global__ void __launch_bounds__(256) merge_kernel(const MergeArgs a) {
+__device__ __forceinline__ void merge_weights(const MergeArgs& a, long long row0, long long rows, int lane, float& my_w,
+                                              long long& my_brow) {
+  my_w = 0.f;
+  my_brow = 0;
+  if (lane < kRowsPerWarp && row0 + lane < rows) {
+    const long long row = row0 + lane;
+    const int h = static_cast<int>(row % a.H);
+    const long long bs = row / a.H;
+    const int s = static_cast<int>(bs % a.S);
+    const int b = static_cast<int>(bs / a.S);
+    const float bl = a.block_lse[(static_cast<long long>(b) * a.H + h) * a.S + s];
+    const float l = a.first ? -INFINITY : a.lse[row];
+    float new_l;
+    if (l == -INFINITY) {  // nothing accumulated yet for this row
+      my_w = 1.f;
+      new_l = bl;
+    } else if (bl == -INFINITY) {  // the block saw no key for this row
+      my_w = 0.f;
+      new_l = l;
+    } else {
+      const float x = bl - l;
+      // fast intrinsics: their error (2^-21 relative in the exponential, ~1e-7 absolute in the logarithm
+      // of a number in [1, 2]) is far below the bf16 block they weigh, and they keep the register count low
+      my_w = __fdividef(1.f, 1.f + __expf(-x));                 // sigmoid(block_lse - lse)
+      new_l = l + fmaxf(x, 0.f) + __logf(1.f + __expf(-fabsf(x)));  // lse - logsigmoid(lse - block_lse)
+    }
+    a.lse[row] = new_l;
+    my_brow = b * a.bo_sb + s * a.bo_ss + h * a.bo_sh;
+  }
+}
+
+// The block's values stay in the form they were loaded in (bf16 pairs: half the registers) until they are used.
+template <bool kBlockF32>
+struct BlockVec;
+template <>
+struct BlockVec<true> {
+  float4 v;
+  __device__ __forceinline__ void load(const void* base, long long idx) {
+    v = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx);
+  }
+  __device__ __forceinline__ float4 get() const { return v; }
+};
+template <>
+struct BlockVec<false> {
+  uint2 raw;
+  __device__ __forceinline__ void load(const void* base, long long idx) {
+    raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + idx);
+  }
+  __device__ __forceinline__ float4 get() const {
+    float4 r;
+    r.x = __uint_as_float(raw.x << 16);
+    r.y = __uint_as_float(raw.x & 0xffff0000u);
+    r.z = __uint_as_float(raw.y << 16);
+    r.w = __uint_as_float(raw.y & 0xffff0000u);
+    return r;
+  }
+};
+
+#ifndef MB_MERGE_BLOCKS_PER_SM
+#define MB_MERGE_BLOCKS_PER_SM 4
+#endif
+
+template <bool kBlockF32>
+__global__ void __launch_bounds__(256, MB_MERGE_BLOCKS_PER_SM) merge_kernel(const MergeArgs a) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const long long rows = static_cast<long long>(a.B) * a.S * a.H;
-  for (long long row0 = warp0 * kRowsPerWarp; row0 < rows; row0 += nwarps * kRowsPerWarp) {
-    // weight of the block and position of its row, per row of the group (lane r serves row r)
-    float my_w = 0.f;
-    long long my_brow = 0;
-    if (lane < kRowsPerWarp && row0 + lane < rows) {
-      const long long row = row0 + lane;
-      const int h = static_cast<int>(row % a.H);
-      const long long bs = row / a.H;
-      const int s = static_cast<int>(bs % a.S);
-      const int b = static_cast<int>(bs / a.S);
-      const float bl = a.block_lse[(static_cast<long long>(b) * a.H + h) * a.S + s];
-      const float l = a.first ? -INFINITY : a.lse[row];
-      float new_l;
-      if (l == -INFINITY) {  // nothing accumulated yet for this row
-        my_w = 1.f;
-        new_l = bl;
-      } else if (bl == -INFINITY) {  // the block saw no key for this row
-        my_w = 0.f;
-        new_l = l;
-      } else {
-        const float x = bl - l;
-        my_w = 1.f / (1.f + expf(-x));                          // sigmoid(block_lse - lse)
-        new_l = l + fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));  // lse - logsigmoid(lse - block_lse)
-      }
-      a.lse[row] = new_l;
-      my_brow = b * a.bo_sb + s * a.bo_ss + h * a.bo_sh;
-    }
+  const long long step = nwarps * kRowsPerWarp;
+  float my_w;
+  long long my_brow;
+  merge_weights(a, warp0 * kRowsPerWarp, rows, lane, my_w, my_brow);
+  for (long long row0 = warp0 * kRowsPerWarp; row0 < rows; row0 += step) {
     float w[kRowsPerWarp];
     long long brow[kRowsPerWarp];
 #pragma unroll
@@ -80,25 +113,29 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeArgs a) {
       brow[r] = __shfl_sync(0xffffffffu, my_brow, r);
     }
     for (int d = lane * 4; d < a.D; d += 128) {
-      float4 bo[kRowsPerWarp], o[kRowsPerWarp];
+      BlockVec<kBlockF32> bo[kRowsPerWarp];
+      float4 o[kRowsPerWarp];
 #pragma unroll
       for (int r = 0; r < kRowsPerWarp; ++r) {
         if (row0 + r < rows) {
-          bo[r] = load4(a.block_out, brow[r] + d, a.block_is_f32);
+          bo[r].load(a.block_out, brow[r] + d);
           // w == 1 adopts the block: the old state (uninitialised on the first step) is not read
           if (w[r] != 1.f) o[r] = *reinterpret_cast<const float4*>(a.out + (row0 + r) * a.D + d);
         }
       }
+      // the next group's weights, while this group's rows are on their way (once per group)
+      if (d == lane * 4 && row0 + step < rows) merge_weights(a, row0 + step, rows, lane, my_w, my_brow);
 #pragma unroll
       for (int r = 0; r < kRowsPerWarp; ++r) {
         if (row0 + r < rows) {
-          float4 v = bo[r];
+          const float4 bv = bo[r].get();
+          float4 v = bv;
           if (w[r] != 1.f) {
             v = o[r];
-            v.x -= w[r] * (v.x - bo[r].x);
-            v.y -= w[r] * (v.y - bo[r].y);
-            v.z -= w[r] * (v.z - bo[r].z);
-            v.w -= w[r] * (v.w - bo[r].w);
+            v.x -= w[r] * (v.x - bv.x);
+            v.y -= w[r] * (v.y - bv.y);
+            v.z -= w[r] * (v.z - bv.z);
+            v.w -= w[r] * (v.w - bv.w);
           }
           *reinterpret_cast<float4*>(a.out + (row0 + r) * a.D + d) = v;
         }
@@ -250,9 +287,10 @@ int launch_merge(const mb_merge_args* x, cudaStream_t stream) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long want = (rows + 8 * kRowsPerWarp - 1) / (8 * kRowsPerWarp);  // 8 warps per block
-  const long long cap = static_cast<long long>(sms) * 8;
+  const long long cap = static_cast<long long>(sms) * MB_MERGE_BLOCKS_PER_SM;  // one resident wave, grid-stride loop
   const int grid = static_cast<int>(want < cap ? want : cap);
-  merge_kernel<<<grid, 256, 0, stream>>>(a);
+  if (a.block_is_f32) merge_kernel<true><<<grid, 256, 0, stream>>>(a);
+  else merge_kernel<false><<<grid, 256, 0, stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? MB_SUCCESS : MB_E_CUDA;
 }
 

@@ -225,6 +225,32 @@ def run_reference(args):
     return 0
 
 
+def bind_host_to_gpu_node(device_index):
+    """Run this process on the CPUs of the NUMA node the GPU hangs off, so that the pinned host buffers of the
+    host-buffer leg are allocated there (a far node halves the PCIe rate the copies see).  Returns
+    (description, previous affinity) -- (None, None) where the node is unknown."""
+    try:
+        import torch
+
+        pr = torch.cuda.get_device_properties(device_index)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read().strip())
+        if node < 0:
+            return None, None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        before = os.sched_getaffinity(0)
+        cpus &= before
+        if not cpus:
+            return None, None
+        os.sched_setaffinity(0, cpus)
+        return f"GPU {bdf} on NUMA node {node}: process bound to its {len(cpus)} CPUs while the pinned buffers were made", before
+    except Exception:
+        return None, None
+
+
 def workload_name(w, n):
     B, S, H, hkv, D, causal = WORKLOADS[w]
     return (f"{w}: ring-attention forward bf16 B{B} S{S} Hq{H} Hkv{hkv} D{D} "
@@ -502,9 +528,12 @@ def run_ours(args):
                 pass
             op = RingAttention(mesh, B, L, H, hkv, D, causal=causal, backward=True, schedule="ring")
             q, kv, dout, o, lse = job.inputs_in(op, B, L, H, hkv, D, with_dout=True)
+    numa_note, affinity_before = bind_host_to_gpu_node(job.local_rank)
     q_host, kv_host = q.cpu().pin_memory(), kv.cpu().pin_memory()
     o_host = torch.empty(B, L, H, D, dtype=torch.bfloat16).pin_memory()
     lse_host = torch.empty(B, H, L, dtype=torch.float32).pin_memory()
+    if affinity_before is not None:
+        os.sched_setaffinity(0, affinity_before)      # the CPU arm and everything else run where they did
     stream = job.stream
 
     def step_resident():
@@ -612,6 +641,7 @@ def run_ours(args):
                                                        (world - 1) * B * L * (H + 2 * hkv) // world * D * 2 / 2 ** 20)),
                 "schedule": getattr(op, "schedule", "ring") if world > 1 else "one rank",
                 "schedule_note": schedule_note,
+                "host_numa": numa_note,
                 "per_gpu_tflops": per_gpu,
                 "buffers": "q / kv / o / lse in the op's symmetric buffers (zero-copy mode)" if world > 1 else "ordinary tensors",
                 "ms_per_step_with_ordinary_tensors": ms_plain,

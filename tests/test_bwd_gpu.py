@@ -215,3 +215,44 @@ def test_backward_full_size_property_config5_shard():
     dq0 = mb.attn_bwd_dq(q, z, st0, [(k, v, 0)], scale, causal=True)
     dk0, dv0 = mb.attn_bwd_dkv(k, v, [(q, z, st0, 0)], scale, causal=True)
     assert (dq0 == 0).all() and (dk0 == 0).all() and (dv0 == 0).all()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_single_sweep_with_eight_query_segments_like_one_rank_of_eight(causal):
+    """The backward launch one rank of an 8-rank heads schedule issues, with all data local: the K/V rows of
+    all eight shards as ONE owner tensor, the query rows (q, dout, statistics) of the eight shards as eight
+    stream segments in an arrival order that starts in the middle, one fp32 dq accumulation per segment, each
+    converted into its place of a strided dq tensor (a head group inside a wider tensor).  GQA 4/2 heads."""
+    import mercury_artifact_b200 as mb
+    from mercury_artifact_b200 import _lib
+    from mercury_artifact_b200.attention import RowStats, _bwd_launch, dq_convert_raw
+
+    P, B, L, Hq, Hkv, D = 8, 1, 256, 4, 2, 128
+    S = P * L
+    q, k, v, do = seeded_qkv(31, B, S, Hq, Hkv, D)
+    scale = D ** -0.5
+    ro, rl, rdq, rdk, rdv = _reference(q, k, v, do, scale, causal, 0)
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    od, ld = ro.cuda(), rl.cuda()
+    me = 5
+    order = [me] + [(me - t) % P for t in range(1, P)]
+    segs, accs = [], []
+    for j in order:
+        rows = slice(j * L, (j + 1) * L)
+        st = mb.bwd_preprocess(dod[:, rows].contiguous(), od[:, rows].contiguous(), ld[:, :, rows].contiguous())
+        acc = torch.zeros(B, Hq, st.pad, D, dtype=torch.float32, device="cuda")
+        accs.append(acc)
+        segs.append({"str": qd[:, rows], "str_g": dod[:, rows], "stats": RowStats(st.lse2, st.delta, L), "off": j * L,
+                     "dq_accum": acc})
+    dk, dv = torch.empty_like(kd), torch.empty_like(vd)
+    _bwd_launch(_lib.MB_BWD_MODE_FUSED, kd, vd, 0, segs, Hq, Hkv, scale, causal, dk, dv, False)
+    wide = torch.zeros(B, S, 3 * Hq, D, dtype=torch.bfloat16, device="cuda")      # dq lands in heads Hq..2Hq-1
+    for acc, j in zip(accs, order):
+        dq_convert_raw(acc, wide[:, j * L, Hq].data_ptr(), (wide.stride(0), wide.stride(1), wide.stride(2)), B, L, Hq,
+                       acc.shape[2], scale)
+    _status_ok()
+    assert wide[:, :, :Hq].abs().max().item() == 0 and wide[:, :, 2 * Hq:].abs().max().item() == 0
+    for got, want in ((wide[:, :, Hq:2 * Hq], rdq), (dk, rdk), (dv, rdv)):
+        got = got.float().cpu()
+        assert not torch.isnan(got).any()
+        assert (got - want).abs().max().item() <= G_TOL

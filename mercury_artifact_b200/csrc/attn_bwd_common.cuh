@@ -176,8 +176,14 @@ __device__ __forceinline__ void ew_compute(const uint32_t (&xr)[32], const uint3
   const uint64_t row_nl2 = pack2(row_nl, row_nl), row_d2 = pack2(row_d, row_d);
 #pragma unroll
   for (int e = 0; e < 32; e += 2) {
-    const uint64_t nl2 = kDkv ? *reinterpret_cast<const uint64_t*>(nl_col + e) : row_nl2;
-    const uint64_t d2 = kDkv ? *reinterpret_cast<const uint64_t*>(d_col + e) : row_d2;
+    // per-column statistics: one 16-byte broadcast load serves two pairs (the arrays are 16-byte aligned)
+    uint64_t nl2 = row_nl2, d2 = row_d2;
+    if (kDkv) {
+      const ulonglong2 nl4 = *reinterpret_cast<const ulonglong2*>(nl_col + (e & ~3));
+      const ulonglong2 d4 = *reinterpret_cast<const ulonglong2*>(d_col + (e & ~3));
+      nl2 = (e & 2) ? nl4.y : nl4.x;
+      d2 = (e & 2) ? d4.y : d4.x;
+    }
     const uint64_t t2 = fma2(pack2(__uint_as_float(xr[e]), __uint_as_float(xr[e + 1])), c2, nl2);
     float t0, t1;
     unpack2(t2, t0, t1);

@@ -231,7 +231,7 @@ class RingAttention:
         self._monitor = getattr(self.ctx, "monitor", None) or _lib.StatusMonitor()
         # Causal attention over contiguous shards gives rank r (r + 1/2) blocks of forward work.  With
         # balancing, the forward re-assigns query half-shards so that every rank computes the same
-        # amount (see _jobs_balanced); inputs and outputs keep the contiguous layout.  The backward
+        # amount; inputs and outputs keep the contiguous layout.  The backward
         # needs no such re-assignment: rank r does (r + 1/2) blocks of dQ work and (P - r - 1/2) blocks
         # of dK/dV work, P blocks on every rank.
         self.balanced = bool(balance_causal) and self.causal and self.world > 1 and seq_local % 2 == 0
@@ -243,7 +243,7 @@ class RingAttention:
         # of the reference's search space (mercury/search) applied inside the call: inputs and outputs keep
         # the sequence-sharded layout.  Default (None, or MB_SCHEDULE): "heads" on a one-dimensional mesh of up
         # to 8 ranks when both head counts divide by the world size and balance_causal is on, else "ring".
-        # The backward always uses the ring schedule.
+        # The heads schedule's backward is head-parallel too (_backward_heads).
         schedule = schedule or os.environ.get("MB_SCHEDULE") or None
         can_heads = (self.world > 1 and len(self.mesh_shape) == 1 and self.world <= 8 and hq % self.world == 0
                      and hkv % self.world == 0 and self.world <= _lib.MB_MAX_SEGMENTS)
@@ -295,8 +295,9 @@ class RingAttention:
                              "(the row statistics travel in 64-row blocks)")
         self.last_launches = 0   # kernels this object launched in its latest forward() / backward()
         # World size 1 runs the backward as one sweep whose dq depends on the order of fp32 additions; set
-        # this to get the two-launch form, which is bitwise reproducible.  (On several ranks the two-launch
-        # form is always used: it needs no cross-rank reduction of dq contributions.)
+        # this to get the two-launch form, which is bitwise reproducible.  (On several ranks the ring
+        # schedule always uses the two-launch form -- it needs no cross-rank reduction of dq contributions --
+        # and the heads schedule always the sweep.)
         self.deterministic_backward = False
 
     # ------------------------------------------------------------------ helpers

@@ -360,6 +360,10 @@ def test_heads_schedule_plan(world, causal):
                 if len(mine) > 1:
                     assert bool(jb["state_in"]) == (p > 0) and bool(jb["state_out"]) == (not last)
                     assert jb["state"][0].shape == (B, Hl, L, D)
+                    # the link before it in the chain is EARLIER in the launch (CTAs are dispatched in job order)
+                    # and sets exactly the value this one waits for, on the same words
+                    assert jb["chain"][0] == mine[0][1]["chain"][0] and jb["chain"][1:] == (64 + p, 64 + p + 1)
+                    assert p == 0 or mine[p - 1][0] < n
                 assert ("done" in jb) == last
                 assert ("q_flag" in jb) == (owner != r)
             assert sorted(seen) == [s_ for s_ in range(world) if (not causal) or s_ <= owner]

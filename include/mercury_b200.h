@@ -111,7 +111,9 @@ typedef struct mb_fwd_job {
    * that is still in flight.  If the jobs of a chain are in ONE launch, give them chain: int32 words
    * [batch, hq, ceil(sq / 256)] on this GPU; a job with state_out stores chain_set to its CTA's word
    * after its state (release), a job with state_in waits (bounded, status 109) until the word is
-   * >= chain_wait.  The continuing job must come later in job[] (CTAs are dispatched in job order).
+   * >= chain_wait.  The continuing job must come later in job[] (CTAs are dispatched in job order), and the
+   * values must grow from launch to launch (or the words be cleared in between): a word left at an old value
+   * that already satisfies the wait lets a link start before the link before it has stored its state.
    * With chain == NULL the jobs must be in different launches of one stream. */
   float* state_o;
   float* state_ml;

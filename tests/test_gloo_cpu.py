@@ -127,3 +127,45 @@ def test_causal_pull_sets_cover_exactly_the_visible_shards():
             assert sorted(seen_by + [r]) == list(range(r, p))
             # every unordered pair of ranks exchanges at least one direction under the causal rule
             assert set(sees) | set(seen_by) == set(range(p)) - {r}
+
+
+def _heads_plan_worker(rank, world, port, ret):
+    """One gloo rank: its own heads-schedule plan (forward and backward) against a recording context, then an
+    all-gather of who delivers which head group to whom."""
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from mercury_artifact_b200 import ring
+    from tests.test_ring_plan_cpu import _run_rank
+
+    L = 256
+    op, launches, fwd_ops, bwd_ops = _run_rank(dist.get_rank(), dist.get_world_size(), (world,), True, 1, True,
+                                               B=1, L=L, H=4, hkv=2, schedule="heads")
+    x = op._x
+    fwd = [l for l in launches if l[0] == "fwd"][0]
+    delivers = sorted((x.sym.where(jb["out_raw"][0])[0], rank) for jb in fwd[1] if "out_raw" in jb)
+    pulls = sorted({x.sym.where(p[2])[0] for k, s, p in fwd_ops if k == "copy2d"})
+    grads = sorted({x.sym.where(p[0])[0] for k, s, p in bwd_ops if k == "copy2d" and x.sym.where(p[0]) is not None
+                    and x.sym.where(p[0])[1] >= x.slot_bytes + op._inbox_dkv})
+    gathered = [None] * world
+    dist.all_gather_object(gathered, {"delivers": delivers, "pulls": pulls, "grads": grads})
+    ret[rank] = gathered
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_heads_schedule_plans_of_two_gloo_ranks_fit_together():
+    """world_size 2 over gloo: every (owner, head group) pair of the forward is delivered by exactly one rank,
+    every rank pulls from its peer, and the backward pushes dk | dv rows to both owners."""
+    import torch.multiprocessing as mp
+
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(_heads_plan_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for r in range(world):
+        views = ret[r]
+        assert sorted(d for v in views for d in v["delivers"]) == [(o, g) for o in range(world) for g in range(world)]
+        for p, v in enumerate(views):
+            assert v["pulls"] == [q for q in range(world) if q != p]
+            assert v["grads"] == list(range(world))
